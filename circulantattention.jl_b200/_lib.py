@@ -1,0 +1,87 @@
+"""ctypes binding of libcircatt_b200.so (the C ABI declared in include/circatt_b200.h).
+
+There is no CPU path, as in the reference ("only CUDA compatible",
+README.md:20): if the shared library has not been built, importing this module
+raises, and every op raises on non-CUDA tensors.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libcircatt_b200.so")
+
+CA_F32, CA_C64 = 0, 1
+CA_DOT, CA_DISTANCE = 0, 1
+CA_SOFTMAX, CA_ENTMAX15 = 0, 1
+
+
+class CircAttError(RuntimeError):
+    """A non-zero status from the C ABI (the Julia wrapper would raise ErrorException)."""
+
+
+class ca_desc(C.Structure):
+    _fields_ = [
+        ("H", C.c_int32), ("W", C.c_int32), ("ndim", C.c_int32), ("channels", C.c_int32),
+        ("units", C.c_int32), ("ws", C.c_int32), ("dtype", C.c_int32), ("similarity", C.c_int32),
+        ("normalizer", C.c_int32), ("Wk", C.c_int32), ("wk_off", C.c_int32), ("scale", C.c_float),
+    ]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback.")
+    return C.CDLL(LIB_PATH)
+
+
+lib = _load()
+
+_p = C.c_void_p
+_D = C.POINTER(ca_desc)
+_i32, _i64, _f32 = C.c_int32, C.c_int64, C.c_float
+
+PROTOTYPES = {
+    "ca_version": (C.c_int, []),
+    "ca_last_error": (C.c_char_p, []),
+    "ca_structure": (C.c_int, [_i32, _i32, _i32, _i32, _i64, _p, _p, _p]),
+    "ca_similarity": (C.c_int, [_D, _p, _p, _p, _p]),
+    "ca_similarity_bwd": (C.c_int, [_D, _p, _p, _p, _p, _p, _p]),
+    "ca_row_normalize": (C.c_int, [_D, _p, _p, _p, _p]),
+    "ca_row_normalize_bwd": (C.c_int, [_D, _p, _p, _p, _p]),
+    "ca_apply": (C.c_int, [_D, _p, _p, _p, _i32, _i32, _i32, _p]),
+    "ca_attention_fwd_workspace": (C.c_size_t, [_D, _i32]),
+    "ca_attention_fwd": (C.c_int, [_D, _p, _p, _p, _p, _p, _p, _p, _p]),
+    "ca_attention_bwd_workspace": (C.c_size_t, [_D]),
+    "ca_attention_bwd": (C.c_int, [_D] + [_p] * 13),
+    "ca_attention_bwd_pre": (C.c_int, [_D] + [_p] * 10),
+    "ca_attention_bwd_dq": (C.c_int, [_D] + [_p] * 9),
+    "ca_attention_bwd_dkdv": (C.c_int, [_D] + [_p] * 10),
+    "ca_axpby": (C.c_int, [_i64, _f32, _p, _f32, _p, _p, _p]),
+    "ca_scale_batch": (C.c_int, [_i64, _i32, _i32, _p, _i32, _i32, _p, _i32, _i32, _p, _p]),
+    "ca_dot_batch": (C.c_int, [_i64, _i32, _i32, _p, _i32, _i32, _p, _i32, _i32, _p, _p]),
+    "ca_sum_batch": (C.c_int, [_i64, _i32, _i32, _i32, _i32, _p, _p, _p]),
+    "ca_sum_rows": (C.c_int, [_D, _p, _p, _p]),
+    "ca_sum_cols": (C.c_int, [_D, _p, _p, _p]),
+}
+
+for _name, (_res, _args) in PROTOTYPES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    return lib.ca_last_error().decode()
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise CircAttError(f"circatt_b200 status {rc}: {last_error()}")
+
+
+def ptr(t):
+    """Device pointer of a tensor (None -> NULL)."""
+    return None if t is None else C.c_void_p(t.data_ptr())

@@ -1,0 +1,439 @@
+// C ABI of the circulant-attention library: argument checks and dispatch.
+#include "common.cuh"
+#include "rowops.cuh"
+#include "window_generic.cuh"
+#include "tiled.cuh"
+
+#include <string.h>
+
+namespace ca {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return CA_ERR_CUDA;
+}
+
+int make_geo(const ca_desc* d, Geo* g, bool allow_band) {
+    if (!d) { set_error("descriptor is NULL"); return CA_ERR_NULL; }
+    if (d->ndim != 1 && d->ndim != 2) { set_error("ndim=%d: only 1 or 2 spatial dims are supported", d->ndim); return CA_ERR_BAD_DESC; }
+    if (d->ws < 1 || d->ws % 2 != 1) { set_error("filter size M=%d must be odd.", d->ws); return CA_ERR_BAD_DESC; }
+    if (d->H < d->ws) { set_error("spatial extent %d is smaller than the window %d", d->H, d->ws); return CA_ERR_BAD_DESC; }
+    if (d->ndim == 1 && d->W != 1) { set_error("1-D signals must have W == 1 (got %d)", d->W); return CA_ERR_BAD_DESC; }
+    if (d->channels < 1 || d->units < 1) { set_error("channels=%d units=%d must be positive", d->channels, d->units); return CA_ERR_BAD_DESC; }
+    if (d->dtype != CA_F32 && d->dtype != CA_C64) { set_error("unknown dtype %d", d->dtype); return CA_ERR_BAD_DESC; }
+    if (d->similarity != CA_DOT && d->similarity != CA_DISTANCE) { set_error("unknown similarity %d", d->similarity); return CA_ERR_BAD_DESC; }
+    if (d->normalizer != CA_SOFTMAX && d->normalizer != CA_ENTMAX15) { set_error("unknown normalizer %d", d->normalizer); return CA_ERR_BAD_DESC; }
+    const int p = (d->ws - 1) / 2;
+    const bool band = d->Wk != 0 && d->Wk != d->W;
+    if (band) {
+        if (!allow_band) { set_error("band mode (Wk != W) is not supported by this entry point"); return CA_ERR_UNSUPPORTED; }
+        if (d->ndim != 2) { set_error("band mode needs 2 spatial dims"); return CA_ERR_BAD_DESC; }
+        if (d->wk_off < p || d->wk_off + d->W + p > d->Wk) {
+            set_error("band mode: key-side tensor (Wk=%d, offset %d) does not cover the window of %d query columns", d->Wk, d->wk_off, d->W);
+            return CA_ERR_BAD_DESC;
+        }
+    } else if (d->ndim == 2 && d->W < d->ws) {
+        set_error("spatial extent %d is smaller than the window %d", d->W, d->ws);
+        return CA_ERR_BAD_DESC;
+    }
+    g->H = d->H; g->W = d->W;
+    g->Wk = band ? d->Wk : d->W;
+    g->wk_off = band ? d->wk_off : 0;
+    g->ws = d->ws; g->p = p;
+    g->wsw = d->ndim == 2 ? d->ws : 1;
+    g->K = g->ws * g->wsw;
+    const int64_t np = (int64_t)d->H * d->W, npk = (int64_t)d->H * g->Wk;
+    if (np > INT32_MAX / 2 || npk > INT32_MAX / 2) { set_error("more than 2^30 pixels per unit"); return CA_ERR_TOO_LARGE; }
+    g->Np = (int)np; g->Npk = (int)npk;
+    g->units = d->units;
+    g->c = d->channels;
+    g->cpe = d->dtype == CA_C64 ? 2 : 1;
+    g->cr = g->c * g->cpe;
+    if (d->units > 65535) { set_error("units=%d exceeds the grid limit 65535", d->units); return CA_ERR_TOO_LARGE; }
+    return CA_OK;
+}
+
+static int pick_cmax(int cr) {
+    for (int c : {4, 8, 16, 32, 64}) if (cr <= c) return c;
+    return 0;
+}
+
+#define CA_DISPATCH_CMAX(cmax, cpe, CALL)                                           \
+    do {                                                                            \
+        if (cpe == 1) {                                                             \
+            switch (cmax) {                                                         \
+                case 4:  { constexpr int CM = 4;  constexpr int CP = 1; CALL; } break; \
+                case 8:  { constexpr int CM = 8;  constexpr int CP = 1; CALL; } break; \
+                case 16: { constexpr int CM = 16; constexpr int CP = 1; CALL; } break; \
+                case 32: { constexpr int CM = 32; constexpr int CP = 1; CALL; } break; \
+                default: { constexpr int CM = 64; constexpr int CP = 1; CALL; } break; \
+            }                                                                       \
+        } else {                                                                    \
+            switch (cmax) {                                                         \
+                case 4:  { constexpr int CM = 4;  constexpr int CP = 2; CALL; } break; \
+                case 8:  { constexpr int CM = 8;  constexpr int CP = 2; CALL; } break; \
+                case 16: { constexpr int CM = 16; constexpr int CP = 2; CALL; } break; \
+                case 32: { constexpr int CM = 32; constexpr int CP = 2; CALL; } break; \
+                default: { constexpr int CM = 64; constexpr int CP = 2; CALL; } break; \
+            }                                                                       \
+        }                                                                           \
+    } while (0)
+
+static int launch_similarity(const Geo& g, float scale, int dist, const float* x, const float* y,
+                             float* nz, cudaStream_t st) {
+    dim3 grid((g.Np + 127) / 128, g.units);
+    if (g.cpe == 1) similarity_generic<1><<<grid, 128, 0, st>>>(g, scale, dist, x, y, nz);
+    else similarity_generic<2><<<grid, 128, 0, st>>>(g, scale, dist, x, y, nz);
+    CA_CHECK_LAUNCH("similarity kernel");
+    return CA_OK;
+}
+
+static int launch_apply(const Geo& g, const float* nz, const float* v, const float* center, float* out,
+                        float alpha, int transpose, int a_bcast, int v_bcast, cudaStream_t st) {
+    ApplyArgs a{g, nz, v, center, out, alpha, transpose, a_bcast, v_bcast};
+    if (g.cr > 65535) { set_error("more than 65535 real channels per unit"); return CA_ERR_TOO_LARGE; }
+    dim3 grid((g.Np + 127) / 128, g.cr, g.units);
+    if (g.cpe == 1) apply_generic<1><<<grid, 128, 0, st>>>(a);
+    else apply_generic<2><<<grid, 128, 0, st>>>(a);
+    CA_CHECK_LAUNCH("apply kernel");
+    return CA_OK;
+}
+
+static int launch_row_normalize(int64_t rows, int K, int entmax, const float* s, float* p, float* stats,
+                                cudaStream_t st) {
+    const int64_t blocks = (rows * 32 + 255) / 256;
+    if (blocks > INT32_MAX) { set_error("too many rows"); return CA_ERR_TOO_LARGE; }
+    if (entmax) row_entmax15_kernel<<<(unsigned)blocks, 256, 0, st>>>(rows, K, s, p, stats);
+    else row_softmax_kernel<<<(unsigned)blocks, 256, 0, st>>>(rows, K, s, p, stats);
+    CA_CHECK_LAUNCH("row normalize kernel");
+    return CA_OK;
+}
+
+static int check_nnz(const Geo& g) {
+    // the reference stores nnz as Int32 (src/circulant.jl:64,86)
+    const int64_t nnz = (int64_t)g.Np * g.K;
+    if (nnz > INT32_MAX) { set_error("Np*K = %lld entries per unit exceed Int32", (long long)nnz); return CA_ERR_TOO_LARGE; }
+    return CA_OK;
+}
+
+static int elementwise_grid(int64_t n) {
+    int64_t b = (n + 255) / 256;
+    const int64_t cap = 148 * 16;
+    return (int)(b < cap ? (b < 1 ? 1 : b) : cap);
+}
+
+}  // namespace ca
+
+using namespace ca;
+
+extern "C" {
+
+int ca_version(void) { return 100; }
+
+const char* ca_last_error(void) { return g_err; }
+
+int ca_structure(int32_t H, int32_t W, int32_t ndim, int32_t ws, int64_t nbatch,
+                 int32_t* rowptr, int32_t* colval, void* stream) {
+    ca_desc d{};
+    d.H = H; d.W = W; d.ndim = ndim; d.ws = ws; d.channels = 1; d.units = 1;
+    Geo g;
+    int rc = make_geo(&d, &g, false);
+    if (rc) return rc;
+    if (!rowptr || !colval) { set_error("rowptr/colval is NULL"); return CA_ERR_NULL; }
+    if (nbatch < 1) { set_error("nbatch must be positive"); return CA_ERR_BAD_DESC; }
+    if ((rc = check_nnz(g))) return rc;
+    const int64_t n = (int64_t)g.Np * g.K;   // >= Np+1 because K >= 1... guard the 1x1 window
+    const int64_t threads = n > g.Np + 1 ? n : g.Np + 1;
+    structure_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, as_stream(stream)>>>(
+        g.H, g.W, g.ws, g.wsw, nbatch, rowptr, colval);
+    CA_CHECK_LAUNCH("structure kernel");
+    return CA_OK;
+}
+
+int ca_similarity(const ca_desc* d, const void* x, const void* y, float* nz, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, false);
+    if (rc) return rc;
+    if (!x || !y || !nz) { set_error("x/y/nz is NULL"); return CA_ERR_NULL; }
+    if ((rc = check_nnz(g))) return rc;
+    return launch_similarity(g, d->scale, d->similarity == CA_DISTANCE, (const float*)x, (const float*)y, nz,
+                             as_stream(stream));
+}
+
+int ca_similarity_bwd(const ca_desc* d, const void* x, const void* y, const float* dS,
+                      void* dx, void* dy, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, false);
+    if (rc) return rc;
+    if (!x || !y || !dS) { set_error("x/y/dS is NULL"); return CA_ERR_NULL; }
+    const bool dist = d->similarity == CA_DISTANCE;
+    cudaStream_t st = as_stream(stream);
+    if (dx && (rc = launch_apply(g, dS, (const float*)y, dist ? (const float*)x : nullptr, (float*)dx,
+                                 d->scale, 0, 0, 0, st))) return rc;
+    if (dy && (rc = launch_apply(g, dS, (const float*)x, dist ? (const float*)y : nullptr, (float*)dy,
+                                 d->scale, 1, 0, 0, st))) return rc;
+    return CA_OK;
+}
+
+int ca_row_normalize(const ca_desc* d, const float* s, float* p, float* stats, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, false);
+    if (rc) return rc;
+    if (!s || !p) { set_error("s/p is NULL"); return CA_ERR_NULL; }
+    return launch_row_normalize((int64_t)g.Np * g.units, g.K, d->normalizer == CA_ENTMAX15, s, p, stats,
+                                as_stream(stream));
+}
+
+int ca_row_normalize_bwd(const ca_desc* d, const float* p, const float* dp, float* ds, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, false);
+    if (rc) return rc;
+    if (!p || !dp || !ds) { set_error("p/dp/ds is NULL"); return CA_ERR_NULL; }
+    const int64_t rows = (int64_t)g.Np * g.units;
+    row_normalize_bwd_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, as_stream(stream)>>>(
+        rows, g.K, d->normalizer == CA_ENTMAX15, p, dp, ds);
+    CA_CHECK_LAUNCH("row normalize pullback kernel");
+    return CA_OK;
+}
+
+int ca_apply(const ca_desc* d, const float* nz, const void* v, void* out,
+             int32_t transpose, int32_t a_bcast, int32_t v_bcast, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, false);
+    if (rc) return rc;
+    if (!nz || !v || !out) { set_error("nz/v/out is NULL"); return CA_ERR_NULL; }
+    if (!a_bcast && !v_bcast && !transpose) {
+        rc = tiled_apply(g, nz, (const float*)v, (float*)out, as_stream(stream));
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+    }
+    return launch_apply(g, nz, (const float*)v, nullptr, (float*)out, 1.f, transpose, a_bcast, v_bcast,
+                        as_stream(stream));
+}
+
+size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {
+    Geo g;
+    if (make_geo(d, &g, true)) return 0;
+    if (d->normalizer == CA_ENTMAX15 && !want_nz) return (size_t)g.Np * g.K * g.units * sizeof(float);
+    return 0;
+}
+
+int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void* v,
+                     void* y, float* nz, float* stats, void* workspace, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, true);
+    if (rc) return rc;
+    if (!q || !k || !v || !y) { set_error("q/k/v/y is NULL"); return CA_ERR_NULL; }
+    const bool band = g.Wk != g.W;
+    if (nz && band) { set_error("band mode never materialises A"); return CA_ERR_UNSUPPORTED; }
+    if (nz && (rc = check_nnz(g))) return rc;
+    cudaStream_t st = as_stream(stream);
+    const int dist = d->similarity == CA_DISTANCE;
+
+    if (d->normalizer == CA_ENTMAX15) {
+        // scores -> threshold per row -> apply; the scores live in nz or in the workspace
+        if (band) { set_error("entmax in band mode is not implemented"); return CA_ERR_UNSUPPORTED; }
+        if ((rc = check_nnz(g))) return rc;
+        float* sbuf = nz ? nz : (float*)workspace;
+        if (!sbuf) { set_error("entmax without nz needs a workspace of ca_attention_fwd_workspace() bytes"); return CA_ERR_NULL; }
+        if ((rc = launch_similarity(g, d->scale, dist, (const float*)q, (const float*)k, sbuf, st))) return rc;
+        if ((rc = launch_row_normalize((int64_t)g.Np * g.units, g.K, 1, sbuf, sbuf, stats, st))) return rc;
+        rc = tiled_apply(g, sbuf, (const float*)v, (float*)y, st);
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+        return launch_apply(g, sbuf, (const float*)v, nullptr, (float*)y, 1.f, 0, 0, 0, st);
+    }
+
+    rc = tiled_attention_fwd(g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v,
+                             (float*)y, nz, stats, st);
+    if (rc != CA_ERR_UNSUPPORTED) return rc;
+
+    const int cmax = pick_cmax(g.cr);
+    if (!cmax) { set_error("fused attention supports at most 64 real channels per unit (got %d); use similarity + normalize + apply", g.cr); return CA_ERR_UNSUPPORTED; }
+    FwdArgs a{g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v, (float*)y, nz, stats};
+    dim3 grid((g.Np + 127) / 128, g.units);
+    CA_DISPATCH_CMAX(cmax, g.cpe, (fwd_softmax_generic<CM, CP><<<grid, 128, 0, st>>>(a)));
+    CA_CHECK_LAUNCH("fused forward kernel");
+    return CA_OK;
+}
+
+size_t ca_attention_bwd_workspace(const ca_desc* d) {
+    Geo g;
+    if (make_geo(d, &g, true)) return 0;
+    return (size_t)g.Npk * g.units * sizeof(float);
+}
+
+int ca_attention_bwd_pre(const ca_desc* d, const void* q, const void* k, const void* v,
+                         const void* y, const void* dy, const float* stats,
+                         const float* nz, const float* dA, float* D, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, true);
+    if (rc) return rc;
+    if (!dy || !D) { set_error("dy/D is NULL"); return CA_ERR_NULL; }
+    if (dA && !nz && d->normalizer == CA_SOFTMAX) { set_error("a cotangent on A needs the saved A (nz)"); return CA_ERR_NULL; }
+    if (dA && g.Wk != g.W) { set_error("band mode never materialises A"); return CA_ERR_UNSUPPORTED; }
+    cudaStream_t st = as_stream(stream);
+    BwdArgs a{g, d->scale, d->similarity == CA_DISTANCE, d->normalizer == CA_ENTMAX15,
+              (const float*)q, (const float*)k, (const float*)v, (const float*)y, (const float*)dy,
+              stats, nz, dA, D, nullptr, nullptr, nullptr};
+    dim3 grid((g.Np + 127) / 128, g.units);
+    if (a.entmax) {
+        if (!q || !k || !v || !stats) { set_error("q/k/v/stats is NULL"); return CA_ERR_NULL; }
+        const int cmax = pick_cmax(g.cr);
+        if (!cmax) { set_error("fused attention supports at most 64 real channels per unit (got %d)", g.cr); return CA_ERR_UNSUPPORTED; }
+        CA_DISPATCH_CMAX(cmax, g.cpe, (bwd_query_generic<CM, CP, 1><<<grid, 128, 0, st>>>(a)));
+    } else {
+        if (!y) { set_error("y is NULL"); return CA_ERR_NULL; }
+        if (g.cpe == 1) bwd_pre_softmax<1><<<grid, 128, 0, st>>>(a);
+        else bwd_pre_softmax<2><<<grid, 128, 0, st>>>(a);
+    }
+    CA_CHECK_LAUNCH("backward pre-pass kernel");
+    return CA_OK;
+}
+
+int ca_attention_bwd_dq(const ca_desc* d, const void* q, const void* k, const void* v,
+                        const void* dy, const float* stats, const float* D, const float* dA,
+                        void* dq, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, true);
+    if (rc) return rc;
+    if (!q || !k || !v || !dy || !stats || !D || !dq) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
+    if (dA && g.Wk != g.W) { set_error("band mode never materialises A"); return CA_ERR_UNSUPPORTED; }
+    cudaStream_t st = as_stream(stream);
+    const int dist = d->similarity == CA_DISTANCE, ent = d->normalizer == CA_ENTMAX15;
+    if (!ent && !dA) {
+        rc = tiled_attention_bwd_dq(g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v,
+                                    (const float*)dy, stats, D, (float*)dq, st);
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+    }
+    const int cmax = pick_cmax(g.cr);
+    if (!cmax) { set_error("fused attention supports at most 64 real channels per unit (got %d)", g.cr); return CA_ERR_UNSUPPORTED; }
+    BwdArgs a{g, d->scale, dist, ent, (const float*)q, (const float*)k, (const float*)v, nullptr,
+              (const float*)dy, stats, nullptr, dA, const_cast<float*>(D), (float*)dq, nullptr, nullptr};
+    dim3 grid((g.Np + 127) / 128, g.units);
+    CA_DISPATCH_CMAX(cmax, g.cpe, (bwd_query_generic<CM, CP, 0><<<grid, 128, 0, st>>>(a)));
+    CA_CHECK_LAUNCH("backward dq kernel");
+    return CA_OK;
+}
+
+int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const void* v,
+                          const void* dy, const float* stats, const float* D, const float* dA,
+                          void* dk, void* dv, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, true);
+    if (rc) return rc;
+    if (!q || !k || !v || !dy || !stats || !D || !dk || !dv) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
+    if (dA && g.Wk != g.W) { set_error("band mode never materialises A"); return CA_ERR_UNSUPPORTED; }
+    cudaStream_t st = as_stream(stream);
+    const int dist = d->similarity == CA_DISTANCE, ent = d->normalizer == CA_ENTMAX15;
+    if (!ent && !dA) {
+        rc = tiled_attention_bwd_dkdv(g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v,
+                                      (const float*)dy, stats, D, (float*)dk, (float*)dv, st);
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+    }
+    const int cmax = pick_cmax(g.cr);
+    if (!cmax) { set_error("fused attention supports at most 64 real channels per unit (got %d)", g.cr); return CA_ERR_UNSUPPORTED; }
+    BwdArgs a{g, d->scale, dist, ent, (const float*)q, (const float*)k, (const float*)v, nullptr,
+              (const float*)dy, stats, nullptr, dA, const_cast<float*>(D), nullptr, (float*)dk, (float*)dv};
+    dim3 grid((g.Np + 127) / 128, g.units);
+    CA_DISPATCH_CMAX(cmax, g.cpe, (bwd_key_generic<CM, CP><<<grid, 128, 0, st>>>(a)));
+    CA_CHECK_LAUNCH("backward dk/dv kernel");
+    return CA_OK;
+}
+
+int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void* v,
+                     const void* y, const void* dy, const float* stats,
+                     const float* nz, const float* dA,
+                     void* dq, void* dk, void* dv, void* workspace, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, false);
+    if (rc) return rc;
+    if (!workspace) { set_error("workspace of ca_attention_bwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
+    float* D = (float*)workspace;
+    if ((rc = ca_attention_bwd_pre(d, q, k, v, y, dy, stats, nz, dA, D, stream))) return rc;
+    if ((rc = ca_attention_bwd_dq(d, q, k, v, dy, stats, D, dA, dq, stream))) return rc;
+    return ca_attention_bwd_dkdv(d, q, k, v, dy, stats, D, dA, dk, dv, stream);
+}
+
+int ca_axpby(int64_t n, float alpha, const float* x, float beta, const float* y, float* out, void* stream) {
+    if (n < 0) { set_error("negative length"); return CA_ERR_BAD_DESC; }
+    if (n == 0) return CA_OK;
+    if (!x || !out || (beta != 0.f && !y)) { set_error("x/y/out is NULL"); return CA_ERR_NULL; }
+    axpby_kernel<<<elementwise_grid((n + 3) / 4), 256, 0, as_stream(stream)>>>(n, alpha, x, beta, beta != 0.f ? y : nullptr, out);
+    CA_CHECK_LAUNCH("axpby kernel");
+    return CA_OK;
+}
+
+static int check_bcast(const char* what, int v1, int v2, int o1, int o2) {
+    if ((v1 != 1 && v1 != o1) || (v2 != 1 && v2 != o2)) {
+        set_error("%s batch dims (%d,%d) do not broadcast to (%d,%d)", what, v1, v2, o1, o2);
+        return CA_ERR_BAD_DESC;
+    }
+    return CA_OK;
+}
+
+int ca_scale_batch(int64_t inner, int32_t o1, int32_t o2, const float* a, int32_t a1, int32_t a2,
+                   const float* c, int32_t c1, int32_t c2, float* out, void* stream) {
+    if (inner < 1 || o1 < 1 || o2 < 1 || o1 > 65535 || o2 > 65535) { set_error("bad extents"); return CA_ERR_BAD_DESC; }
+    if (!a || !c || !out) { set_error("a/c/out is NULL"); return CA_ERR_NULL; }
+    int rc;
+    if ((rc = check_bcast("values", a1, a2, o1, o2)) || (rc = check_bcast("scale", c1, c2, o1, o2))) return rc;
+    dim3 grid(elementwise_grid(inner), o1, o2);
+    scale_batch_kernel<<<grid, 256, 0, as_stream(stream)>>>(inner, o1, o2, a, a1, a2, c, c1, c2, out);
+    CA_CHECK_LAUNCH("scale kernel");
+    return CA_OK;
+}
+
+int ca_dot_batch(int64_t inner, int32_t o1, int32_t o2, const float* x, int32_t x1, int32_t x2,
+                 const float* y, int32_t y1, int32_t y2, float* out, void* stream) {
+    if (inner < 1 || o1 < 1 || o2 < 1 || o1 > 65535 || o2 > 65535) { set_error("bad extents"); return CA_ERR_BAD_DESC; }
+    if (!x || !out) { set_error("x/out is NULL"); return CA_ERR_NULL; }
+    int rc;
+    if ((rc = check_bcast("x", x1, x2, o1, o2))) return rc;
+    if (y && (rc = check_bcast("y", y1, y2, o1, o2))) return rc;
+    dim3 grid(o1, o2);
+    dot_batch_kernel<<<grid, 1024, 0, as_stream(stream)>>>(inner, o1, x, x1, x2, y, y1, y2, out);
+    CA_CHECK_LAUNCH("dot kernel");
+    return CA_OK;
+}
+
+int ca_sum_batch(int64_t inner, int32_t b1, int32_t b2, int32_t sum1, int32_t sum2,
+                 const float* in, float* out, void* stream) {
+    if (inner < 1 || b1 < 1 || b2 < 1) { set_error("bad extents"); return CA_ERR_BAD_DESC; }
+    if (!in || !out) { set_error("in/out is NULL"); return CA_ERR_NULL; }
+    const int64_t total = inner * (sum1 ? 1 : b1) * (sum2 ? 1 : b2);
+    sum_batch_kernel<<<elementwise_grid(total), 256, 0, as_stream(stream)>>>(inner, b1, b2, sum1, sum2, in, out);
+    CA_CHECK_LAUNCH("batch sum kernel");
+    return CA_OK;
+}
+
+int ca_sum_rows(const ca_desc* d, const float* nz, float* out, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, false);
+    if (rc) return rc;
+    if (!nz || !out) { set_error("nz/out is NULL"); return CA_ERR_NULL; }
+    const int64_t rows = (int64_t)g.Np * g.units;
+    sum_rows_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, as_stream(stream)>>>(rows, g.K, nz, out);
+    CA_CHECK_LAUNCH("row sum kernel");
+    return CA_OK;
+}
+
+int ca_sum_cols(const ca_desc* d, const float* nz, float* out, void* stream) {
+    Geo g;
+    int rc = make_geo(d, &g, false);
+    if (rc) return rc;
+    if (!nz || !out) { set_error("nz/out is NULL"); return CA_ERR_NULL; }
+    dim3 grid((g.Np + 127) / 128, g.units);
+    sum_cols_kernel<<<grid, 128, 0, as_stream(stream)>>>(g, nz, out);
+    CA_CHECK_LAUNCH("column sum kernel");
+    return CA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,269 @@
+"""Thin tensor-level wrappers over the C ABI: shape bookkeeping, output
+allocation (the caller owns every buffer, as CUDA.jl's pool does on the Julia
+side) and the ctypes calls.  No arithmetic happens here."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib, jl
+from ._lib import CA_C64, CA_F32, ca_desc, check, lib, ptr
+
+
+@dataclass(frozen=True)
+class Meta:
+    """What a windowed kernel needs to know about a (spatial..., c, units) tensor."""
+    spatial: tuple
+    channels: int
+    units: int
+    ws: int
+    cplx: bool
+
+    @property
+    def ndim(self):
+        return len(self.spatial)
+
+    @property
+    def H(self):
+        return self.spatial[0]
+
+    @property
+    def W(self):
+        return self.spatial[1] if len(self.spatial) == 2 else 1
+
+    @property
+    def Np(self):
+        return self.H * self.W
+
+    @property
+    def K(self):
+        return self.ws ** self.ndim
+
+    def desc(self, similarity=0, normalizer=0, scale=1.0, Wk=0, wk_off=0, units=None, W=None):
+        return ca_desc(self.H, self.W if W is None else W, self.ndim, self.channels,
+                       self.units if units is None else units, self.ws,
+                       CA_C64 if self.cplx else CA_F32, similarity, normalizer, Wk, wk_off, float(scale))
+
+
+def meta_of(x: torch.Tensor, ws: int) -> Meta:
+    if x.ndim not in (3, 4):
+        raise AssertionError(f"expected a (spatial..., channels, batch) array with 1 or 2 spatial dims, got {tuple(x.shape)}")
+    return Meta(tuple(x.shape[:-2]), x.shape[-2], x.shape[-1], int(ws), x.is_complex())
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("CirculantAttention is only CUDA compatible (no CPU path): got a tensor on " + str(t.device))
+
+
+def _dense_ok(t, cplx=None):
+    want = (torch.float32, torch.complex64)
+    if t.dtype not in want:
+        raise TypeError(f"only Float32 and ComplexF32 are supported, got {t.dtype}")
+    return jl.colmajor(t)
+
+
+def structure(spatial, ws, batch, device):
+    """rowPtr (Np+1, batch...) and colVal (Np*K, batch...) Int32, 1-based."""
+    spatial = tuple(spatial)
+    H, W = spatial[0], (spatial[1] if len(spatial) == 2 else 1)
+    Np, K = H * W, ws ** len(spatial)
+    nb = int(math.prod(batch)) if batch else 1
+    rowptr = jl.empty((Np + 1,) + tuple(batch), torch.int32, device)
+    colval = jl.empty((Np * K,) + tuple(batch), torch.int32, device)
+    with torch.cuda.device(rowptr.device):
+        check(lib.ca_structure(H, W, len(spatial), ws, nb, ptr(rowptr), ptr(colval), _stream()))
+    return rowptr, colval
+
+
+def similarity(kind, x, y, ws, scale=1.0):
+    require_cuda(x, y)
+    x, y = _dense_ok(x), _dense_ok(y)
+    m = meta_of(x, ws)
+    nz = jl.empty((m.Np * m.K, m.units), torch.float32, x.device)
+    d = m.desc(similarity=kind, scale=scale)
+    with torch.cuda.device(x.device):
+        check(lib.ca_similarity(d, ptr(x), ptr(y), ptr(nz), _stream()))
+    return nz
+
+
+def similarity_bwd(kind, x, y, ws, dS, scale=1.0):
+    x, y = _dense_ok(x), _dense_ok(y)
+    dS = jl.colmajor(dS)
+    m = meta_of(x, ws)
+    dx, dy = jl.empty(x.shape, x.dtype, x.device), jl.empty(y.shape, y.dtype, y.device)
+    d = m.desc(similarity=kind, scale=scale)
+    with torch.cuda.device(x.device):
+        check(lib.ca_similarity_bwd(d, ptr(x), ptr(y), ptr(dS), ptr(dx), ptr(dy), _stream()))
+    return dx, dy
+
+
+def _nz_meta(spatial, ws, units):
+    return Meta(tuple(spatial), 1, int(units), int(ws), False)
+
+
+def row_normalize(nz, spatial, ws, normalizer, out=None, want_stats=False):
+    require_cuda(nz)
+    nz = jl.colmajor(nz)
+    units = nz.numel() // nz.shape[0]
+    m = _nz_meta(spatial, ws, units)
+    out = jl.empty(nz.shape, torch.float32, nz.device) if out is None else out
+    stats = jl.empty((m.Np, units), torch.float32, nz.device) if want_stats else None
+    with torch.cuda.device(nz.device):
+        check(lib.ca_row_normalize(m.desc(normalizer=normalizer), ptr(nz), ptr(out), ptr(stats), _stream()))
+    return (out, stats) if want_stats else out
+
+
+def row_normalize_bwd(p, dp, spatial, ws, normalizer):
+    p, dp = jl.colmajor(p), jl.colmajor(dp)
+    units = p.numel() // p.shape[0]
+    m = _nz_meta(spatial, ws, units)
+    ds = jl.empty(p.shape, torch.float32, p.device)
+    with torch.cuda.device(p.device):
+        check(lib.ca_row_normalize_bwd(m.desc(normalizer=normalizer), ptr(p), ptr(dp), ptr(ds), _stream()))
+    return ds
+
+
+def apply(nz, v, ws, transpose=False, out=None):
+    """A (x) v or A^T (x) v.  nz: (Np*K, ua); v: (spatial..., c, uv); ua, uv broadcast."""
+    require_cuda(nz, v)
+    nz, v = jl.colmajor(nz), _dense_ok(v)
+    m = meta_of(v, ws)
+    ua = nz.numel() // nz.shape[0]
+    units = max(ua, m.units)
+    if ua not in (1, units) or m.units not in (1, units):
+        raise AssertionError(f"batch dims of A ({ua}) and of x ({m.units}) do not broadcast")
+    if nz.shape[0] != m.Np * m.K:
+        raise AssertionError(f"A has {nz.shape[0]} stored entries per batch, x needs {m.Np * m.K}")
+    if out is None:
+        out = jl.empty(tuple(v.shape[:-1]) + (units,), v.dtype, v.device)
+    d = m.desc(units=units)
+    with torch.cuda.device(v.device):
+        check(lib.ca_apply(d, ptr(nz), ptr(v), ptr(out), int(transpose), int(ua == 1 and units > 1),
+                           int(m.units == 1 and units > 1), _stream()))
+    return out
+
+
+def attention_fwd(kind, normalizer, q, k, v, ws, want_nz, scale=None, band=None):
+    """Fused forward on (spatial..., c, units) tensors.  Returns (y, nz | None, stats).
+    `band=(Wk, wk_off)` selects band mode: k, v then have Wk columns."""
+    require_cuda(q, k, v)
+    q, k, v = _dense_ok(q), _dense_ok(k), _dense_ok(v)
+    m = meta_of(q, ws)
+    scale = 1.0 / math.sqrt(m.channels) if scale is None else scale
+    Wk, wk_off = band if band else (0, 0)
+    d = m.desc(similarity=kind, normalizer=normalizer, scale=scale, Wk=Wk, wk_off=wk_off)
+    y = jl.empty(q.shape, q.dtype, q.device)
+    nz = jl.empty((m.Np * m.K, m.units), torch.float32, q.device) if want_nz else None
+    stats = jl.empty((m.Np, m.units), torch.float32, q.device)
+    nbytes = lib.ca_attention_fwd_workspace(d, int(want_nz))
+    wsb = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
+    with torch.cuda.device(q.device):
+        check(lib.ca_attention_fwd(d, ptr(q), ptr(k), ptr(v), ptr(y), ptr(nz), ptr(stats), ptr(wsb), _stream()))
+    return y, nz, stats
+
+
+def attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=None, dA=None, scale=None):
+    """Fused backward.  Returns (dq, dk, dv)."""
+    q, k, v, y, dy = (_dense_ok(t) for t in (q, k, v, y, dy))
+    m = meta_of(q, ws)
+    scale = 1.0 / math.sqrt(m.channels) if scale is None else scale
+    d = m.desc(similarity=kind, normalizer=normalizer, scale=scale)
+    dq, dk, dv = (jl.empty(q.shape, q.dtype, q.device) for _ in range(3))
+    if dA is not None:
+        dA = jl.colmajor(dA)
+    wsb = torch.empty(lib.ca_attention_bwd_workspace(d), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        check(lib.ca_attention_bwd(d, ptr(q), ptr(k), ptr(v), ptr(y), ptr(dy), ptr(stats), ptr(nz), ptr(dA),
+                                   ptr(dq), ptr(dk), ptr(dv), ptr(wsb), _stream()))
+    return dq, dk, dv
+
+
+# ------------------------------------------------------------------ algebra
+def axpby(alpha, x, beta=0.0, y=None):
+    require_cuda(x, y)
+    x = jl.colmajor(x)
+    y = jl.colmajor(y) if y is not None else None
+    out = jl.empty(x.shape, torch.float32, x.device)
+    with torch.cuda.device(x.device):
+        check(lib.ca_axpby(x.numel(), float(alpha), ptr(x), float(beta), ptr(y), ptr(out), _stream()))
+    return out
+
+
+def _b12(batch):
+    batch = tuple(batch)
+    if len(batch) > 2:
+        raise NotImplementedError("at most two batch dims (heads, batch) are supported")
+    return (batch + (1, 1))[:2]
+
+
+def scale_batch(c, nz):
+    """nz (inner, a...) times c (c...) with Julia-style extent-1 broadcasting."""
+    require_cuda(c, nz)
+    c, nz = jl.colmajor(c), jl.colmajor(nz)
+    a1, a2 = _b12(nz.shape[1:])
+    c1, c2 = _b12(c.shape)
+    o1, o2 = max(a1, c1), max(a2, c2)
+    nb = max(nz.ndim - 1, c.ndim)
+    out = jl.empty((nz.shape[0],) + (o1, o2)[:nb], torch.float32, nz.device)
+    with torch.cuda.device(nz.device):
+        check(lib.ca_scale_batch(nz.shape[0], o1, o2, ptr(nz), a1, a2, ptr(c), c1, c2, ptr(out), _stream()))
+    return out
+
+
+def dot_batch(x, y=None):
+    """per-slice sum_n x*y (y None: sum of x); x, y: (inner, b...) broadcasting -> (b...)"""
+    require_cuda(x, y)
+    x = jl.colmajor(x)
+    x1, x2 = _b12(x.shape[1:])
+    if y is not None:
+        y = jl.colmajor(y)
+        y1, y2 = _b12(y.shape[1:])
+    else:
+        y1 = y2 = 1
+    o1, o2 = max(x1, y1), max(x2, y2)
+    nb = max(x.ndim, y.ndim if y is not None else 0) - 1
+    out = jl.empty((o1, o2)[:nb] if nb else (1,), torch.float32, x.device)
+    with torch.cuda.device(x.device):
+        check(lib.ca_dot_batch(x.shape[0], o1, o2, ptr(x), x1, x2, ptr(y), y1, y2, ptr(out), _stream()))
+    return out
+
+
+def sum_batch(nz, sum1, sum2):
+    require_cuda(nz)
+    nz = jl.colmajor(nz)
+    b1, b2 = _b12(nz.shape[1:])
+    o = (1 if sum1 else b1, 1 if sum2 else b2)[:nz.ndim - 1]
+    out = jl.empty((nz.shape[0],) + o, torch.float32, nz.device)
+    with torch.cuda.device(nz.device):
+        check(lib.ca_sum_batch(nz.shape[0], b1, b2, int(sum1), int(sum2), ptr(nz), ptr(out), _stream()))
+    return out
+
+
+def sum_rows(nz, spatial, ws):
+    require_cuda(nz)
+    nz = jl.colmajor(nz)
+    units = nz.numel() // nz.shape[0]
+    m = _nz_meta(spatial, ws, units)
+    out = jl.empty((m.Np, 1) + tuple(nz.shape[1:]), torch.float32, nz.device)
+    with torch.cuda.device(nz.device):
+        check(lib.ca_sum_rows(m.desc(), ptr(nz), ptr(out), _stream()))
+    return out
+
+
+def sum_cols(nz, spatial, ws):
+    require_cuda(nz)
+    nz = jl.colmajor(nz)
+    units = nz.numel() // nz.shape[0]
+    m = _nz_meta(spatial, ws, units)
+    out = jl.empty((1, m.Np) + tuple(nz.shape[1:]), torch.float32, nz.device)
+    with torch.cuda.device(nz.device):
+        check(lib.ca_sum_cols(m.desc(), ptr(nz), ptr(out), _stream()))
+    return out

@@ -1,0 +1,189 @@
+/*
+ * circatt_b200.h -- C ABI of the B200 (sm_100a) circulant-attention library.
+ *
+ * Every entry point replaces a piece of device work that the Julia package
+ * CirculantAttention.jl (v1.0.1) performs through CUDA.jl codegen, cuSPARSE or
+ * NNlib/cuDNN.  The citation on each declaration is the reference file:line
+ * whose device work the entry point stands in for.
+ *
+ * Conventions
+ *  - All pointers are DEVICE pointers into memory owned by the caller.  The
+ *    library never allocates or frees caller-visible memory, never
+ *    synchronises the device, and launches only on the stream it is given
+ *    (`stream` is a cudaStream_t passed as void*; NULL = legacy default).
+ *  - Dense tensors use the Julia column-major layout of the reference:
+ *    element (h, w, ch, u) of a (H, W, c, units) array sits at
+ *    h + H*(w + W*(ch + c*u)); 1-D signals have W = 1.  `units` is the merged
+ *    head*batch dimension after the reference's `splitheads`
+ *    (src/attention.jl:44): head index fastest.  CA_C64 tensors hold
+ *    interleaved (re, im) float pairs.
+ *  - Sparse values (`nz`) are float32 (also for complex inputs,
+ *    src/array.jl:12-14, src/similarity.jl:139), laid out as the reference's
+ *    nzVal: K = ws^ndim consecutive entries per row (query pixel), rows
+ *    consecutive, units outermost: nz[k + K*(row + Np*u)].  Inside a row the
+ *    entries are in ascending column order -- the order `cartesian_circulant`
+ *    (src/circulant.jl:4-44) defines.
+ *  - Every function returns CA_OK (0) or a negative ca_status; the text of the
+ *    last failure on the calling thread is returned by ca_last_error().
+ */
+#ifndef CIRCATT_B200_H
+#define CIRCATT_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ca_status {
+    CA_OK = 0,
+    CA_ERR_BAD_DESC = -1,      /* inconsistent descriptor (even window, extent < window, ...) */
+    CA_ERR_UNSUPPORTED = -2,   /* legal but not implemented combination */
+    CA_ERR_NULL = -3,          /* a required pointer is NULL */
+    CA_ERR_CUDA = -4,          /* a CUDA runtime call or launch failed */
+    CA_ERR_TOO_LARGE = -5      /* a size exceeds a documented limit */
+} ca_status;
+
+enum { CA_F32 = 0, CA_C64 = 1 };            /* element type of dense tensors */
+enum { CA_DOT = 0, CA_DISTANCE = 1 };       /* src/similarity.jl:15,29 */
+enum { CA_SOFTMAX = 0, CA_ENTMAX15 = 1 };   /* row normaliser; entmax has no reference counterpart */
+
+/* Problem descriptor shared by the windowed kernels. */
+typedef struct ca_desc {
+    int32_t H;          /* fast spatial extent (Julia dim 1) */
+    int32_t W;          /* slow spatial extent (Julia dim 2); 1 when ndim == 1 */
+    int32_t ndim;       /* number of spatial dims: 1 or 2 */
+    int32_t channels;   /* channels per unit (C / nheads), counted in elements of `dtype` */
+    int32_t units;      /* independent head*batch units */
+    int32_t ws;         /* odd window length; every spatial extent must be >= ws */
+    int32_t dtype;      /* CA_F32 or CA_C64 */
+    int32_t similarity; /* CA_DOT or CA_DISTANCE */
+    int32_t normalizer; /* CA_SOFTMAX or CA_ENTMAX15 */
+    int32_t Wk;         /* band mode: columns of the key-side tensors (0 or W = circular wrap) */
+    int32_t wk_off;     /* band mode: key-side column that holds query column 0 */
+    float   scale;      /* factor applied to the raw similarity (1/sqrt(c) inside attention) */
+} ca_desc;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int ca_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* ca_last_error(void);
+
+/* ---------------------------------------------------------------- structure
+ * CSR structure of the circulant / BCCB pattern, 1-based Int32, replicated
+ * `nbatch` times as the reference does with `repeat` (src/array.jl:9):
+ *   rowptr[r + (Np+1)*b] = 1 + K*r           (src/circulant.jl:71-73, 93-95)
+ *   colval[n + Np*K*b]   = column of entry n  (src/circulant.jl:46-62 -> :4-44)
+ */
+int ca_structure(int32_t H, int32_t W, int32_t ndim, int32_t ws, int64_t nbatch,
+                 int32_t* rowptr, int32_t* colval, void* stream);
+
+/* ---------------------------------------------------------------- similarity
+ * nz = scale * simfun(x[row pixel], y[column pixel]) for every stored entry.
+ * Replaces circulant_similarity_kernel! (src/similarity.jl:55-103) and its
+ * launcher (src/similarity.jl:36-53). */
+int ca_similarity(const ca_desc* d, const void* x, const void* y, float* nz, void* stream);
+
+/* Pullback of ca_similarity (src/rrules.jl:1-32):
+ *   Dot:      dx = scale * dS Y               dy = scale * dS^T X
+ *   Distance: dx = scale * (dS Y - rowsum(dS) X)   dy = scale * (dS^T X - colsum(dS) Y) */
+int ca_similarity_bwd(const ca_desc* d, const void* x, const void* y, const float* dS,
+                      void* dx, void* dy, void* stream);
+
+/* ---------------------------------------------------------------- row normaliser
+ * Row softmax (src/similarity.jl:105-126; NNlib.softmax! over each row's K
+ * entries) or 1.5-entmax.  `p` may alias `s`.  `stats` (nullable, Np*units
+ * floats) receives the row log-sum-exp (softmax) or threshold tau (entmax). */
+int ca_row_normalize(const ca_desc* d, const float* s, float* p, float* stats, void* stream);
+
+/* Pullback (src/rrules.jl:42-56 -> NNlib.∇softmax_data): ds = p*(dp - sum_row p*dp);
+ * entmax: ds = g*(dp - sum g*dp / sum g), g = sqrt(p).  `ds` may alias `dp`. */
+int ca_row_normalize_bwd(const ca_desc* d, const float* p, const float* dp, float* ds, void* stream);
+
+/* ---------------------------------------------------------------- apply
+ * out = A (x) v or A^T (x) v: the CUSPARSE.bmm! call sites of
+ * src/batchedmul.jl:82-110 as used by circulant_attention!/
+ * circulant_transposed_attention! (src/attention.jl:53-80).  Real A with a
+ * CA_C64 v multiplies both parts (replaces the promotion copy of
+ * src/batchedmul.jl:43-80).  a_bcast / v_bcast != 0 mean that A / v hold one
+ * unit that is shared by all d->units outputs. */
+int ca_apply(const ca_desc* d, const float* nz, const void* v, void* out,
+             int32_t transpose, int32_t a_bcast, int32_t v_bcast, void* stream);
+
+/* ---------------------------------------------------------------- fused attention
+ * y = rownormalize(scale * simfun(q, k)) (x) v  in one pass
+ * (circulant_attention, src/attention.jl:19-25; per-head via the merged unit
+ * dimension, src/attention.jl:38-44).  `nz` (nullable) receives A's values in
+ * CSR order; `stats` (nullable, Np*units floats) the per-row log-sum-exp /
+ * entmax threshold needed by ca_attention_bwd.  `workspace` must hold
+ * ca_attention_fwd_workspace() bytes (may be NULL when that is 0). */
+size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz);
+int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void* v,
+                     void* y, float* nz, float* stats, void* workspace, void* stream);
+
+/* Gradient of the above (the composition of the reference's rrules for
+ * similarity, softmax and apply: src/rrules.jl:1-72).  `dA` (nullable) is the
+ * cotangent arriving on the returned A (CSR order); when it is given, `nz`
+ * (the A saved by the forward) must be given as well.  `y` is the forward
+ * output.  dq, dk, dv are overwritten.  Deterministic: no atomics. */
+size_t ca_attention_bwd_workspace(const ca_desc* d);
+int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void* v,
+                     const void* y, const void* dy, const float* stats,
+                     const float* nz, const float* dA,
+                     void* dq, void* dk, void* dv, void* workspace, void* stream);
+
+/* The three stages of ca_attention_bwd, exposed separately for the band-split
+ * (multi-GPU) path, where D and the query-side halos are exchanged between
+ * stages.  D holds one float per (query-side pixel, unit):
+ *   softmax: D = dy . y + sum_k A_k dA_k      entmax: D = sum g dP / sum g.
+ * In band mode (d->Wk = W + 2p) ca_attention_bwd_dq reads k, v with Wk columns,
+ * and ca_attention_bwd_dkdv reads q, dy, stats, D with Wk columns. */
+int ca_attention_bwd_pre(const ca_desc* d, const void* q, const void* k, const void* v,
+                         const void* y, const void* dy, const float* stats,
+                         const float* nz, const float* dA, float* D, void* stream);
+int ca_attention_bwd_dq(const ca_desc* d, const void* q, const void* k, const void* v,
+                        const void* dy, const float* stats, const float* D, const float* dA,
+                        void* dq, void* stream);
+int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const void* v,
+                          const void* dy, const float* stats, const float* D, const float* dA,
+                          void* dk, void* dv, void* stream);
+
+/* ---------------------------------------------------------------- algebra on values
+ * out[n,i,j] = alpha*x[n,i,j] + beta*y[n,i,j] over a flat length (X+Y, X-Y, c*X:
+ * src/array.jl:66-81).  y may be NULL when beta == 0. */
+int ca_axpby(int64_t n, float alpha, const float* x, float beta, const float* y,
+             float* out, void* stream);
+
+/* scale (src/array.jl:179-186): values of shape (inner, a1, a2) times c of shape
+ * (c1, c2), each batch extent either 1 or the output's (o1, o2). */
+int ca_scale_batch(int64_t inner, int32_t o1, int32_t o2,
+                   const float* a, int32_t a1, int32_t a2,
+                   const float* c, int32_t c1, int32_t c2,
+                   float* out, void* stream);
+
+/* out[i,j] = sum_n x[n,i,j]*y[n,i,j] (y NULL: sum of x) per batch slice, with the
+ * same broadcasting rule.  Covers LinearAlgebra.dot (src/array.jl:83-85),
+ * sum(A) (src/array.jl:162), sum(dims=(1,2)) (src/array.jl:151-154) and the
+ * reduction inside the scale pullback (src/rrules.jl:105-108). */
+int ca_dot_batch(int64_t inner, int32_t o1, int32_t o2,
+                 const float* x, int32_t x1, int32_t x2,
+                 const float* y, int32_t y1, int32_t y2,
+                 float* out, void* stream);
+
+/* Sum of values over batch dims (src/array.jl:132-149): in (inner, b1, b2) ->
+ * out (inner, sum1 ? 1 : b1, sum2 ? 1 : b2). */
+int ca_sum_batch(int64_t inner, int32_t b1, int32_t b2, int32_t sum1, int32_t sum2,
+                 const float* in, float* out, void* stream);
+
+/* Row sums (dims=2, src/array.jl:126-130) and column sums (dims=1,
+ * src/array.jl:119-124; the reference does a transposed SpMM against ones).
+ * out has Np*units floats. */
+int ca_sum_rows(const ca_desc* d, const float* nz, float* out, void* stream);
+int ca_sum_cols(const ca_desc* d, const float* nz, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CIRCATT_B200_H */

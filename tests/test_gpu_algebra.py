@@ -1,0 +1,119 @@
+"""Circulant algebra, sums, cat and the scale rrule against the oracle
+(src/array.jl:66-189, src/rrules.jl:97-114, README.md:121-148)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import circatt_oracle as orc
+from tests.helpers import TOL, randn, rel_err
+
+pytestmark = pytest.mark.gpu
+
+SPATIAL, WS = (9, 8), 5
+K, NP = 25, 72
+
+
+def make(ca, rng, batch):
+    A = ca.Circulant(WS, SPATIAL + batch)
+    nzn = np.asfortranarray(rng.standard_normal(tuple(A.nzVal.shape)).astype(np.float32))
+    A.data.nzVal = ca.jl.from_numpy(nzn)
+    return A, nzn.astype(np.float64).reshape((K, NP) + batch, order="F")
+
+
+def test_add_sub_scalar_neg_dot_eq(ca):
+    rng = np.random.default_rng(0)
+    A, a = make(ca, rng, (2, 3))
+    B, b = make(ca, rng, (2, 3))
+    assert np.array_equal(ca.jl.to_numpy((A + B).nzVal).reshape(a.shape, order="F"), (a + b).astype(np.float32))
+    assert np.array_equal(ca.jl.to_numpy((A - B).nzVal).reshape(a.shape, order="F"), (a - b).astype(np.float32))
+    assert np.array_equal(ca.jl.to_numpy((2.5 * A).nzVal).reshape(a.shape, order="F"), (2.5 * a).astype(np.float32))
+    assert np.array_equal(ca.jl.to_numpy((-A).nzVal).reshape(a.shape, order="F"), (-a).astype(np.float32))
+    assert abs(float(ca.dot(A, B)) - (a * b).sum()) < 1e-4 * np.abs(a * b).sum()
+    assert A == A.copy() and not (A == B)
+    assert A.data.colVal.data_ptr() == B.data.colVal.data_ptr()      # structure is shared, not copied
+
+
+@pytest.mark.parametrize("abatch,cshape", [((2, 3), (1, 1, 2, 3)), ((1, 3), (1, 1, 2, 3)), ((2, 3), (1, 1, 1, 3)),
+                                           ((2, 1), (1, 1, 2, 4)), ((1, 2), (1, 1, 2, 2)), ((2, 2), (1, 1, 1, 1))])
+def test_scale_and_pullback(ca, abatch, cshape):
+    """test/rrule.jl:22 and README.md:130-134 (`m*B`)."""
+    rng = np.random.default_rng(1)
+    A, a = make(ca, rng, abatch)
+    A.data.nzVal.requires_grad_(True)
+    cn = np.asfortranarray(rng.standard_normal(cshape).astype(np.float32))
+    c = ca.jl.from_numpy(cn).requires_grad_(True)
+    Bm = c * A
+    want = orc.scale(cn.astype(np.float64), a)
+    assert Bm.shape == (NP, NP) + want.shape[2:]
+    assert rel_err(ca.jl.to_numpy(Bm.nzVal), want) < 1e-6
+    dBn = np.asfortranarray(rng.standard_normal(tuple(Bm.nzVal.shape)).astype(np.float32))
+    (Bm.nzVal * ca.jl.from_numpy(dBn)).sum().backward()
+    dco, dAo = orc.scale_pullback(cn.astype(np.float64), a, dBn.astype(np.float64).reshape(want.shape, order="F"))
+    assert rel_err(ca.jl.to_numpy(c.grad), dco) < TOL
+    assert rel_err(ca.jl.to_numpy(A.nzVal.grad), dAo) < TOL
+
+
+def test_scale_rejects_non_batch_dims(ca):
+    rng = np.random.default_rng(2)
+    A, _ = make(ca, rng, (1, 2))
+    with pytest.raises(AssertionError, match="Scaling of non-batchdims"):
+        ca.scale(ca.jl.ones((1, 2, 1, 2)), A)
+
+
+def test_sums(ca):
+    """README.md:137-143."""
+    rng = np.random.default_rng(3)
+    A, a = make(ca, rng, (2, 3))
+    assert rel_err(ca.jl.to_numpy(ca.sum(A, dims=2)), orc.sum_dims2(a).reshape((NP, 1, 2, 3))) < TOL
+    assert rel_err(ca.jl.to_numpy(ca.sum(A, dims=1)), orc.sum_dims1(a, SPATIAL, WS).reshape((1, NP, 2, 3))) < TOL
+    s3 = ca.sum(A, dims=3)
+    assert isinstance(s3, ca.Circulant) and s3.shape == (NP, NP, 1, 3)
+    assert rel_err(ca.jl.to_numpy(s3.nzVal), orc.sum_batch(a, (3,))) < TOL
+    s4 = ca.sum(A, dims=4)
+    assert s4.shape == (NP, NP, 2, 1)
+    assert rel_err(ca.jl.to_numpy(s4.nzVal), orc.sum_batch(a, (4,))) < TOL
+    s34 = ca.sum(A, dims=(3, 4))
+    assert s34.shape == (NP, NP, 1, 1)
+    assert rel_err(ca.jl.to_numpy(s34.nzVal), orc.sum_batch(a, (3, 4))) < TOL
+    s12 = ca.sum(A, dims=(1, 2))
+    assert tuple(s12.shape) == (1, 1, 2, 3)
+    assert rel_err(ca.jl.to_numpy(s12), a.sum(axis=(0, 1)).reshape((1, 1, 2, 3))) < TOL
+    assert abs(float(ca.sum(A)) - a.sum()) < 1e-3
+    with pytest.raises(RuntimeError, match="not implemented"):
+        ca.sum(A, dims=(1, 3))
+
+
+def test_cat_repeat_reshape(ca):
+    """README.md:145-148."""
+    rng = np.random.default_rng(4)
+    A, a = make(ca, rng, (2, 3))
+    B, b = make(ca, rng, (1, 3))
+    D = ca.cat(A, B, dims=3)
+    assert D.shape == (NP, NP, 3, 3)
+    assert np.array_equal(ca.jl.to_numpy(D.nzVal).reshape((K, NP, 3, 3), order="F"),
+                          np.concatenate([a, b], axis=2).astype(np.float32))
+    R = B.repeat(1, 1, 2, 1)
+    assert R.shape == (NP, NP, 2, 3)
+    assert np.array_equal(ca.jl.to_numpy(R.nzVal).reshape((K, NP, 2, 3), order="F"),
+                          np.repeat(b, 2, axis=2).astype(np.float32))
+    F = A.reshape(NP, NP, -1)
+    assert F.shape == (NP, NP, 6)
+    assert np.array_equal(ca.jl.to_numpy(F.nzVal).reshape((K, NP, 6), order="F"),
+                          a.reshape((K, NP, 6), order="F").astype(np.float32))
+
+
+def test_grad_smoke_network(ca):
+    """test/grad.jl:17-21,34-38: C = α*A + (1-α)*B, z = C ⨷ v, gradients for every input."""
+    rng = np.random.default_rng(5)
+    shape, ws, nheads = (10, 10, 8, 2), 3, 2
+    for sim in (ca.DotSimilarity(), ca.DistanceSimilarity()):
+        xx, k, q, v = (ca.jl.from_numpy(randn(rng, shape)).requires_grad_(True) for _ in range(4))
+        alpha = (0.8 * ca.jl.ones((1, 1, nheads, 1))).requires_grad_(True)
+        A = ca.circulant_mh_adjacency(sim, k, q, ws, nheads)
+        B = ca.circulant_mh_adjacency(sim, xx, xx, ws, nheads)
+        Cm = alpha * A + (1.0 - alpha) * B
+        z = ca.Otimes(Cm, v)
+        assert tuple(z.shape) == shape
+        (z * z).sum().backward()
+        for t in (xx, k, q, v, alpha):
+            assert t.grad is not None and torch.isfinite(t.grad).all() and t.grad.abs().sum() > 0

@@ -1,0 +1,257 @@
+"""Parity of the CUDA library (through the C ABI) with the CPU oracle on the
+same seeded inputs.  Bar: bit-exact CSR structure; y, A and gradients within
+1e-5 relative (to the tensor's largest magnitude) for Float32 / ComplexF32."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import circatt_oracle as orc
+from tests.helpers import KIND, TOL, randn, rel_err, up
+
+pytestmark = pytest.mark.gpu
+
+
+def sim_of(ca, name):
+    return ca.DotSimilarity() if name == "dot" else ca.DistanceSimilarity()
+
+
+# ------------------------------------------------------------------ structure (bit exact)
+@pytest.mark.parametrize("spatial,ws,batch", [
+    ((8,), 5, (1, 2)), ((8, 8), 5, (1, 2)), ((5, 5), 5, (2, 1)), ((7, 9), 7, (1, 1)), ((12, 6), 5, (3, 2)),
+    ((32, 32), 7, (1, 1)), ((31,), 9, (1, 3)), ((10, 10), 3, (2, 2)), ((128, 96), 15, (1, 1)),
+])
+def test_structure_bit_exact(ca, spatial, ws, batch):
+    rowptr, colval = ca.ops.structure(spatial, ws, batch, "cuda")
+    rp, cv = orc.structure(spatial, ws)
+    got_rp, got_cv = ca.jl.to_numpy(rowptr), ca.jl.to_numpy(colval)
+    assert got_rp.dtype == np.int32 and got_cv.dtype == np.int32
+    assert got_rp.shape == (len(rp),) + batch and got_cv.shape == (len(cv),) + batch
+    for idx in np.ndindex(*batch):
+        assert np.array_equal(got_rp[(slice(None),) + idx], rp)
+        assert np.array_equal(got_cv[(slice(None),) + idx], cv)
+
+
+def test_structure_matches_literal_reference_index_function(ca):
+    _, colval = ca.ops.structure((9, 7), 5, (1, 1), "cuda")
+    assert np.array_equal(ca.jl.to_numpy(colval)[:, 0, 0], orc.structure_literal((9, 7), 5))
+
+
+# ------------------------------------------------------------------ fused attention
+CASES = [
+    # (shape (spatial..., C, B), ws, nheads, cplx)
+    ((32, 32, 16, 1), 7, 1, False),      # BASELINE config 1
+    ((8, 8, 4, 2), 5, 1, False),         # reference test/rrule.jl shapes
+    ((8, 4, 2), 5, 1, False),
+    ((8, 8, 4, 2), 5, 1, True),
+    ((8, 4, 2), 5, 1, True),
+    ((10, 10, 8, 2), 3, 2, False),       # reference test/grad.jl shapes
+    ((10, 8, 2), 3, 2, True),
+    ((7, 7, 3, 1), 7, 1, False),         # extent == window: every row wraps on both sides
+    ((8, 7, 5, 2), 7, 1, False),         # extent == window + 1
+    ((13, 11, 6, 3), 5, 3, False),       # prime extents, odd channels per head
+    ((37, 29, 32, 2), 9, 2, False),      # 16 channels per head, ragged tiles
+    ((64, 48, 64, 1), 15, 4, False),     # quarter-size BASELINE config 2
+    ((40, 6, 2), 13, 2, True),
+    ((300, 16, 2), 31, 2, False),        # long 1-D window
+    ((20, 20, 33, 1), 5, 1, False),      # 33 channels: 64-wide register path
+    ((24, 20, 20, 2), 7, 1, True),       # 40 real channels
+]
+
+
+@pytest.mark.parametrize("simname", ["dot", "distance"])
+@pytest.mark.parametrize("shape,ws,nheads,cplx", CASES)
+def test_attention_forward_backward(ca, shape, ws, nheads, cplx, simname):
+    rng = np.random.default_rng(0)
+    qn, kn, vn, rn = (randn(rng, shape, cplx) for _ in range(4))
+    q, k, v = (ca.jl.from_numpy(t).requires_grad_(True) for t in (qn, kn, vn))
+    y, A = ca.circulant_mh_attention(sim_of(ca, simname), q, k, v, ws, nheads)
+    B = shape[-1]
+    Np = int(np.prod(shape[:-2]))
+    assert tuple(y.shape) == shape and A.shape == (Np, Np, nheads, B)
+    r = ca.jl.from_numpy(rn)
+    loss = (y * r.conj()).real.sum() if cplx else (y * r).sum()
+    loss.backward()
+
+    yo, nzo = orc.mh_attention(KIND[simname], up(qn), up(kn), up(vn), ws, nheads)
+    dqo, dko, dvo = orc.mh_attention_pullback(KIND[simname], up(qn), up(kn), up(vn), ws, nheads, up(rn))
+    assert rel_err(ca.jl.to_numpy(y), yo) < TOL
+    assert rel_err(ca.jl.to_numpy(A.nzVal), nzo) < TOL
+    assert rel_err(ca.jl.to_numpy(q.grad), dqo) < TOL
+    assert rel_err(ca.jl.to_numpy(k.grad), dko) < TOL
+    assert rel_err(ca.jl.to_numpy(v.grad), dvo) < TOL
+
+
+@pytest.mark.parametrize("simname", ["dot", "distance"])
+def test_flash_mode_equals_materialised(ca, simname):
+    """return_A=False never writes A; y and gradients are the same bits."""
+    rng = np.random.default_rng(1)
+    shape = (24, 20, 32, 2)
+    qn, kn, vn, rn = (randn(rng, shape) for _ in range(4))
+    outs = []
+    for want in (True, False):
+        q, k, v = (ca.jl.from_numpy(t).requires_grad_(True) for t in (qn, kn, vn))
+        y, A = ca.circulant_mh_attention(sim_of(ca, simname), q, k, v, 7, 2, return_A=want)
+        assert (A is None) == (not want)
+        (y * ca.jl.from_numpy(rn)).sum().backward()
+        outs.append([ca.jl.to_numpy(t) for t in (y, q.grad, k.grad, v.grad)])
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+
+
+def test_cotangent_on_returned_A(ca):
+    """Loss uses both y and A (e.g. sparsity penalties): dA flows into the fused backward."""
+    rng = np.random.default_rng(2)
+    shape, ws, nheads = (12, 10, 8, 2), 5, 2
+    qn, kn, vn, rn = (randn(rng, shape) for _ in range(4))
+    q, k, v = (ca.jl.from_numpy(t).requires_grad_(True) for t in (qn, kn, vn))
+    y, A = ca.circulant_mh_attention(ca.DistanceSimilarity(), q, k, v, ws, nheads)
+    dAn = np.asfortranarray(rng.standard_normal(tuple(A.nzVal.shape)).astype(np.float32))
+    ((y * ca.jl.from_numpy(rn)).sum() + (A.nzVal * ca.jl.from_numpy(dAn)).sum()).backward()
+    K = ws * ws
+    dA64 = dAn.astype(np.float64).reshape((K, 120, nheads * 2), order="F")
+    dqo, dko, dvo = orc.mh_attention_pullback(orc.DISTANCE, up(qn), up(kn), up(vn), ws, nheads, up(rn), dA64)
+    assert rel_err(ca.jl.to_numpy(q.grad), dqo) < TOL
+    assert rel_err(ca.jl.to_numpy(k.grad), dko) < TOL
+    assert rel_err(ca.jl.to_numpy(v.grad), dvo) < TOL
+
+
+def test_large_scores_running_max(ca):
+    """Inputs scaled x30: scores in the hundreds; exercises the online-softmax rescale."""
+    rng = np.random.default_rng(3)
+    shape = (16, 16, 16, 1)
+    qn, kn, vn = (randn(rng, shape, scale=30.0) for _ in range(3))
+    q, k, v = (ca.jl.from_numpy(t) for t in (qn, kn, vn))
+    y, A = ca.circulant_attention(q, k, v, 7)
+    yo, nzo = orc.attention(orc.DOT, up(qn), up(kn), up(vn), 7)
+    assert np.isfinite(ca.jl.to_numpy(y)).all()
+    # scores ~ 1e3, so one float32 ulp of a score is ~1e-4 relative in exp(): looser bar, stated here
+    assert rel_err(ca.jl.to_numpy(y), yo) < 2e-3
+    assert rel_err(ca.jl.to_numpy(A.nzVal), nzo) < 2e-3
+
+
+def test_deterministic_gradients(ca):
+    rng = np.random.default_rng(4)
+    shape = (40, 33, 32, 2)
+    qn, kn, vn, rn = (randn(rng, shape) for _ in range(4))
+    runs = []
+    for _ in range(2):
+        q, k, v = (ca.jl.from_numpy(t).requires_grad_(True) for t in (qn, kn, vn))
+        y, _ = ca.circulant_mh_attention(ca.DotSimilarity(), q, k, v, 9, 2, return_A=False)
+        (y * ca.jl.from_numpy(rn)).sum().backward()
+        runs.append([ca.jl.to_numpy(t) for t in (y, q.grad, k.grad, v.grad)])
+    for a, b in zip(*runs):
+        assert np.array_equal(a, b)
+
+
+# ------------------------------------------------------------------ entmax (no reference counterpart)
+@pytest.mark.parametrize("want_A", [True, False])
+@pytest.mark.parametrize("shape,ws,nheads,simname", [((64, 16, 2), 15, 2, "distance"), ((12, 11, 8, 1), 5, 2, "dot")])
+def test_entmax_attention(ca, shape, ws, nheads, simname, want_A):
+    rng = np.random.default_rng(5)
+    qn, kn, vn, rn = (randn(rng, shape, scale=1.5) for _ in range(4))
+    q, k, v = (ca.jl.from_numpy(t).requires_grad_(True) for t in (qn, kn, vn))
+    y, A = ca.circulant_mh_attention(sim_of(ca, simname), q, k, v, ws, nheads, normalizer=ca.ENTMAX15, return_A=want_A)
+    (y * ca.jl.from_numpy(rn)).sum().backward()
+    yo, nzo = orc.mh_attention(KIND[simname], up(qn), up(kn), up(vn), ws, nheads, orc.ENTMAX15)
+    dqo, dko, dvo = orc.mh_attention_pullback(KIND[simname], up(qn), up(kn), up(vn), ws, nheads, up(rn),
+                                              norm=orc.ENTMAX15)
+    assert (nzo == 0).any()
+    assert rel_err(ca.jl.to_numpy(y), yo) < TOL
+    if want_A:
+        assert rel_err(ca.jl.to_numpy(A.nzVal), nzo) < TOL
+    assert rel_err(ca.jl.to_numpy(q.grad), dqo) < 2 * TOL
+    assert rel_err(ca.jl.to_numpy(k.grad), dko) < 2 * TOL
+    assert rel_err(ca.jl.to_numpy(v.grad), dvo) < TOL
+
+
+# ------------------------------------------------------------------ the unfused pieces and their rrules
+@pytest.mark.parametrize("cplx", [False, True])
+@pytest.mark.parametrize("simname", ["dot", "distance"])
+@pytest.mark.parametrize("spatial", [(8,), (8, 8), (11, 7)])
+def test_similarity_and_pullback(ca, spatial, simname, cplx):
+    """test/rrule.jl:18-19 shapes (8 / 8x8, 4 channels, batch 2, ws 5)."""
+    rng = np.random.default_rng(6)
+    shape, ws = spatial + (4, 2), 5
+    xn, yn = randn(rng, shape, cplx), randn(rng, shape, cplx)
+    x, y = (ca.jl.from_numpy(t).requires_grad_(True) for t in (xn, yn))
+    S = ca.circulant_similarity(sim_of(ca, simname), x, y, ws)
+    Np = int(np.prod(spatial))
+    assert S.shape == (Np, Np, 1, 2)
+    So = orc.similarity(KIND[simname], up(xn), up(yn), ws)
+    assert rel_err(ca.jl.to_numpy(S.nzVal), So) < TOL
+    dSn = rng.standard_normal(So.shape).astype(np.float32)
+    (S.nzVal * ca.jl.from_numpy(np.asfortranarray(dSn.reshape(tuple(S.nzVal.shape), order="F")))).sum().backward()
+    dxo, dyo = orc.similarity_pullback(KIND[simname], up(xn), up(yn), ws, dSn.astype(np.float64))
+    assert rel_err(ca.jl.to_numpy(x.grad), dxo) < TOL
+    assert rel_err(ca.jl.to_numpy(y.grad), dyo) < TOL
+
+
+@pytest.mark.parametrize("norm", ["softmax", "entmax"])
+def test_row_normalize_and_pullback(ca, norm):
+    """test/rrule.jl:21."""
+    rng = np.random.default_rng(7)
+    spatial, ws = (9, 8), 5
+    A = ca.Circulant(ws, spatial + (2, 3))
+    nzn = np.asfortranarray((2.0 * rng.standard_normal(tuple(A.nzVal.shape))).astype(np.float32))
+    A.data.nzVal = ca.jl.from_numpy(nzn).requires_grad_(True)
+    nrm = ca.SOFTMAX if norm == "softmax" else ca.ENTMAX15
+    P = ca.softmax(A, normalizer=nrm)
+    onorm = orc.SOFTMAX if norm == "softmax" else orc.ENTMAX15
+    nz64 = nzn.astype(np.float64).reshape((25, 72, 2, 3), order="F")
+    Po = orc.row_normalize(onorm, nz64)
+    assert rel_err(ca.jl.to_numpy(P.nzVal), Po) < TOL
+    dPn = np.asfortranarray(rng.standard_normal(nzn.shape).astype(np.float32))
+    (P.nzVal * ca.jl.from_numpy(dPn)).sum().backward()
+    dSo = orc.row_normalize_pullback(onorm, Po, dPn.astype(np.float64).reshape(Po.shape, order="F"))
+    assert rel_err(ca.jl.to_numpy(A.nzVal.grad), dSo) < TOL
+    # in-place form
+    B = ca.Circulant._from_nz(ca.jl.from_numpy(nzn), ws, spatial)
+    ca.softmax_(B, normalizer=nrm)
+    assert rel_err(ca.jl.to_numpy(B.nzVal), Po) < TOL
+
+
+@pytest.mark.parametrize("cplx", [False, True])
+@pytest.mark.parametrize("transpose", [False, True])
+@pytest.mark.parametrize("spatial", [(8,), (8, 8), (9, 12)])
+def test_apply_and_pullback(ca, spatial, transpose, cplx):
+    """test/rrule.jl:20 (and the transposed apply, which the reference does not test)."""
+    rng = np.random.default_rng(8)
+    ws, c, B = 5, 4, 2
+    A = ca.Circulant(ws, spatial + (1, B))
+    nzn = np.asfortranarray(rng.standard_normal(tuple(A.nzVal.shape)).astype(np.float32))
+    A.data.nzVal = ca.jl.from_numpy(nzn).requires_grad_(True)
+    bn, dcn = randn(rng, spatial + (c, B), cplx), randn(rng, spatial + (c, B), cplx)
+    b = ca.jl.from_numpy(bn).requires_grad_(True)
+    out = ca.circulant_transposed_attention(A, b) if transpose else ca.otimes(A, b)
+    K, Np = ws ** len(spatial), int(np.prod(spatial))
+    nz64 = nzn.astype(np.float64).reshape((K, Np, B), order="F")
+    oo = orc.apply(nz64, up(bn), ws, transpose)
+    assert rel_err(ca.jl.to_numpy(out), oo) < TOL
+    dc = ca.jl.from_numpy(dcn)
+    ((out * dc.conj()).real.sum() if cplx else (out * dc).sum()).backward()
+    if not transpose:
+        dAo, dbo = orc.apply_pullback(nz64, up(bn), ws, up(dcn))
+    else:
+        dAo = orc.similarity(orc.DOT, up(bn), up(dcn), ws)
+        dbo = orc.apply(nz64, up(dcn), ws, False)
+    assert rel_err(ca.jl.to_numpy(A.nzVal.grad), dAo) < TOL
+    assert rel_err(ca.jl.to_numpy(b.grad), dbo) < TOL
+
+
+def test_readme_identity_and_mh_apply(ca):
+    """README.md:115-119: softmax(S) ⊗ v ≈ y, and A ⨷ v ≈ y for the multi-head A."""
+    rng = np.random.default_rng(9)
+    shape, ws, nheads = (16, 12, 8, 2), 5, 2
+    q, k, v = (ca.jl.from_numpy(randn(rng, shape)) for _ in range(3))
+    y, A = ca.circulant_attention(ca.DistanceSimilarity(), q, k, v, ws)
+    t = float(np.sqrt(shape[2]))
+    S = ca.circulant_similarity(ca.DistanceSimilarity(), q / np.sqrt(t), k / np.sqrt(t), ws)
+    u = ca.otimes(ca.softmax(S), v)
+    assert rel_err(ca.jl.to_numpy(u), ca.jl.to_numpy(y).astype(np.float64)) < TOL
+    ym, Am = ca.circulant_mh_attention(ca.DotSimilarity(), q, k, v, ws, nheads)
+    um = ca.Otimes(Am, v)
+    assert rel_err(ca.jl.to_numpy(um), ca.jl.to_numpy(ym).astype(np.float64)) < TOL
+    ut = ca.circulant_mh_transposed_attention(Am, v)
+    nz64 = ca.jl.to_numpy(Am.nzVal).astype(np.float64).reshape((25, 192, 4), order="F")
+    uo = orc.apply(nz64, orc.splitheads(up(ca.jl.to_numpy(v)), nheads), ws, True)
+    assert rel_err(ca.jl.to_numpy(ut), uo) < TOL
