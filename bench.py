@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Benchmark of the circulant-attention hot path.
+
+A step = one fused forward + backward of multi-head circulant attention over one
+batch of synthetic input at the README quickstart shape (H, W, C, B = 128, 96,
+64, 2; ws = 15; 4 heads; DotSimilarity + softmax; Float32), flash mode (A is not
+written).  Metric: query pixels per second (one query pixel = one spatial
+location of one batch element with all channels and heads).
+
+    python bench.py [--gpus N --steps K --warmup W] [--impl reference]
+
+`--impl reference` times the CPU restatement (C + OpenMP; the reference package
+has no CPU path and cannot run without Julia) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(H=128, W=96, C=64, B=2, ws=15, nheads=4)
+METRIC = "fwd+bwd query-pixels/sec (ws=15, C=64, 4 heads)"
+UNIT = "px/s"
+NOMINAL_FFMA_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
+
+
+def algorithmic(workload, what):
+    """Algorithmic flops and bytes per query pixel: Dot fwd 4*K*C, bwd 10*K*C flop;
+    bytes fwd 4*C*4, bwd 7*C*4 (A not materialised)."""
+    K, C = workload["ws"] ** 2, workload["C"]
+    flops = {"fwd": 4 * K * C, "bwd": 10 * K * C, "bwd_dq": 6 * K * C, "bwd_dkdv": 4 * K * C}
+    flops["fwd+bwd"] = flops["fwd"] + flops["bwd"]
+    bytes_ = {"fwd": 16 * C, "bwd": 28 * C, "fwd+bwd": 44 * C, "bwd_dq": 20 * C, "bwd_dkdv": 28 * C}
+    return flops[what], bytes_[what]
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, f"/tmp/circatt_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- reference arm (CPU)
+def make_inputs(workload, seed):
+    rng = np.random.default_rng(seed)
+    shape = (workload["H"], workload["W"], workload["C"], workload["B"])
+    return [np.asfortranarray(rng.standard_normal(shape).astype(np.float32)) for _ in range(4)]
+
+
+def cpu_step(cpu, orc, arrs, workload):
+    q, k, v, r = (orc.splitheads(t, workload["nheads"]) for t in arrs)
+    y, lse = cpu.attention_fwd(q, k, v, workload["ws"])
+    return cpu.attention_bwd(q, k, v, y, r, lse, workload["ws"])
+
+
+def run_cpu(workload, steps, warmup):
+    from oracle import circatt_oracle as orc
+    from oracle import cpu_baseline as cpu
+    arrs = make_inputs(workload, 0)
+    for _ in range(warmup):
+        cpu_step(cpu, orc, arrs, workload)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(cpu, orc, arrs, workload)
+    dt = (time.perf_counter() - t0) / steps
+    px = workload["H"] * workload["W"] * workload["B"]
+    return px / dt, dt, cpu.threads()
+
+
+def reference_main(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 20)), max(1, min(args.warmup, 3))
+    value, dt, threads = run_cpu(WORKLOAD, steps, warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic (numpy default_rng(0) standard normal)",
+        "config": {"workload": "circulant_mh_attention fwd+bwd, H,W,C,B=128,96,64,2, ws=15, 4 heads, Dot, softmax",
+                   **WORKLOAD},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": "the full step (24576 query pixels), C + OpenMP float32 restatement; "
+                                   "the reference is Julia + CUDA.jl only and has no CPU path"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- B200 arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_main(args)
+
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ca = load_package()
+    lib, ops, jl = ca.lib, ca.ops, ca.jl
+    warmup = max(args.warmup, 3)
+    steps = args.steps
+
+    wl = WORKLOAD
+    H, W, C, B, ws, nheads = (wl[k] for k in ("H", "W", "C", "B", "ws", "nheads"))
+    px_per_step = H * W * B
+    kind, norm = 0, 0
+
+    # every rank owns one batch of the workload (weak scaling over batch x heads units, no collective)
+    host = [torch.from_numpy(np.ascontiguousarray(a.T)).pin_memory() for a in make_inputs(wl, rank)]
+    q, k, v, r = (ca.splitheads(t.to(dev).permute(3, 2, 1, 0), nheads) for t in host)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def step():
+        y, _, stats = ops.attention_fwd(kind, norm, q, k, v, ws, False)
+        return ops.attention_bwd(kind, norm, q, k, v, y, r, stats, ws)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step()
+    barrier()
+
+    # ---- timed region: K steps, each bracketed by CUDA events on the launching stream;
+    # L2 (126 MB) is flushed between steps because the 25 MB working set would stay resident.
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    n0 = lib.ca_probe_launch_count()
+    barrier()
+    for a, b in ev:
+        flush.fill_(1)
+        a.record()
+        step()
+        b.record()
+    barrier()
+    launches = (lib.ca_probe_launch_count() - n0) // steps
+    clocks = sampler.stop()
+    t_steps = [a.elapsed_time(b) * 1e-3 for a, b in ev]
+    total = torch.tensor([sum(t_steps)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    total = float(total.item())
+    value = px_per_step * steps * world / total
+
+    # ---- per-kernel durations (same inputs, L2 flushed before each launch) for the roofline
+    def time_stage(fn, n=20):
+        for _ in range(3):
+            fn()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for a, b in evs:
+            flush.fill_(1)
+            a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        ts = sorted(a.elapsed_time(b) * 1e-3 for a, b in evs)
+        return sum(ts) / len(ts), ts[len(ts) // 2]
+
+    y, _, stats = ops.attention_fwd(kind, norm, q, k, v, ws, False)
+    m = ops.meta_of(q, ws)
+    d = m.desc(similarity=kind, normalizer=norm, scale=1.0 / np.sqrt(m.channels))
+    D = torch.empty(lib.ca_attention_bwd_workspace(d) // 4, dtype=torch.float32, device=dev)
+    dq, dk, dv = (jl.empty(q.shape, q.dtype, dev) for _ in range(3))
+    st = lambda: torch.cuda.current_stream().cuda_stream
+    P = ca.ops.ptr
+    stages = {
+        "fwd": lambda: ops.attention_fwd(kind, norm, q, k, v, ws, False),
+        "bwd_pre": lambda: lib.ca_attention_bwd_pre(d, P(q), P(k), P(v), P(y), P(r), P(stats), None, None, P(D), st()),
+        "bwd_dq": lambda: lib.ca_attention_bwd_dq(d, P(q), P(k), P(v), P(r), P(stats), P(D), None, P(dq), st()),
+        "bwd_dkdv": lambda: lib.ca_attention_bwd_dkdv(d, P(q), P(k), P(v), P(r), P(stats), P(D), None, P(dk), P(dv), st()),
+    }
+    stage_s = {name: time_stage(fn)[0] for name, fn in stages.items()}
+
+    # ---- FP32 FMA peak measured on this GPU (not in MEASURED_PEAKS.json)
+    sink = torch.empty(148 * 8 * 256, dtype=torch.float32, device=dev)
+    ffma_s, _ = time_stage(lambda: lib.ca_probe_ffma(148 * 8, 4096, P(sink), st()), n=10)
+    ffma_tflops = 148 * 8 * 256 * 4096 * 16 * 2 * 2 / ffma_s / 1e12
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    dom = max(("fwd", "bwd_dq", "bwd_dkdv"), key=lambda s: stage_s[s])
+    fl, by = algorithmic(wl, dom)
+    achieved = fl * px_per_step / stage_s[dom] / 1e12
+    fl_all, by_all = algorithmic(wl, "fwd+bwd")
+    roofline = {
+        "bound": "ffma", "kernel": dom, "achieved": achieved, "peak": ffma_tflops, "unit": "TFLOP/s",
+        "frac": achieved / ffma_tflops, "traffic": None,
+        "peak_source": "FP32 FMA peak measured live by ca_probe_ffma (fma.rn.f32x2, 16 chains/thread); "
+                       f"nominal {NOMINAL_FFMA_TFLOPS:.2f}",
+        "hbm": {"achieved_gbs": by * px_per_step / stage_s[dom] / 1e9, "peak_gbs": hbm_peak,
+                "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"},
+        "step": {"achieved": fl_all * px_per_step / (total / steps) / 1e12,
+                 "frac": fl_all * px_per_step / (total / steps) / 1e12 / ffma_tflops,
+                 "roofline_px_per_s": ffma_tflops * 1e12 / fl_all},
+        "stage_us": {k_: v_ * 1e6 for k_, v_ in stage_s.items()},
+    }
+
+    # ---- end to end through the public API: pinned host inputs in, loss and gradients out
+    qh, kh, vh, rh = host
+    out_host = [torch.empty_like(qh).pin_memory() for _ in range(3)]
+
+    def e2e_step():
+        ins = [t.to(dev, non_blocking=True).permute(3, 2, 1, 0) for t in (qh, kh, vh, rh)]
+        qd, kd, vd = (t.requires_grad_(True) for t in ins[:3])
+        yy, _ = ca.circulant_mh_attention(ca.DotSimilarity(), qd, kd, vd, ws, nheads, return_A=False)
+        loss = (yy * ins[3]).sum()
+        loss.backward()
+        for o, t in zip(out_host, (qd, kd, vd)):
+            o.copy_(jl.colmajor(t.grad).permute(3, 2, 1, 0), non_blocking=True)
+        return float(loss.item())
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    n_e2e = max(5, min(steps, 30))
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    barrier()
+    e2e_t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_value = px_per_step * n_e2e * world / float(e2e_t.item())
+    nbytes = qh.numel() * 4
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cv, cdt, threads = run_cpu(wl, 5, 1)
+        cpu_baseline = {"value": cv, "unit": UNIT, "cores": threads, "kind": "port",
+                        "sample": "5 full steps (24576 query pixels each) of the C + OpenMP float32 restatement; "
+                                  "the reference has no CPU path"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": total / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic (numpy default_rng(rank) standard normal, random weights for the loss)",
+            "config": {"workload": "circulant_mh_attention fwd+bwd, H,W,C,B=128,96,64,2 per GPU, ws=15, 4 heads, Dot, "
+                                   "softmax, flash mode (A not written)", **wl, "units_per_gpu": nheads * B,
+                       "l2": "256 MB buffer written between timed steps (inputs are smaller than L2)",
+                       "sharding": "batch x heads units per rank, no collective"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 3 * nbytes + 4,
+                    "steps": n_e2e, "timing": "wall clock around the steps, synchronised on both sides, max over ranks"},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

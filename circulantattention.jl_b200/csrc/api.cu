@@ -5,10 +5,38 @@
 #include "tiled.cuh"
 
 #include <string.h>
+#include <atomic>
 
 namespace ca {
 
 static thread_local char g_err[512] = "";
+static std::atomic<int64_t> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// FP32 FMA peak probe: 16 independent packed-FMA chains per thread, registers only.
+__global__ void __launch_bounds__(256) ffma_probe_kernel(int iters, float* __restrict__ sink) {
+    unsigned long long acc[16];
+    const float seed = 1.0f + 1e-6f * threadIdx.x;
+    unsigned long long a, b;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(seed), "f"(seed * 0.5f));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(1e-7f), "f"(-1e-7f));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) asm("mov.b64 %0, {%1, %2};" : "=l"(acc[i]) : "f"((float)i), "f"(0.5f * i));
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            asm volatile("fma.rn.f32x2 %0, %1, %0, %2;" : "+l"(acc[i]) : "l"(a), "l"(b));
+    }
+    float out = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float x, y;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(acc[i]));
+        out += x + y;
+    }
+    sink[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = out;
+}
 
 void set_error(const char* fmt, ...) {
     va_list ap;
@@ -138,6 +166,16 @@ using namespace ca;
 extern "C" {
 
 int ca_version(void) { return 100; }
+
+int64_t ca_probe_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int ca_probe_ffma(int32_t blocks, int32_t iters, float* sink, void* stream) {
+    if (blocks < 1 || iters < 1) { set_error("blocks and iters must be positive"); return CA_ERR_BAD_DESC; }
+    if (!sink) { set_error("sink is NULL"); return CA_ERR_NULL; }
+    ffma_probe_kernel<<<blocks, 256, 0, as_stream(stream)>>>(iters, sink);
+    CA_CHECK_LAUNCH("FFMA probe kernel");
+    return CA_OK;
+}
 
 const char* ca_last_error(void) { return g_err; }
 

@@ -5,6 +5,7 @@
 #include <stdio.h>
 #include <stdarg.h>
 #include "../../include/circatt_b200.h"
+#include "../../include/circatt_b200_probe.h"
 
 namespace ca {
 
@@ -12,8 +13,11 @@ namespace ca {
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 
+void count_launch();
+
 #define CA_CHECK_LAUNCH(what)                                        \
     do {                                                             \
+        ca::count_launch();                                          \
         cudaError_t e__ = cudaGetLastError();                        \
         if (e__ != cudaSuccess) return ca::cuda_fail(e__, what);     \
     } while (0)

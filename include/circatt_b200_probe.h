@@ -1,0 +1,26 @@
+/*
+ * circatt_b200_probe.h -- measurement helpers exported by libcircatt_b200.so.
+ * They have no counterpart in the reference; the benchmark uses them to count
+ * the library's own kernel launches and to measure the FP32 FMA peak that the
+ * roofline fraction of the windowed kernels is quoted against.
+ */
+#ifndef CIRCATT_B200_PROBE_H
+#define CIRCATT_B200_PROBE_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Number of kernels this library has launched in the calling process so far. */
+int64_t ca_probe_launch_count(void);
+
+/* Launches one kernel of `blocks` x 256 threads; each thread runs `iters`
+ * rounds of 16 independent packed FP32 FMAs (fma.rn.f32x2) on registers and
+ * stores one value to `sink` (blocks*256 floats).  The kernel executes
+ * blocks*256*iters*16*2 FMAs = twice that many flops. */
+int ca_probe_ffma(int32_t blocks, int32_t iters, float* sink, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
