@@ -221,15 +221,16 @@ def main():
     y, _, stats = ops.attention_fwd(kind, norm, q, k, v, ws, False)
     m = ops.meta_of(q, ws)
     d = m.desc(similarity=kind, normalizer=norm, scale=1.0 / np.sqrt(m.channels))
-    D = torch.empty(lib.ca_attention_bwd_workspace(d) // 4, dtype=torch.float32, device=dev)
+    D = torch.empty(m.Np * m.units, dtype=torch.float32, device=dev)
+    sws = torch.empty(max(lib.ca_attention_bwd_stage_workspace(d), 16), dtype=torch.uint8, device=dev)
     dq, dk, dv = (jl.empty(q.shape, q.dtype, dev) for _ in range(3))
     st = lambda: torch.cuda.current_stream().cuda_stream
     P = ca.ops.ptr
     stages = {
         "fwd": lambda: ops.attention_fwd(kind, norm, q, k, v, ws, False),
         "bwd_pre": lambda: lib.ca_attention_bwd_pre(d, P(q), P(k), P(v), P(y), P(r), P(stats), None, None, P(D), st()),
-        "bwd_dq": lambda: lib.ca_attention_bwd_dq(d, P(q), P(k), P(v), P(r), P(stats), P(D), None, P(dq), st()),
-        "bwd_dkdv": lambda: lib.ca_attention_bwd_dkdv(d, P(q), P(k), P(v), P(r), P(stats), P(D), None, P(dk), P(dv), st()),
+        "bwd_dq": lambda: lib.ca_attention_bwd_dq(d, P(q), P(k), P(v), P(r), P(stats), P(D), None, P(dq), P(sws), st()),
+        "bwd_dkdv": lambda: lib.ca_attention_bwd_dkdv(d, P(q), P(k), P(v), P(r), P(stats), P(D), None, P(dk), P(dv), P(sws), st()),
     }
     stage_s = {name: time_stage(fn)[0] for name, fn in stages.items()}
 

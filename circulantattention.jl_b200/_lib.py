@@ -57,8 +57,10 @@ PROTOTYPES = {
     "ca_attention_bwd_workspace": (C.c_size_t, [_D]),
     "ca_attention_bwd": (C.c_int, [_D] + [_p] * 13),
     "ca_attention_bwd_pre": (C.c_int, [_D] + [_p] * 10),
-    "ca_attention_bwd_dq": (C.c_int, [_D] + [_p] * 9),
-    "ca_attention_bwd_dkdv": (C.c_int, [_D] + [_p] * 10),
+    "ca_attention_bwd_stage_workspace": (C.c_size_t, [_D]),
+    "ca_attention_bwd_dq": (C.c_int, [_D] + [_p] * 10),
+    "ca_attention_bwd_dkdv": (C.c_int, [_D] + [_p] * 11),
+    "ca_stage_timeouts": (C.c_int, [C.POINTER(C.c_int32)]),
     "ca_axpby": (C.c_int, [_i64, _f32, _p, _f32, _p, _p, _p]),
     "ca_scale_batch": (C.c_int, [_i64, _i32, _i32, _p, _i32, _i32, _p, _i32, _i32, _p, _p]),
     "ca_dot_batch": (C.c_int, [_i64, _i32, _i32, _p, _i32, _i32, _p, _i32, _i32, _p, _p]),

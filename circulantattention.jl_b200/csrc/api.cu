@@ -260,8 +260,8 @@ int ca_apply(const ca_desc* d, const float* nz, const void* v, void* out,
 size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {
     Geo g;
     if (make_geo(d, &g, true)) return 0;
-    if (d->normalizer == CA_ENTMAX15 && !want_nz) return (size_t)g.Np * g.K * g.units * sizeof(float);
-    return 0;
+    if (d->normalizer == CA_ENTMAX15) return want_nz ? 0 : (size_t)g.Np * g.K * g.units * sizeof(float);
+    return want_nz ? 0 : tiled_fwd_workspace(g);
 }
 
 int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void* v,
@@ -289,9 +289,11 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
         return launch_apply(g, sbuf, (const float*)v, nullptr, (float*)y, 1.f, 0, 0, 0, st);
     }
 
-    rc = tiled_attention_fwd(g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v,
-                             (float*)y, nz, stats, st);
-    if (rc != CA_ERR_UNSUPPORTED) return rc;
+    if (workspace) {
+        rc = tiled_attention_fwd(g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v,
+                                 (float*)y, nz, stats, workspace, st);
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+    }
 
     const int cmax = pick_cmax(g.cr);
     if (!cmax) { set_error("fused attention supports at most 64 real channels per unit (got %d); use similarity + normalize + apply", g.cr); return CA_ERR_UNSUPPORTED; }
@@ -302,10 +304,26 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
     return CA_OK;
 }
 
+static size_t d_bytes(const Geo& g) { return (((size_t)g.Npk * g.units * sizeof(float)) + 255) & ~(size_t)255; }
+
 size_t ca_attention_bwd_workspace(const ca_desc* d) {
     Geo g;
+    if (make_geo(d, &g, false)) return 0;
+    return d_bytes(g) + (d->normalizer == CA_SOFTMAX ? tiled_bwd_workspace(g) : 0);
+}
+
+size_t ca_attention_bwd_stage_workspace(const ca_desc* d) {
+    Geo g;
     if (make_geo(d, &g, true)) return 0;
-    return (size_t)g.Npk * g.units * sizeof(float);
+    return d->normalizer == CA_SOFTMAX ? tiled_bwd_stage_workspace(g) : 0;
+}
+
+int ca_stage_timeouts(int32_t* count) {
+    if (!count) { set_error("count is NULL"); return CA_ERR_NULL; }
+    int c = 0;
+    int rc = tiled_stage_timeouts(&c);
+    *count = c;
+    return rc;
 }
 
 int ca_attention_bwd_pre(const ca_desc* d, const void* q, const void* k, const void* v,
@@ -338,7 +356,7 @@ int ca_attention_bwd_pre(const ca_desc* d, const void* q, const void* k, const v
 
 int ca_attention_bwd_dq(const ca_desc* d, const void* q, const void* k, const void* v,
                         const void* dy, const float* stats, const float* D, const float* dA,
-                        void* dq, void* stream) {
+                        void* dq, void* workspace, void* stream) {
     Geo g;
     int rc = make_geo(d, &g, true);
     if (rc) return rc;
@@ -346,9 +364,9 @@ int ca_attention_bwd_dq(const ca_desc* d, const void* q, const void* k, const vo
     if (dA && g.Wk != g.W) { set_error("band mode never materialises A"); return CA_ERR_UNSUPPORTED; }
     cudaStream_t st = as_stream(stream);
     const int dist = d->similarity == CA_DISTANCE, ent = d->normalizer == CA_ENTMAX15;
-    if (!ent && !dA) {
+    if (!ent && !dA && workspace) {
         rc = tiled_attention_bwd_dq(g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v,
-                                    (const float*)dy, stats, D, (float*)dq, st);
+                                    (const float*)dy, stats, D, (float*)dq, workspace, st);
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
     const int cmax = pick_cmax(g.cr);
@@ -363,7 +381,7 @@ int ca_attention_bwd_dq(const ca_desc* d, const void* q, const void* k, const vo
 
 int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const void* v,
                           const void* dy, const float* stats, const float* D, const float* dA,
-                          void* dk, void* dv, void* stream) {
+                          void* dk, void* dv, void* workspace, void* stream) {
     Geo g;
     int rc = make_geo(d, &g, true);
     if (rc) return rc;
@@ -371,9 +389,9 @@ int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const 
     if (dA && g.Wk != g.W) { set_error("band mode never materialises A"); return CA_ERR_UNSUPPORTED; }
     cudaStream_t st = as_stream(stream);
     const int dist = d->similarity == CA_DISTANCE, ent = d->normalizer == CA_ENTMAX15;
-    if (!ent && !dA) {
+    if (!ent && !dA && workspace) {
         rc = tiled_attention_bwd_dkdv(g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v,
-                                      (const float*)dy, stats, D, (float*)dk, (float*)dv, st);
+                                      (const float*)dy, stats, D, (float*)dk, (float*)dv, workspace, st);
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
     const int cmax = pick_cmax(g.cr);
@@ -395,9 +413,16 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
     if (rc) return rc;
     if (!workspace) { set_error("workspace of ca_attention_bwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
     float* D = (float*)workspace;
+    if (d->normalizer == CA_SOFTMAX && !dA) {
+        if (!q || !k || !v || !y || !dy || !stats || !dq || !dk || !dv) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
+        rc = tiled_attention_bwd(g, d->scale, d->similarity == CA_DISTANCE, (const float*)q, (const float*)k,
+                                 (const float*)v, (const float*)y, (const float*)dy, stats, D, (float*)dq,
+                                 (float*)dk, (float*)dv, (char*)workspace + d_bytes(g), as_stream(stream));
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+    }
     if ((rc = ca_attention_bwd_pre(d, q, k, v, y, dy, stats, nz, dA, D, stream))) return rc;
-    if ((rc = ca_attention_bwd_dq(d, q, k, v, dy, stats, D, dA, dq, stream))) return rc;
-    return ca_attention_bwd_dkdv(d, q, k, v, dy, stats, D, dA, dk, dv, stream);
+    if ((rc = ca_attention_bwd_dq(d, q, k, v, dy, stats, D, dA, dq, nullptr, stream))) return rc;
+    return ca_attention_bwd_dkdv(d, q, k, v, dy, stats, D, dA, dk, dv, nullptr, stream);
 }
 
 int ca_axpby(int64_t n, float alpha, const float* x, float beta, const float* y, float* out, void* stream) {

@@ -4,16 +4,27 @@
 
 namespace ca {
 
+// Workspace sizes in bytes; 0 when the shape is outside what the tiled kernels cover.
+size_t tiled_fwd_workspace(const Geo& g);
+size_t tiled_bwd_workspace(const Geo& g);        // whole backward (without D)
+size_t tiled_bwd_stage_workspace(const Geo& g);  // one of the separately callable stages
+
 // Each returns CA_ERR_UNSUPPORTED (without touching the error text) when the
 // shape is outside what the tiled kernels cover; the caller then falls back
 // to the generic kernels.
 int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
-                        float* y, float* nz, float* stats, cudaStream_t st);
+                        float* y, float* nz, float* stats, void* workspace, cudaStream_t st);
+int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
+                        const float* y, const float* dy, const float* stats, float* D, float* dq, float* dk,
+                        float* dv, void* workspace, cudaStream_t st);
 int tiled_attention_bwd_dq(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
-                           const float* dy, const float* stats, const float* D, float* dq, cudaStream_t st);
+                           const float* dy, const float* stats, const float* D, float* dq, void* workspace,
+                           cudaStream_t st);
 int tiled_attention_bwd_dkdv(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                              const float* dy, const float* stats, const float* D, float* dk, float* dv,
-                             cudaStream_t st);
+                             void* workspace, cudaStream_t st);
+// Copies the count of stage-copy timeouts to the host (synchronises the device).
+int tiled_stage_timeouts(int* count);
 int tiled_apply(const Geo& g, const float* nz, const float* v, float* out, cudaStream_t st);
 
 }  // namespace ca

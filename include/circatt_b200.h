@@ -118,7 +118,10 @@ int ca_apply(const ca_desc* d, const float* nz, const void* v, void* out,
  * dimension, src/attention.jl:38-44).  `nz` (nullable) receives A's values in
  * CSR order; `stats` (nullable, Np*units floats) the per-row log-sum-exp /
  * entmax threshold needed by ca_attention_bwd.  `workspace` must hold
- * ca_attention_fwd_workspace() bytes (may be NULL when that is 0). */
+ * ca_attention_fwd_workspace() bytes (may be NULL when that is 0); the tiled
+ * sm_100a kernels keep their packed copies of k and v there.  A NULL workspace
+ * where one is needed selects the slower untiled kernels (softmax) or is an
+ * error (entmax without nz). */
 size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz);
 int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void* v,
                      void* y, float* nz, float* stats, void* workspace, void* stream);
@@ -139,16 +142,25 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
  * stages.  D holds one float per (query-side pixel, unit):
  *   softmax: D = dy . y + sum_k A_k dA_k      entmax: D = sum g dP / sum g.
  * In band mode (d->Wk = W + 2p) ca_attention_bwd_dq reads k, v with Wk columns,
- * and ca_attention_bwd_dkdv reads q, dy, stats, D with Wk columns. */
+ * and ca_attention_bwd_dkdv reads q, dy, stats, D with Wk columns.
+ * `workspace` of the dq / dkdv stages (nullable: NULL selects the slower
+ * untiled kernels) must hold ca_attention_bwd_stage_workspace() bytes. */
 int ca_attention_bwd_pre(const ca_desc* d, const void* q, const void* k, const void* v,
                          const void* y, const void* dy, const float* stats,
                          const float* nz, const float* dA, float* D, void* stream);
+size_t ca_attention_bwd_stage_workspace(const ca_desc* d);
 int ca_attention_bwd_dq(const ca_desc* d, const void* q, const void* k, const void* v,
                         const void* dy, const float* stats, const float* D, const float* dA,
-                        void* dq, void* stream);
+                        void* dq, void* workspace, void* stream);
 int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const void* v,
                           const void* dy, const float* stats, const float* D, const float* dA,
-                          void* dk, void* dv, void* stream);
+                          void* dk, void* dv, void* workspace, void* stream);
+
+/* Diagnostics (synchronises the device): number of thread blocks that gave up
+ * waiting for a shared-memory stage copy since the library was loaded.  Every
+ * device-side wait in the library is bounded; a non-zero count means results
+ * of some call are invalid.  No counterpart in the reference. */
+int ca_stage_timeouts(int32_t* count);
 
 /* ---------------------------------------------------------------- algebra on values
  * out[n,i,j] = alpha*x[n,i,j] + beta*y[n,i,j] over a flat length (X+Y, X-Y, c*X:

@@ -55,6 +55,12 @@ CASES = [
     ((300, 16, 2), 31, 2, False),        # long 1-D window
     ((20, 20, 33, 1), 5, 1, False),      # 33 channels: 64-wide register path
     ((24, 20, 20, 2), 7, 1, True),       # 40 real channels
+    ((40, 21, 16, 2), 7, 2, True),       # 8 complex = 16 real channels per head: tiled kernels, complex loads
+    ((128, 24, 16, 1), 21, 1, False),    # window 21, full-height tile
+    ((33, 9, 16, 1), 9, 1, False),       # ragged tile rows, extent == window along w
+    ((50, 18, 32, 1), 11, 2, False),
+    ((48, 16, 16, 2), 13, 1, False),
+    ((16, 17, 16, 1), 3, 1, False),
 ]
 
 
@@ -83,7 +89,8 @@ def test_attention_forward_backward(ca, shape, ws, nheads, cplx, simname):
 
 @pytest.mark.parametrize("simname", ["dot", "distance"])
 def test_flash_mode_equals_materialised(ca, simname):
-    """return_A=False never writes A; y and gradients are the same bits."""
+    """return_A=False never writes A; y and gradients agree with the materialising path
+    (different kernels, so to rounding, not to the bit)."""
     rng = np.random.default_rng(1)
     shape = (24, 20, 32, 2)
     qn, kn, vn, rn = (randn(rng, shape) for _ in range(4))
@@ -95,7 +102,7 @@ def test_flash_mode_equals_materialised(ca, simname):
         (y * ca.jl.from_numpy(rn)).sum().backward()
         outs.append([ca.jl.to_numpy(t) for t in (y, q.grad, k.grad, v.grad)])
     for a, b in zip(*outs):
-        assert np.array_equal(a, b)
+        assert rel_err(a, b.astype(np.float64)) < TOL
 
 
 def test_cotangent_on_returned_A(ca):
@@ -255,3 +262,11 @@ def test_readme_identity_and_mh_apply(ca):
     nz64 = ca.jl.to_numpy(Am.nzVal).astype(np.float64).reshape((25, 192, 4), order="F")
     uo = orc.apply(nz64, orc.splitheads(up(ca.jl.to_numpy(v)), nheads), ws, True)
     assert rel_err(ca.jl.to_numpy(ut), uo) < TOL
+
+
+def test_no_stage_copy_timed_out(ca):
+    """Every device-side wait is bounded; a healthy run never hits the bound."""
+    import ctypes
+    n = ctypes.c_int32(-1)
+    assert ca.lib.ca_stage_timeouts(ctypes.byref(n)) == 0
+    assert n.value == 0
