@@ -1,37 +1,46 @@
 // Tiled sm_100a kernels for 2-D windows with 16 real channels per unit
 // (16 Float32 or 8 ComplexF32 channels per head) and softmax.
 //
-// Work decomposition.  A CTA owns TH consecutive rows (the fast axis h) of FOUR
-// consecutive columns w0..w0+3 of one unit.  A thread owns one row and the four
-// pixels of that row ("centre" pixels: queries in the forward and dq kernels,
-// keys in the dk/dv kernel) and keeps their 16-channel vectors in registers.
-// The other side of the window is streamed through shared memory one image
-// column at a time: column stage s holds column w0 - p + s (wrapped circularly,
-// or taken from the neighbour halo in band mode) for rows h0-p' .. h0+TH+p'-1.
-// Centre pixel r pairs with stage s iff r <= s <= r + 2p, so every loaded
-// 16-float vector is used by up to four centre pixels from registers.
+// Work decomposition.  A CTA owns TH consecutive rows (the fast axis h) of NQ
+// consecutive columns w0..w0+NQ-1 of one unit (NQ = 4 in the forward and dq
+// kernels, 3 in the dk/dv kernel).  A thread owns one row and the NQ pixels of
+// that row ("centre" pixels: queries in the forward and dq kernels, keys in
+// the dk/dv kernel) and keeps their 16-channel vectors in registers.  The other
+// side of the window is streamed through shared memory one image column at a
+// time: column stage s holds column w0 - p + s (wrapped circularly, or taken
+// from the neighbour halo in band mode) for rows h0-p' .. h0+TH+p'-1.  Centre
+// pixel r pairs with stage s iff r <= s <= r + 2p, so every loaded vector is
+// used by up to NQ centre pixels straight from registers.
 //
 // Feeding the stages.  The reference layout is channel-planar, which no bulk
-// copy can turn into pixel vectors, so a pack kernel first rewrites the
-// streamed tensors as [unit][column][row'][16 channels] with the circular halo
-// along h already unrolled (row' = h + p', p' = p rounded up to even, rows
-// -p'..-1 and H..H+p'-1 are copies of the wrapped rows).  A column stage is
-// then ONE contiguous box per tensor, fetched by cp.async.bulk.tensor (TMA) with
-// the 64-byte hardware swizzle and tracked by an mbarrier; three stages are in
-// flight.  The wrap along w is just the column coordinate of the box.
+// copy can turn into pixel vectors, so a pack kernel first rewrites the two
+// streamed tensors as ONE array [unit][column][row'][36] = (16 channels of the
+// first | 16 of the second | 4 floats of padding) with the circular halo along
+// h already unrolled (row' = h + p', p' = p rounded up to even; rows -p'..-1
+// and H..H+p'-1 are copies of the wrapped rows).  A column stage is then a
+// single contiguous box fetched by cp.async.bulk.tensor (TMA) and tracked by an
+// mbarrier; three stages are in flight.  The wrap along w is just the column
+// coordinate of the box.
 //
-// Shared-memory layout: pixel (row) = 64 bytes = four 16-byte chunks; the TMA
-// 64B swizzle stores chunk cq of row `row` at chunk position
-// cq ^ ((row >> 1) & 3).  Eight consecutive rows then hit eight distinct
-// 4-bank groups, so the 128-bit loads of a warp whose lanes hold consecutive
-// rows are conflict free.
+// Shared-memory layout: a pixel row is 144 bytes (36 words).  The rows that the
+// eight lanes of a 128-bit load phase touch are consecutive, 36 words apart,
+// i.e. nine 4-bank groups apart: eight distinct groups, so the loads are
+// conflict free without any address swizzle and every chunk of every row of a
+// window column is the thread's row base plus a compile-time constant.
 //
-// Arithmetic: FP32 on the FMA pipe, issued as packed fma.rn.f32x2 so that a
-// 16-channel dot product or axpy is 8 instructions; softmax in the log2 domain
-// with ex2.approx; the running maximum is only rescaled when some lane of the
-// warp actually raises it.
+// Arithmetic: FP32 on the FMA pipe, issued as packed fma.rn.f32x2 (a
+// 16-channel dot product or axpy is 8 instructions); softmax in the log2
+// domain with ex2.approx.  The running maximum (forward) or the saved row
+// statistic (backward) is folded into the initial value of the dot-product
+// chain, and the forward only touches the maximum when the sign bits of a chunk
+// of relative scores say that one of them is positive.
+//
+// Small grids.  When the grid would not fill the GPU, the column stages of a
+// tile are split between two groups of warps of the same CTA (each with its own
+// copy pipeline) whose partial results are merged through shared memory.
 #include "tiled.cuh"
 #include "tma.cuh"
+#include <stdlib.h>
 
 namespace ca {
 namespace {
@@ -56,6 +65,11 @@ __device__ __forceinline__ u64 mul2(u64 a, u64 b) {
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
+__device__ __forceinline__ u64 add2(u64 a, u64 b) {
+    u64 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ float hsum2(u64 v) {
     float a, b;
     unpack2(v, a, b);
@@ -68,6 +82,7 @@ struct TileArgs {
     int TH;                 // rows per CTA
     int roff;               // p' - p: first window row inside a stage buffer
     int stage_bytes;        // bytes of one stage buffer (multiple of 1024)
+    int nsplit;             // 1 or 2 groups of warps sharing the stages of a tile
     const float* c0;        // centre tensors (reference layout)
     const float* c1;
     const float* cs0;       // centre scalars (dq kernel: stats, D)
@@ -77,30 +92,26 @@ struct TileArgs {
     float* ostats;
 };
 
+constexpr int kStages = 3;
+
 // Number of CTAs that gave up waiting for a stage copy (stays 0 in a healthy run).
 __device__ int g_stage_timeouts = 0;
 
-constexpr int kStages = 3;
+constexpr int kRowFloats = 36;                 // 16 + 16 + 4 padding
+constexpr int kRowBytes = kRowFloats * 4;      // 144
 
-__device__ __forceinline__ int swz(int row, int cq) { return row * 16 + ((cq ^ ((row >> 1) & 3)) << 2); }
-
-// One 16-channel pixel vector as eight packed pairs.
-__device__ __forceinline__ void lds_vec16(const float* buf, int row, u64 (&v)[8]) {
-#pragma unroll
-    for (int cq = 0; cq < 4; ++cq) {
-        const float4 t = *reinterpret_cast<const float4*>(buf + swz(row, cq));
-        v[2 * cq] = pack2(t.x, t.y);
-        v[2 * cq + 1] = pack2(t.z, t.w);
-    }
+__device__ __forceinline__ void lds128(uint32_t addr, u64& lo, u64& hi) {
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(addr));
 }
-// Half of it (channels 8*half .. 8*half+7) as four packed pairs.
-__device__ __forceinline__ void lds_vec8(const float* buf, int row, int half, u64 (&v)[4]) {
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const float4 t = *reinterpret_cast<const float4*>(buf + swz(row, 2 * half + j));
-        v[2 * j] = pack2(t.x, t.y);
-        v[2 * j + 1] = pack2(t.z, t.w);
-    }
+
+// 16-channel vector `which` (0: first tensor, 1: second) of the pixel row at
+// shared-space byte address `a0`, as eight packed pairs.
+__device__ __forceinline__ void lds_vec16(uint32_t a0, int which, u64 (&v)[8]) {
+    const uint32_t b = a0 + which * 64;
+    lds128(b, v[0], v[1]);
+    lds128(b + 16, v[2], v[3]);
+    lds128(b + 32, v[4], v[5]);
+    lds128(b + 48, v[6], v[7]);
 }
 
 // Global offset of real channel cc of unit u at pixel pix (npix pixels per plane).
@@ -115,32 +126,44 @@ __device__ __forceinline__ int stage_column(const Geo& g, int w0, int s) {
     return kc < 0 ? kc + g.Wk : kc;
 }
 
-// Stage pipeline shared by the three kernels.  Thread 0 is the producer: it
-// arms the stage's mbarrier with the byte count and issues the TMA boxes.
+template <int NQ>
+__device__ __forceinline__ int stage_mask(int s, int p) {
+    int mask = 0;
+#pragma unroll
+    for (int r = 0; r < NQ; ++r)
+        if (s >= r && s <= r + 2 * p) mask |= 1 << r;
+    return mask;
+}
+
+// Barrier of one group of warps (ids 1 and 2; id 0 stays the CTA-wide barrier).
+__device__ __forceinline__ void part_sync(int part, int nthreads) {
+    if (part == 0) asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    else asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Stage pipeline of one group of warps ("part").  Thread 0 of the part is the
+// producer: it arms the stage's mbarrier with the byte count and issues the
+// TMA boxes; every consumer wait is bounded.
+// ---------------------------------------------------------------------------
 template <bool NSC>
 struct StagePipe {
-    uint64_t* full;
-    unsigned char* base;
-    const CUtensorMap* m0;
-    const CUtensorMap* m1;
+    uint64_t* full;          // kStages barriers of this part
+    unsigned char* base;     // kStages stage buffers of this part
+    const CUtensorMap* mv;
     const CUtensorMap* msc;
     int ROWS, stage_bytes, u, h0, w0;
 
-    // Each vector region starts on a 512-byte boundary so that the swizzle phase
-    // (address bits 7-8) equals (row >> 1) & 3; scalar rows start on 128 bytes.
-    __device__ __forceinline__ int vstride() const { return (ROWS * 64 + 511) & ~511; }
+    __device__ __forceinline__ unsigned char* vec(int buf) const { return base + (size_t)buf * stage_bytes; }
     __device__ __forceinline__ int sstride() const { return (ROWS * 4 + 127) & ~127; }
-    __device__ __forceinline__ float* vec0(int buf) const { return reinterpret_cast<float*>(base + (size_t)buf * stage_bytes); }
-    __device__ __forceinline__ float* vec1(int buf) const { return reinterpret_cast<float*>(base + (size_t)buf * stage_bytes + vstride()); }
-    __device__ __forceinline__ float* sc0(int buf) const { return reinterpret_cast<float*>(base + (size_t)buf * stage_bytes + 2 * vstride()); }
-    __device__ __forceinline__ float* sc1(int buf) const { return reinterpret_cast<float*>(base + (size_t)buf * stage_bytes + 2 * vstride() + sstride()); }
+    __device__ __forceinline__ int vbytes() const { return (ROWS * kRowBytes + 127) & ~127; }
+    __device__ __forceinline__ float* sc0(int buf) const { return reinterpret_cast<float*>(vec(buf) + vbytes()); }
+    __device__ __forceinline__ float* sc1(int buf) const { return reinterpret_cast<float*>(vec(buf) + vbytes() + sstride()); }
 
-    __device__ __forceinline__ void issue(const Geo& g, int s) const {
-        const int buf = s % kStages;
+    __device__ __forceinline__ void issue(const Geo& g, int s, int buf) const {
         const int kc = stage_column(g, w0, s);
-        mbar_arrive_expect_tx(&full[buf], (uint32_t)(ROWS * 128 + (NSC ? ROWS * 8 : 0)));
-        tma_load_4d(vec0(buf), m0, 0, h0, kc, u, &full[buf]);
-        tma_load_4d(vec1(buf), m1, 0, h0, kc, u, &full[buf]);
+        mbar_arrive_expect_tx(&full[buf], (uint32_t)(ROWS * kRowBytes + (NSC ? ROWS * 8 : 0)));
+        tma_load_4d(vec(buf), mv, 0, h0, kc, u, &full[buf]);
         if (NSC) {
             tma_load_3d(sc0(buf), msc, h0, kc, 2 * u, &full[buf]);
             tma_load_3d(sc1(buf), msc, h0, kc, 2 * u + 1, &full[buf]);
@@ -148,58 +171,58 @@ struct StagePipe {
     }
 };
 
-#define CA_PIPE_PROLOGUE(NSCV)                                                                      \
-    extern __shared__ unsigned char smem_raw[];                                                     \
-    __shared__ __align__(8) uint64_t full_bar[kStages];                                             \
-    __shared__ int s_err;                                                                           \
-    StagePipe<NSCV> pipe;                                                                           \
-    pipe.full = full_bar;                                                                           \
-    pipe.base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);                        \
-    pipe.m0 = &m0; pipe.m1 = &m1; pipe.msc = &msc;                                                  \
-    pipe.ROWS = ROWS; pipe.stage_bytes = a.stage_bytes; pipe.u = u; pipe.h0 = h0; pipe.w0 = w0;     \
-    if (threadIdx.x == 0) {                                                                         \
-        for (int i = 0; i < kStages; ++i) mbar_init(&full_bar[i], 1);                               \
-        s_err = 0;                                                                                  \
-        mbar_fence_init();                                                                          \
-    }                                                                                               \
-    __syncthreads();                                                                                \
-    const int NS = g.ws + 3;                                                                        \
-    if (threadIdx.x == 0)                                                                           \
-        for (int s = 0; s < kStages && s < NS; ++s) pipe.issue(g, s);
+// Declares the pipeline of this thread's part and starts the first copies.
+// Needs in scope: a (TileArgs), g, ROWS, u, h0, w0, NS (stages of the tile), mv, msc.
+#define CA_PIPE_PROLOGUE(NSCV)                                                                       \
+    extern __shared__ unsigned char smem_raw[];                                                      \
+    __shared__ __align__(8) uint64_t full_bar[2 * kStages];                                          \
+    __shared__ int s_err;                                                                            \
+    const int PT = blockDim.x / a.nsplit;          /* threads per part */                            \
+    const int part = threadIdx.x / PT;                                                               \
+    const int lt = threadIdx.x - part * PT;                                                          \
+    const int s_begin = part * (NS / a.nsplit);                                                      \
+    const int s_end = (part + 1 == a.nsplit) ? NS : (part + 1) * (NS / a.nsplit);                    \
+    unsigned char* smem_al = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);            \
+    StagePipe<NSCV> pipe;                                                                            \
+    pipe.full = full_bar + part * kStages;                                                           \
+    pipe.base = smem_al + (size_t)part * kStages * a.stage_bytes;                                    \
+    pipe.mv = &mv; pipe.msc = &msc;                                                                  \
+    pipe.ROWS = ROWS; pipe.stage_bytes = a.stage_bytes; pipe.u = u; pipe.h0 = h0; pipe.w0 = w0;      \
+    if (threadIdx.x == 0) {                                                                          \
+        for (int i = 0; i < 2 * kStages; ++i) mbar_init(&full_bar[i], 1);                            \
+        s_err = 0;                                                                                   \
+        mbar_fence_init();                                                                           \
+    }                                                                                                \
+    __syncthreads();                                                                                 \
+    if (lt == 0)                                                                                     \
+        for (int i = 0; i < kStages && s_begin + i < s_end; ++i) pipe.issue(g, s_begin + i, i);
 
-// Consumer side of one stage: bounded wait, compute, then recycle the buffer.
-#define CA_PIPE_LOOP(...)                                                                           \
-    for (int s = 0; s < NS; ++s) {                                                                  \
-        const int buf = s % kStages;                                                                \
-        if (!mbar_wait(&full_bar[buf], (uint32_t)((s / kStages) & 1))) s_err = 1;                   \
-        __VA_ARGS__                                                                                 \
-        __syncthreads();                                                                            \
-        if (s_err) break;                                                                           \
-        if (threadIdx.x == 0 && s + kStages < NS) pipe.issue(g, s + kStages);                       \
-    }                                                                                               \
-    if (s_err) {                                                                                    \
-        /* give copies still in flight a bounded chance to land before the CTA exits */             \
-        if (threadIdx.x == 0) {                                                                     \
-            for (int i = 0; i < kStages; ++i) mbar_wait(&full_bar[i], 0, 1u << 12);                 \
-            atomicAdd(&g_stage_timeouts, 1);                                                        \
-        }                                                                                           \
-        return;                                                                                     \
+// Consumer loop over the stages of this part: bounded wait, BODY, recycle the buffer.
+#define CA_PIPE_LOOP(...)                                                                            \
+    for (int s = s_begin; s < s_end; ++s) {                                                          \
+        const int it = s - s_begin;                                                                  \
+        const int buf = it % kStages;                                                                \
+        if (!mbar_wait(&pipe.full[buf], (uint32_t)((it / kStages) & 1))) s_err = 1;                  \
+        __VA_ARGS__                                                                                  \
+        part_sync(part, PT);                                                                         \
+        if (s_err) break;                                                                            \
+        if (lt == 0 && s + kStages < s_end) pipe.issue(g, s + kStages, buf);                         \
+    }                                                                                                \
+    __syncthreads();                                                                                 \
+    if (s_err) {                                                                                     \
+        /* give copies still in flight a bounded chance to land before the CTA exits */              \
+        if (lt == 0)                                                                                 \
+            for (int i = 0; i < kStages; ++i) mbar_wait(&pipe.full[i], 0, 1u << 12);                 \
+        if (threadIdx.x == 0) atomicAdd(&g_stage_timeouts, 1);                                       \
+        return;                                                                                      \
     }
 
-__device__ __forceinline__ int stage_mask(int s, int p) {
-    int mask = 0;
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-        if (s >= r && s <= r + 2 * p) mask |= 1 << r;
-    return mask;
-}
-
-// Loads the 16-channel vectors of the four centre pixels of this thread, times `mul`.
-template <int CPE>
+// Loads the 16-channel vectors of the NQ centre pixels of this thread, times `mul`.
+template <int CPE, int NQ>
 __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int u, int h, int w0, bool active,
-                                            float mul, u64 (&dst)[4][8]) {
+                                            float mul, u64 (&dst)[NQ][8]) {
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < NQ; ++r) {
         const bool ok = active && (w0 + r < g.W);
         const int pix = h + g.H * (w0 + r);
 #pragma unroll
@@ -233,20 +256,28 @@ __device__ __forceinline__ void store_centre(float* dst, const Geo& g, int u, in
     }
 }
 
+// MASK != 0: all centre pixels pair with this stage (compile time);
+// MASK == 0: the set is the run-time `rm` (warp-uniform branches).
+#define CA_ON(r) ((MASK != 0) || ((rm >> (r)) & 1))
+
 // =====================================================================
 // Forward
 // =====================================================================
+// Scores are kept relative to the running maximum: the dot-product chain
+// starts at -m, so sc = s - m and p = 2^sc needs no subtraction.  The
+// maximum moves only when some relative score of the chunk is positive, which
+// the AND of the sign bits of the chunk reveals.
 template <int DC, bool DIST, int MASK>
-__device__ __forceinline__ void fwd_stage(const float* kb, const float* vb, int lr, int ws, float sl2,
-                                          const u64 (&q)[4][8], u64 (&acc)[4][8], float (&m)[4], float (&l)[4],
-                                          const float (&bq)[4]) {
+__device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[4][8],
+                                          u64 (&acc)[4][8], u64 (&nm2)[4], float (&l)[4], const float (&bq)[4]) {
     for (int c0 = 0; c0 < ws; c0 += DC) {
+        const uint32_t cb = rowbase + c0 * kRowBytes;
         float sc[4][DC];
 #pragma unroll
         for (int t = 0; t < DC; ++t) {
             if (c0 + t < ws) {
                 u64 k2[8];
-                lds_vec16(kb, lr + c0 + t, k2);
+                lds_vec16(cb + t * kRowBytes, 0, k2);
                 float bk = 0.f;
                 if (DIST) {
                     u64 n = 0ull;
@@ -256,59 +287,57 @@ __device__ __forceinline__ void fwd_stage(const float* kb, const float* vb, int 
                 }
 #pragma unroll
                 for (int r = 0; r < 4; ++r)
-                    if (MASK & (1 << r)) {
-                        u64 s2 = 0ull;
+                    if (CA_ON(r)) {
+                        u64 sa = nm2[r];                          // (-m, 0)
+                        if (DIST) sa = add2(sa, pack2(bq[r] + bk, 0.f));
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) s2 = fma2(q[r][i], k2[i], s2);
-                        sc[r][t] = hsum2(s2) + (DIST ? bq[r] + bk : 0.f);
+                        for (int i = 0; i < 8; ++i) sa = fma2(q[r][i], k2[i], sa);
+                        sc[r][t] = hsum2(sa);
+                    } else {
+                        sc[r][t] = -INFINITY;
                     }
             } else {
 #pragma unroll
                 for (int r = 0; r < 4; ++r) sc[r][t] = -INFINITY;
             }
         }
-        float mn[4];
-        bool raise = false;
+        // any relative score >= 0 ?  (sign bit clear)
+        uint32_t allneg = 0x80000000u;
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-            if (MASK & (1 << r)) {
+#pragma unroll
+            for (int t = 0; t < DC; ++t) allneg &= __float_as_uint(sc[r][t]);
+        if (__any_sync(0xffffffffu, allneg == 0u)) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
                 float cm = sc[r][0];
 #pragma unroll
                 for (int t = 1; t < DC; ++t) cm = fmaxf(cm, sc[r][t]);
-                mn[r] = fmaxf(m[r], cm);
-                raise |= mn[r] > m[r];
-            }
-        if (__any_sync(0xffffffffu, raise)) {
-#pragma unroll
-            for (int r = 0; r < 4; ++r)
-                if (MASK & (1 << r)) {
-                    const float corr = fast_exp2(m[r] - mn[r]);
-                    m[r] = mn[r];
+                if (cm > 0.f) {                 // raise the maximum of this row by cm
+                    const float corr = fast_exp2(-cm);
+                    float nm, zero;
+                    unpack2(nm2[r], nm, zero);
+                    nm2[r] = pack2(nm - cm, 0.f);
                     l[r] *= corr;
                     const u64 c2 = pack2(corr, corr);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) acc[r][i] = mul2(acc[r][i], c2);
-                }
-        }
 #pragma unroll
-        for (int r = 0; r < 4; ++r)
-            if (MASK & (1 << r)) {
-#pragma unroll
-                for (int t = 0; t < DC; ++t) {
-                    const float pt = fast_exp2(sc[r][t] - m[r]);
-                    l[r] += pt;
-                    sc[r][t] = pt;
+                    for (int t = 0; t < DC; ++t) sc[r][t] -= cm;
                 }
             }
+        }
 #pragma unroll
         for (int t = 0; t < DC; ++t) {
             if (c0 + t < ws) {
                 u64 v2[8];
-                lds_vec16(vb, lr + c0 + t, v2);
+                lds_vec16(cb + t * kRowBytes, 1, v2);
 #pragma unroll
                 for (int r = 0; r < 4; ++r)
-                    if (MASK & (1 << r)) {
-                        const u64 p2 = pack2(sc[r][t], sc[r][t]);
+                    if (CA_ON(r)) {
+                        const float pt = fast_exp2(sc[r][t]);
+                        l[r] += pt;
+                        const u64 p2 = pack2(pt, pt);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) acc[r][i] = fma2(p2, v2[i], acc[r][i]);
                     }
@@ -317,36 +346,53 @@ __device__ __forceinline__ void fwd_stage(const float* kb, const float* vb, int 
     }
 }
 
-#define CA_MASK_SWITCH(mask, CALL)                       \
-    switch (mask) {                                      \
-        case 1:  { constexpr int MK = 1;  CALL; } break; \
-        case 3:  { constexpr int MK = 3;  CALL; } break; \
-        case 7:  { constexpr int MK = 7;  CALL; } break; \
-        case 15: { constexpr int MK = 15; CALL; } break; \
-        case 14: { constexpr int MK = 14; CALL; } break; \
-        case 12: { constexpr int MK = 12; CALL; } break; \
-        case 8:  { constexpr int MK = 8;  CALL; } break; \
-        default: break;                                  \
+// First score of each centre pixel that starts in this stage: the reference
+// point of its running maximum.
+template <bool DIST>
+__device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float sl2, const u64 (&q)[4][8],
+                                             u64 (&nm2)[4], const float (&bq)[4]) {
+    u64 k2[8];
+    lds_vec16(rowbase, 0, k2);
+    float bk = 0.f;
+    if (DIST) {
+        u64 n = 0ull;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
+        bk = -0.5f * sl2 * hsum2(n);
     }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+        if ((init >> r) & 1) {
+            u64 sa = 0ull;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sa = fma2(q[r][i], k2[i], sa);
+            nm2[r] = pack2(-(hsum2(sa) + (DIST ? bq[r] + bk : 0.f)), 0.f);
+        }
+}
+
+#define CA_MASK_SWITCH(FULL, mask, CALL)                            \
+    if ((mask) == (FULL)) { constexpr int MK = (FULL); CALL; }      \
+    else { constexpr int MK = 0; CALL; }
 
 template <int DC, bool DIST, int CPE>
-__global__ void __launch_bounds__(128) fwd_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap m0,
-                                                        const __grid_constant__ CUtensorMap m1,
-                                                        const __grid_constant__ CUtensorMap msc) {
+__global__ void __launch_bounds__(128, 3) fwd_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+                                                           const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
+    const int NS = g.ws + 3;
     const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
-    const int lr = threadIdx.x, h = h0 + lr;
-    const bool active = h < g.H;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
+    const int lr = lt, h = h0 + lr;
+    const bool active = h < g.H;
 
     u64 q[4][8], acc[4][8];
-    load_centre<CPE>(a.c0, g, u, h, w0, active, sl2, q);
-    float m[4], l[4], bq[4];
+    load_centre<CPE, 4>(a.c0, g, u, h, w0, active, sl2, q);
+    u64 nm2[4];
+    float l[4], bq[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-        m[r] = -INFINITY;
+        nm2[r] = pack2(INFINITY, 0.f);           // (-m, 0); running maximum -inf: no key seen yet
         l[r] = 0.f;
         bq[r] = 0.f;
         if (DIST) {
@@ -360,11 +406,55 @@ __global__ void __launch_bounds__(128) fwd_tiled_kernel(TileArgs a, const __grid
     }
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask(s, g.p);
-        const float* kb = pipe.vec0(buf);
-        const float* vb = pipe.vec1(buf);
-        CA_MASK_SWITCH(mask, (fwd_stage<DC, DIST, MK>(kb, vb, lr + a.roff, g.ws, sl2, q, acc, m, l, bq)));
+        const int mask = stage_mask<4>(s, g.p);
+        const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes;
+        // pixels whose first stage (of this part) is s
+        const int init = (s == s_begin) ? mask : (mask & ~stage_mask<4>(s - 1, g.p));
+        if (init) fwd_init_max<DIST>(rowbase, init, sl2, q, nm2, bq);
+        CA_MASK_SWITCH(15, mask, (fwd_stage<DC, DIST, MK>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq)));
     })
+
+    float nm[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        float zero;
+        unpack2(nm2[r], nm[r], zero);
+    }
+    if (a.nsplit == 2) {
+        // merge the two partial softmaxes: part 1 publishes (m, l, acc), part 0 combines
+        float* xch = reinterpret_cast<float*>(smem_al);
+        if (part == 1) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                xch[(r * 18 + 0) * PT + lt] = nm[r];
+                xch[(r * 18 + 1) * PT + lt] = l[r];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float x, y;
+                    unpack2(acc[r][i], x, y);
+                    xch[(r * 18 + 2 + 2 * i) * PT + lt] = x;
+                    xch[(r * 18 + 3 + 2 * i) * PT + lt] = y;
+                }
+            }
+        }
+        __syncthreads();
+        if (part == 1) return;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float nm1 = xch[(r * 18 + 0) * PT + lt], l1 = xch[(r * 18 + 1) * PT + lt];
+            const float nmn = fminf(nm[r], nm1);           // -max(m0, m1)
+            const float c0 = (nm[r] == INFINITY) ? 0.f : fast_exp2(nmn - nm[r]);
+            const float c1 = (nm1 == INFINITY) ? 0.f : fast_exp2(nmn - nm1);
+            l[r] = l[r] * c0 + l1 * c1;
+            nm[r] = nmn;
+            const u64 c02 = pack2(c0, c0), c12 = pack2(c1, c1);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const u64 o = pack2(xch[(r * 18 + 2 + 2 * i) * PT + lt], xch[(r * 18 + 3 + 2 * i) * PT + lt]);
+                acc[r][i] = fma2(o, c12, mul2(acc[r][i], c02));
+            }
+        }
+    }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
         const float inv = 1.f / l[r];
@@ -375,35 +465,36 @@ __global__ void __launch_bounds__(128) fwd_tiled_kernel(TileArgs a, const __grid
             store_centre<CPE>(a.o0, g, u, h, w0, active, r, i, x * inv, y * inv);
         }
         if (a.ostats && active && w0 + r < g.W)
-            a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = (m[r] + log2f(l[r])) * kLn2;
+            a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = (log2f(l[r]) - nm[r]) * kLn2;
     }
 }
 
 // =====================================================================
-// Backward, query-owned: dq
+// Backward, query-owned: dq.  The s chain starts at -L (log2 domain) and the
+// dP chain at -D, so P = 2^chain and dS = P * chain'.
 // =====================================================================
 template <bool DIST, int MASK>
-__device__ __forceinline__ void dq_stage(const float* kb, const float* vb, int lr, int ws, float sl2,
-                                         const u64 (&q)[4][8], const u64 (&dy)[4][8], u64 (&dq)[4][8],
-                                         const float (&L2)[4], const float (&D)[4], const float (&bq)[4],
-                                         float (&sumds)[4]) {
+__device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[4][8],
+                                         const u64 (&dy)[4][8], u64 (&dq)[4][8], const u64 (&nL2)[4],
+                                         const u64 (&nD2)[4], const float (&bq)[4], float (&sumds)[4]) {
 #pragma unroll 1
     for (int di = 0; di < ws; ++di) {
+        const uint32_t a0 = rowbase + di * kRowBytes;
         float dp[4];
         {
             u64 v2[8];
-            lds_vec16(vb, lr + di, v2);
+            lds_vec16(a0, 1, v2);
 #pragma unroll
             for (int r = 0; r < 4; ++r)
-                if (MASK & (1 << r)) {
-                    u64 t = 0ull;
+                if (CA_ON(r)) {
+                    u64 t = nD2[r];                               // (-D, 0)
 #pragma unroll
                     for (int i = 0; i < 8; ++i) t = fma2(dy[r][i], v2[i], t);
                     dp[r] = hsum2(t);
                 }
         }
         u64 k2[8];
-        lds_vec16(kb, lr + di, k2);
+        lds_vec16(a0, 0, k2);
         float bk = 0.f;
         if (DIST) {
             u64 n = 0ull;
@@ -413,13 +504,12 @@ __device__ __forceinline__ void dq_stage(const float* kb, const float* vb, int l
         }
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-            if (MASK & (1 << r)) {
-                u64 t = 0ull;
+            if (CA_ON(r)) {
+                u64 t = nL2[r];                                   // (-L, 0), log2 domain
+                if (DIST) t = add2(t, pack2(bq[r] + bk, 0.f));
 #pragma unroll
                 for (int i = 0; i < 8; ++i) t = fma2(q[r][i], k2[i], t);
-                const float s2 = hsum2(t) + (DIST ? bq[r] + bk : 0.f);
-                const float P = fast_exp2(s2 - L2[r]);
-                const float ds = P * (dp[r] - D[r]);
+                const float ds = fast_exp2(hsum2(t)) * dp[r];
                 if (DIST) sumds[r] += ds;
                 const u64 d2 = pack2(ds, ds);
 #pragma unroll
@@ -429,27 +519,28 @@ __device__ __forceinline__ void dq_stage(const float* kb, const float* vb, int l
 }
 
 template <bool DIST, int CPE>
-__global__ void __launch_bounds__(128) dq_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap m0,
-                                                       const __grid_constant__ CUtensorMap m1,
-                                                       const __grid_constant__ CUtensorMap msc) {
+__global__ void __launch_bounds__(128, 2) dq_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+                                                          const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
+    const int NS = g.ws + 3;
     const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
-    const int lr = threadIdx.x, h = h0 + lr;
-    const bool active = h < g.H;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
+    const int lr = lt, h = h0 + lr;
+    const bool active = h < g.H;
 
     u64 q[4][8], dy[4][8], dq[4][8];
-    load_centre<CPE>(a.c0, g, u, h, w0, active, sl2, q);
-    load_centre<CPE>(a.c1, g, u, h, w0, active, 1.f, dy);
-    float L2[4], D[4], bq[4], sumds[4];
+    load_centre<CPE, 4>(a.c0, g, u, h, w0, active, sl2, q);
+    load_centre<CPE, 4>(a.c1, g, u, h, w0, active, 1.f, dy);
+    u64 nL2[4], nD2[4];
+    float bq[4], sumds[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
         const bool ok = active && (w0 + r < g.W);
         const int64_t o = (int64_t)u * g.Np + h + g.H * (w0 + r);
-        L2[r] = ok ? __ldg(a.cs0 + o) * kLog2e : 0.f;
-        D[r] = ok ? __ldg(a.cs1 + o) : 0.f;
+        nL2[r] = pack2(ok ? -__ldg(a.cs0 + o) * kLog2e : 0.f, 0.f);
+        nD2[r] = pack2(ok ? -__ldg(a.cs1 + o) : 0.f, 0.f);
         sumds[r] = 0.f;
         bq[r] = 0.f;
         if (DIST) {
@@ -463,11 +554,36 @@ __global__ void __launch_bounds__(128) dq_tiled_kernel(TileArgs a, const __grid_
     }
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask(s, g.p);
-        const float* kb = pipe.vec0(buf);
-        const float* vb = pipe.vec1(buf);
-        CA_MASK_SWITCH(mask, (dq_stage<DIST, MK>(kb, vb, lr + a.roff, g.ws, sl2, q, dy, dq, L2, D, bq, sumds)));
+        const int mask = stage_mask<4>(s, g.p);
+        CA_MASK_SWITCH(15, mask, (dq_stage<DIST, MK>(smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes, g.ws, mask,
+                                                     sl2, q, dy, dq, nL2, nD2, bq, sumds)));
     })
+
+    if (a.nsplit == 2) {
+        float* xch = reinterpret_cast<float*>(smem_al);
+        if (part == 1) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                xch[(r * 17 + 16) * PT + lt] = sumds[r];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float x, y;
+                    unpack2(dq[r][i], x, y);
+                    xch[(r * 17 + 2 * i) * PT + lt] = x;
+                    xch[(r * 17 + 2 * i + 1) * PT + lt] = y;
+                }
+            }
+        }
+        __syncthreads();
+        if (part == 1) return;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            sumds[r] += xch[(r * 17 + 16) * PT + lt];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                dq[r][i] = add2(dq[r][i], pack2(xch[(r * 17 + 2 * i) * PT + lt], xch[(r * 17 + 2 * i + 1) * PT + lt]));
+        }
+    }
     // dq = scale * (sum ds*k - [distance] sum(ds) * q);  q registers hold q*scale*log2(e)
 #pragma unroll
     for (int r = 0; r < 4; ++r)
@@ -483,49 +599,50 @@ __global__ void __launch_bounds__(128) dq_tiled_kernel(TileArgs a, const __grid_
 }
 
 // =====================================================================
-// Backward, key-owned: dk and dv.  Two lanes share a row: lane&1 selects the
-// channel half; partial dot products are completed with one shuffle.
+// Backward, key-owned: dk and dv of three key pixels per thread.  The stage
+// rows carry (q | dy) of the query pixels plus their L and D.
 // =====================================================================
 template <bool DIST, int MASK>
-__device__ __forceinline__ void dkdv_stage(const float* qb, const float* dyb, const float* Lb, const float* Db,
-                                           int lr, int half, int ws, float sl2, const u64 (&k)[4][4],
-                                           const u64 (&v)[4][4], u64 (&dk)[4][4], u64 (&dv)[4][4],
-                                           const float (&bk)[4], float (&sumds)[4]) {
+__device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const float* Db, int row0, int ws, int rm,
+                                           float sl2, const u64 (&k)[3][8], const u64 (&v)[3][8], u64 (&dk)[3][8],
+                                           u64 (&dv)[3][8], const float (&bk)[3], float (&sumds)[3]) {
 #pragma unroll 1
     for (int di = 0; di < ws; ++di) {
-        const int row = lr + di;
-        u64 q2[4], y2[4];
-        lds_vec8(qb, row, half, q2);
-        lds_vec8(dyb, row, half, y2);
-        const float Lj = Lb[row], Dj = Db[row];
+        const int row = row0 + di;
+        const uint32_t a0 = base + row * kRowBytes;
+        const float nLj = -Lb[row], nDj = -Db[row];
+        u64 y2[8];
+        lds_vec16(a0, 1, y2);
+        float dp[3];
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+            if (CA_ON(r)) {
+                u64 t = pack2(nDj, 0.f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t = fma2(v[r][i], y2[i], t);
+                dp[r] = hsum2(t);
+            }
+        u64 q2[8];
+        lds_vec16(a0, 0, q2);
         float bqj = 0.f;
         if (DIST) {
             u64 n = 0ull;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) n = fma2(q2[i], q2[i], n);
-            float t = hsum2(n);
-            t += __shfl_xor_sync(0xffffffffu, t, 1);
-            bqj = -0.5f * sl2 * t;
+            for (int i = 0; i < 8; ++i) n = fma2(q2[i], q2[i], n);
+            bqj = -0.5f * sl2 * hsum2(n);
         }
 #pragma unroll
-        for (int r = 0; r < 4; ++r)
-            if (MASK & (1 << r)) {
-                u64 t = 0ull, w = 0ull;
+        for (int r = 0; r < 3; ++r)
+            if (CA_ON(r)) {
+                u64 t = pack2(DIST ? nLj + bk[r] + bqj : nLj, 0.f);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    t = fma2(k[r][i], q2[i], t);
-                    w = fma2(v[r][i], y2[i], w);
-                }
-                float s2 = hsum2(t), dp = hsum2(w);
-                s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
-                dp += __shfl_xor_sync(0xffffffffu, dp, 1);
-                if (DIST) s2 += bk[r] + bqj;
-                const float P = fast_exp2(s2 - Lj);
-                const float ds = P * (dp - Dj);
+                for (int i = 0; i < 8; ++i) t = fma2(k[r][i], q2[i], t);
+                const float P = fast_exp2(hsum2(t));
+                const float ds = P * dp[r];
                 if (DIST) sumds[r] += ds;
                 const u64 d2 = pack2(ds, ds), p2 = pack2(P, P);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < 8; ++i) {
                     dk[r][i] = fma2(d2, q2[i], dk[r][i]);
                     dv[r][i] = fma2(p2, y2[i], dv[r][i]);
                 }
@@ -534,100 +651,103 @@ __device__ __forceinline__ void dkdv_stage(const float* qb, const float* dyb, co
 }
 
 template <bool DIST, int CPE>
-__global__ void __launch_bounds__(256) dkdv_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap m0,
-                                                         const __grid_constant__ CUtensorMap m1,
-                                                         const __grid_constant__ CUtensorMap msc) {
+__global__ void __launch_bounds__(128, 2) dkdv_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+                                                            const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
-    const int lr = threadIdx.x >> 1, half = threadIdx.x & 1, h = h0 + lr;
-    const bool active = h < g.H;
+    const int NS = g.ws + 2;
+    const int w0 = blockIdx.x * 3, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(true)
+    const int lr = lt, h = h0 + lr;
+    const bool active = h < g.H;
 
-    u64 k[4][4], v[4][4], dk[4][4], dv[4][4];
-    float bk[4], sumds[4];
+    u64 k[3][8], v[3][8], dk[3][8], dv[3][8];
+    load_centre<CPE, 3>(a.c0, g, u, h, w0, active, sl2, k);
+    load_centre<CPE, 3>(a.c1, g, u, h, w0, active, 1.f, v);
+    float bk[3], sumds[3];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        const bool ok = active && (w0 + r < g.W);
-        const int pix = h + g.H * (w0 + r);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float kx = 0.f, ky = 0.f, vx = 0.f, vy = 0.f;
-            if (ok) {
-                const int cc = 8 * half + 2 * i;
-                if (CPE == 1) {
-                    kx = __ldg(a.c0 + goff<1>(u, cc, g.Np, pix));
-                    ky = __ldg(a.c0 + goff<1>(u, cc + 1, g.Np, pix));
-                    vx = __ldg(a.c1 + goff<1>(u, cc, g.Np, pix));
-                    vy = __ldg(a.c1 + goff<1>(u, cc + 1, g.Np, pix));
-                } else {
-                    const float2 tk = __ldg(reinterpret_cast<const float2*>(a.c0 + goff<2>(u, cc, g.Np, pix)));
-                    const float2 tv = __ldg(reinterpret_cast<const float2*>(a.c1 + goff<2>(u, cc, g.Np, pix)));
-                    kx = tk.x; ky = tk.y; vx = tv.x; vy = tv.y;
-                }
-            }
-            k[r][i] = pack2(kx * sl2, ky * sl2);
-            v[r][i] = pack2(vx, vy);
-            dk[r][i] = 0ull;
-            dv[r][i] = 0ull;
-        }
+    for (int r = 0; r < 3; ++r) {
         sumds[r] = 0.f;
         bk[r] = 0.f;
         if (DIST) {
             u64 n = 0ull;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) n = fma2(k[r][i], k[r][i], n);
-            float t = hsum2(n);
-            t += __shfl_xor_sync(0xffffffffu, t, 1);
-            bk[r] = -0.5f * t / sl2;
+            for (int i = 0; i < 8; ++i) n = fma2(k[r][i], k[r][i], n);
+            bk[r] = -0.5f * hsum2(n) / sl2;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            dk[r][i] = 0ull;
+            dv[r][i] = 0ull;
         }
     }
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask(s, g.p);
-        CA_MASK_SWITCH(mask, (dkdv_stage<DIST, MK>(pipe.vec0(buf), pipe.vec1(buf), pipe.sc0(buf), pipe.sc1(buf),
-                                                   lr + a.roff, half, g.ws, sl2, k, v, dk, dv, bk, sumds)));
+        const int mask = stage_mask<3>(s, g.p);
+        CA_MASK_SWITCH(7, mask, (dkdv_stage<DIST, MK>(smem_u32(pipe.vec(buf)), pipe.sc0(buf), pipe.sc1(buf),
+                                                      lr + a.roff, g.ws, mask, sl2, k, v, dk, dv, bk, sumds)));
     })
+
+    if (a.nsplit == 2) {
+        float* xch = reinterpret_cast<float*>(smem_al);
+        if (part == 1) {
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                xch[(r * 33 + 32) * PT + lt] = sumds[r];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float x, y;
+                    unpack2(dk[r][i], x, y);
+                    xch[(r * 33 + 2 * i) * PT + lt] = x;
+                    xch[(r * 33 + 2 * i + 1) * PT + lt] = y;
+                    unpack2(dv[r][i], x, y);
+                    xch[(r * 33 + 16 + 2 * i) * PT + lt] = x;
+                    xch[(r * 33 + 17 + 2 * i) * PT + lt] = y;
+                }
+            }
+        }
+        __syncthreads();
+        if (part == 1) return;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            sumds[r] += xch[(r * 33 + 32) * PT + lt];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                dk[r][i] = add2(dk[r][i], pack2(xch[(r * 33 + 2 * i) * PT + lt], xch[(r * 33 + 2 * i + 1) * PT + lt]));
+                dv[r][i] = add2(dv[r][i], pack2(xch[(r * 33 + 16 + 2 * i) * PT + lt], xch[(r * 33 + 17 + 2 * i) * PT + lt]));
+            }
+        }
+    }
     // dk = scale * (sum ds*q - [distance] sum(ds) * k);  k registers hold k*scale*log2(e)
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        if (!(active && (w0 + r < g.W))) continue;
-        const int pix = h + g.H * (w0 + r);
+    for (int r = 0; r < 3; ++r)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 8; ++i) {
             float x, y, kx, ky, vx, vy;
             unpack2(dk[r][i], x, y);
             unpack2(k[r][i], kx, ky);
             unpack2(dv[r][i], vx, vy);
             x = a.scale * x - (DIST ? sumds[r] * kx * kLn2 : 0.f);
             y = a.scale * y - (DIST ? sumds[r] * ky * kLn2 : 0.f);
-            const int cc = 8 * half + 2 * i;
-            if (CPE == 1) {
-                a.o0[goff<1>(u, cc, g.Np, pix)] = x;
-                a.o0[goff<1>(u, cc + 1, g.Np, pix)] = y;
-                a.o1[goff<1>(u, cc, g.Np, pix)] = vx;
-                a.o1[goff<1>(u, cc + 1, g.Np, pix)] = vy;
-            } else {
-                *reinterpret_cast<float2*>(a.o0 + goff<2>(u, cc, g.Np, pix)) = make_float2(x, y);
-                *reinterpret_cast<float2*>(a.o1 + goff<2>(u, cc, g.Np, pix)) = make_float2(vx, vy);
-            }
+            store_centre<CPE>(a.o0, g, u, h, w0, active, r, i, x, y);
+            store_centre<CPE>(a.o1, g, u, h, w0, active, r, i, vx, vy);
         }
-    }
 }
 
 // =====================================================================
-// Pack kernel: reference layout -> [unit][column][row'][16] with the circular
-// halo along h unrolled, plus (optionally) the two scalar planes
-// [2*unit + {0: stats*log2(e), 1: D}][column][row'].  One thread per (row', column, unit).
+// Pack kernel: two tensors in the reference layout -> [unit][column][row'][32]
+// with the circular halo along h unrolled, plus (optionally) the two scalar
+// planes [2*unit + {0: stats*log2(e), 1: D}][column][row'].
+// One thread per (row', column, unit, tensor pair).
 // =====================================================================
 struct PackArgs {
     Geo g;
     int pp;                 // p' (even)
     int Hp;                 // padded rows per column: roundup4(H + 2p')
-    int nt;                 // number of tensors to pack (<= 4)
-    const float* src[4];
-    float* dst[4];
+    int npairs;             // 1 or 2 tensor pairs
+    const float* src[4];    // pair j = (src[2j], src[2j+1])
+    float* dst[2];
     float* planes;          // nullable
     const float* stats;     // with planes
     const float* Din;       // with planes: D given ...
@@ -640,17 +760,22 @@ template <int CPE>
 __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
     const Geo& g = a.g;
     const int rr = blockIdx.x * blockDim.x + threadIdx.x;
-    const int w = blockIdx.y, u = blockIdx.z;
+    const int w = blockIdx.y;
+    const int u = blockIdx.z / a.npairs, pair = blockIdx.z % a.npairs;
     if (rr >= a.Hp) return;
     const bool real_row = rr < g.H + 2 * a.pp;
     const int hs = real_row ? (rr - a.pp + g.H) % g.H : 0;
     const int pix = hs + g.H * w;
     const int64_t orow = ((int64_t)u * g.Wk + w) * a.Hp + rr;
-    for (int t = 0; t < a.nt; ++t) {
+    float4* dp = reinterpret_cast<float4*>(a.dst[pair] + orow * kRowFloats);
+    dp[8] = make_float4(0.f, 0.f, 0.f, 0.f);                     // padding
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const float* src = a.src[2 * pair + t];
         float4 c[4];
         if (real_row) {
             if (CPE == 1) {
-                const float* sp = a.src[t] + goff<1>(u, 0, g.Npk, pix);
+                const float* sp = src + goff<1>(u, 0, g.Npk, pix);
                 float v[16];
 #pragma unroll
                 for (int cc = 0; cc < 16; ++cc) v[cc] = __ldg(sp + (int64_t)cc * g.Npk);
@@ -659,8 +784,8 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
             } else {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float2 lo = __ldg(reinterpret_cast<const float2*>(a.src[t] + goff<2>(u, 4 * i, g.Npk, pix)));
-                    const float2 hi = __ldg(reinterpret_cast<const float2*>(a.src[t] + goff<2>(u, 4 * i + 2, g.Npk, pix)));
+                    const float2 lo = __ldg(reinterpret_cast<const float2*>(src + goff<2>(u, 4 * i, g.Npk, pix)));
+                    const float2 hi = __ldg(reinterpret_cast<const float2*>(src + goff<2>(u, 4 * i + 2, g.Npk, pix)));
                     c[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
                 }
             }
@@ -668,11 +793,10 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) c[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        float4* dp = reinterpret_cast<float4*>(a.dst[t] + orow * 16);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) dp[i] = c[i];
+        for (int i = 0; i < 4; ++i) dp[4 * t + i] = c[i];
     }
-    if (a.planes) {
+    if (a.planes && pair == a.npairs - 1) {
         float L = 0.f, D = 0.f;
         if (real_row) {
             const int64_t so = (int64_t)u * g.Npk + pix;
@@ -697,7 +821,7 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
 // ---------------------------------------------------------------- host side
 struct Padded {
     int pp, Hp;
-    size_t tensor_floats;   // one packed tensor
+    size_t pair_floats;     // one packed tensor pair
     size_t plane_floats;    // both scalar planes
 };
 
@@ -705,7 +829,7 @@ Padded padded_of(const Geo& g) {
     Padded P;
     P.pp = (g.p + 1) & ~1;
     P.Hp = (g.H + 2 * P.pp + 3) & ~3;
-    P.tensor_floats = (size_t)g.units * g.Wk * P.Hp * 16;
+    P.pair_floats = (size_t)g.units * g.Wk * P.Hp * kRowFloats;
     P.plane_floats = (size_t)2 * g.units * g.Wk * P.Hp;
     return P;
 }
@@ -714,10 +838,9 @@ bool tiled_shape_ok(const Geo& g) {
     return g.cr == 16 && g.wsw == g.ws && g.ws >= 3 && g.H >= 16 && g.ws <= 63;
 }
 
-int pick_rows(const Geo& g, int rows_per_warp, int max_warps) {
-    int warps = (g.H + rows_per_warp - 1) / rows_per_warp;
-    if (warps > max_warps) warps = max_warps;
-    return warps;
+int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
 }
 
 int pick_dc(int ws) {
@@ -730,7 +853,7 @@ int pick_dc(int ws) {
 }
 
 int launch_pack(const PackArgs& a, cudaStream_t st) {
-    dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units);
+    dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * a.npairs);
     if (a.g.cpe == 1) pack_kernel<1><<<grid, 128, 0, st>>>(a);
     else pack_kernel<2><<<grid, 128, 0, st>>>(a);
     CA_CHECK_LAUNCH("pack kernel");
@@ -739,41 +862,66 @@ int launch_pack(const PackArgs& a, cudaStream_t st) {
 
 struct Launch {
     TileArgs a;
-    CUtensorMap m0, m1, msc;
+    CUtensorMap mv, msc;
     dim3 grid;
     int threads;
     size_t smem;
 };
 
-// Fills the launch geometry and the tensor maps of the packed tensors t0, t1
-// (and the scalar planes when given).
-int prepare(const Geo& g, const Padded& P, int rows_per_warp, int max_warps, const float* t0, const float* t1,
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
+// Fills the launch geometry and the tensor maps of the packed pair (and of the
+// scalar planes when given).  `nq` centre pixels per thread, `xch_floats` per
+// thread for the merge of a split tile.  CTAs have at most 128 threads: four
+// warps of rows, or two warps of rows times two stage groups on small grids.
+int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* env_warps, const float* pair,
             const float* planes, Launch* L) {
-    const int warps = pick_rows(g, rows_per_warp, max_warps);
+    int warps = (g.H + 31) / 32;
+    if (warps > 4) warps = 4;
+    const long cols = (g.W + nq - 1) / nq;
+    const long ctas4 = cols * ((g.H + 32 * warps - 1) / (32 * warps)) * g.units;
+    int nsplit = (ctas4 * warps < 8L * sm_count()) ? 2 : 1;
+    nsplit = env_int("CIRCATT_SPLIT", nsplit);
+    if (nsplit == 2 && warps > 2) warps = 2;
+    warps = env_int(env_warps, warps);
+    if (warps * nsplit > 4) warps = 4 / nsplit;
     TileArgs& a = L->a;
     a.g = g;
-    a.TH = rows_per_warp * warps;
+    a.TH = 32 * warps;
     a.roff = P.pp - g.p;
+    a.nsplit = nsplit;
     const int ROWS = a.TH + 2 * P.pp;
     if (ROWS > 256) { set_error("tile of %d rows exceeds the TMA box limit", ROWS); return CA_ERR_UNSUPPORTED; }
-    const int vstride = (ROWS * 64 + 511) & ~511, sstride = (ROWS * 4 + 127) & ~127;
-    a.stage_bytes = (2 * vstride + (planes ? 2 * sstride : 0) + 1023) & ~1023;
-    L->smem = (size_t)kStages * a.stage_bytes + 1024;
-    L->grid = dim3((g.W + 3) / 4, (g.H + a.TH - 1) / a.TH, g.units);
-    L->threads = 32 * warps;
-    const uint64_t dims[4] = {16, (uint64_t)P.Hp, (uint64_t)g.Wk, (uint64_t)g.units};
-    const uint64_t strides[3] = {64, (uint64_t)P.Hp * 64, (uint64_t)P.Hp * 64 * g.Wk};
-    const uint32_t box[4] = {16, (uint32_t)ROWS, 1, 1};
+    const int sstride = (ROWS * 4 + 127) & ~127;
+    const int vbytes = (ROWS * kRowBytes + 127) & ~127;
+    a.stage_bytes = (vbytes + (planes ? 2 * sstride : 0) + 1023) & ~1023;
+    L->grid = dim3((unsigned)cols, (g.H + a.TH - 1) / a.TH, g.units);
+    L->threads = 32 * warps * nsplit;
+    size_t smem = (size_t)nsplit * kStages * a.stage_bytes;
+    const size_t xch = (size_t)xch_floats * 32 * warps * sizeof(float);
+    if (nsplit == 2 && xch > smem) smem = xch;
+    L->smem = smem + 1024;
+    const uint64_t dims[4] = {(uint64_t)kRowFloats, (uint64_t)P.Hp, (uint64_t)g.Wk, (uint64_t)g.units};
+    const uint64_t strides[3] = {(uint64_t)kRowBytes, (uint64_t)P.Hp * kRowBytes, (uint64_t)P.Hp * kRowBytes * g.Wk};
+    const uint32_t box[4] = {(uint32_t)kRowFloats, (uint32_t)ROWS, 1, 1};
     int rc;
-    if ((rc = encode_tensor_map(&L->m0, t0, 4, dims, strides, box, true))) return rc;
-    if ((rc = encode_tensor_map(&L->m1, t1, 4, dims, strides, box, true))) return rc;
+    if ((rc = encode_tensor_map(&L->mv, pair, 4, dims, strides, box, false))) return rc;
     if (planes) {
         const uint64_t sdims[3] = {(uint64_t)P.Hp, (uint64_t)g.Wk, (uint64_t)2 * g.units};
         const uint64_t sstr[2] = {(uint64_t)P.Hp * 4, (uint64_t)P.Hp * 4 * g.Wk};
         const uint32_t sbox[3] = {(uint32_t)ROWS, 1, 1};
         if ((rc = encode_tensor_map(&L->msc, planes, 3, sdims, sstr, sbox, false))) return rc;
     } else {
-        L->msc = L->m0;
+        L->msc = L->mv;
     }
     return CA_OK;
 }
@@ -787,29 +935,51 @@ int set_smem(K kernel, size_t bytes) {
     return CA_OK;
 }
 
-#define CA_LAUNCH_TILED(KERNEL, L, st)                                                        \
-    do {                                                                                      \
-        int rc__ = set_smem(KERNEL, (L).smem);                                                \
-        if (rc__) return rc__;                                                                \
-        KERNEL<<<(L).grid, (L).threads, (L).smem, st>>>((L).a, (L).m0, (L).m1, (L).msc);      \
+#define CA_LAUNCH_TILED(KERNEL, L, st)                                                \
+    do {                                                                              \
+        int rc__ = set_smem(KERNEL, (L).smem);                                        \
+        if (rc__) return rc__;                                                        \
+        KERNEL<<<(L).grid, (L).threads, (L).smem, st>>>((L).a, (L).mv, (L).msc);      \
     } while (0)
 
-#define CA_DIST_CPE(KERNEL_T, dist, cpe, L, st)                                               \
-    do {                                                                                      \
-        if ((cpe) == 1) {                                                                     \
-            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 1>), L, st);                            \
-            else CA_LAUNCH_TILED((KERNEL_T<false, 1>), L, st);                                \
-        } else {                                                                              \
-            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 2>), L, st);                            \
-            else CA_LAUNCH_TILED((KERNEL_T<false, 2>), L, st);                                \
-        }                                                                                     \
+#define CA_DIST_CPE(KERNEL_T, dist, cpe, L, st)                                       \
+    do {                                                                              \
+        if ((cpe) == 1) {                                                             \
+            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 1>), L, st);                    \
+            else CA_LAUNCH_TILED((KERNEL_T<false, 1>), L, st);                        \
+        } else {                                                                      \
+            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 2>), L, st);                    \
+            else CA_LAUNCH_TILED((KERNEL_T<false, 2>), L, st);                        \
+        }                                                                             \
     } while (0)
+
+int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q, const float* dy, const float* stats,
+           const float* D, const float* kv, float* dq, cudaStream_t st) {
+    Launch L{};
+    int rc = prepare(g, P, 4, 68, "CIRCATT_DQ_WARPS", kv, nullptr, &L);
+    if (rc) return rc;
+    L.a.scale = scale; L.a.c0 = q; L.a.c1 = dy; L.a.cs0 = stats; L.a.cs1 = D; L.a.o0 = dq;
+    CA_DIST_CPE(dq_tiled_kernel, dist, g.cpe, L, st);
+    CA_CHECK_LAUNCH("tiled dq kernel");
+    return CA_OK;
+}
+
+int run_dkdv(const Geo& g, const Padded& P, float scale, int dist, const float* k, const float* v, const float* qdy,
+             const float* planes, float* dk, float* dv, cudaStream_t st) {
+    Launch L{};
+    int rc = prepare(g, P, 3, 99, "CIRCATT_DKDV_WARPS", qdy, planes, &L);
+    if (rc) return rc;
+    L.a.scale = scale; L.a.c0 = k; L.a.c1 = v; L.a.o0 = dk; L.a.o1 = dv;
+    CA_DIST_CPE(dkdv_tiled_kernel, dist, g.cpe, L, st);
+    CA_CHECK_LAUNCH("tiled dk/dv kernel");
+    return CA_OK;
+}
 
 }  // namespace
 
 // ---------------------------------------------------------------- tensor maps
 int encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle64) {
+                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -830,7 +1000,7 @@ int encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint6
     for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), gdims, gstr,
                     gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -842,19 +1012,19 @@ int encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint6
 // ---------------------------------------------------------------- entry points of this file
 size_t tiled_fwd_workspace(const Geo& g) {
     if (!tiled_shape_ok(g)) return 0;
-    return 2 * padded_of(g).tensor_floats * sizeof(float) + 256;
+    return padded_of(g).pair_floats * sizeof(float);
 }
 
 size_t tiled_bwd_stage_workspace(const Geo& g) {
     if (!tiled_shape_ok(g)) return 0;
     const Padded P = padded_of(g);
-    return (2 * P.tensor_floats + P.plane_floats) * sizeof(float) + 256;
+    return (P.pair_floats + P.plane_floats) * sizeof(float);
 }
 
 size_t tiled_bwd_workspace(const Geo& g) {
     if (!tiled_shape_ok(g)) return 0;
     const Padded P = padded_of(g);
-    return (4 * P.tensor_floats + P.plane_floats) * sizeof(float) + 256;
+    return (2 * P.pair_floats + P.plane_floats) * sizeof(float);
 }
 
 int tiled_stage_timeouts(int* count) {
@@ -868,26 +1038,25 @@ int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, con
     if (!tiled_shape_ok(g) || nz) return CA_ERR_UNSUPPORTED;
     if (!workspace) { set_error("workspace of ca_attention_fwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
     const Padded P = padded_of(g);
-    float* kT = static_cast<float*>(workspace);
-    float* vT = kT + P.tensor_floats;
+    float* kv = static_cast<float*>(workspace);
     PackArgs pa{};
-    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.nt = 2;
-    pa.src[0] = k; pa.src[1] = v; pa.dst[0] = kT; pa.dst[1] = vT;
+    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1;
+    pa.src[0] = k; pa.src[1] = v; pa.dst[0] = kv;
     int rc = launch_pack(pa, st);
     if (rc) return rc;
     Launch L{};
-    if ((rc = prepare(g, P, 32, 4, kT, vT, nullptr, &L))) return rc;
+    if ((rc = prepare(g, P, 4, 72, "CIRCATT_FWD_WARPS", kv, nullptr, &L))) return rc;
     L.a.scale = scale; L.a.c0 = q; L.a.o0 = y; L.a.ostats = stats;
     const int dc = pick_dc(g.ws);
-#define CA_FWD(DCV)                                                                              \
-    do {                                                                                         \
-        if (g.cpe == 1) {                                                                        \
-            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 1>), L, st);                  \
-            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 1>), L, st);                      \
-        } else {                                                                                 \
-            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 2>), L, st);                  \
-            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 2>), L, st);                      \
-        }                                                                                        \
+#define CA_FWD(DCV)                                                                      \
+    do {                                                                                 \
+        if (g.cpe == 1) {                                                                \
+            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 1>), L, st);          \
+            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 1>), L, st);              \
+        } else {                                                                         \
+            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 2>), L, st);          \
+            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 2>), L, st);              \
+        }                                                                                \
     } while (0)
     switch (dc) {
         case 3: CA_FWD(3); break;
@@ -900,43 +1069,19 @@ int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, con
     return CA_OK;
 }
 
-static int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q, const float* dy,
-                  const float* stats, const float* D, const float* kT, const float* vT, float* dq, cudaStream_t st) {
-    Launch L{};
-    int rc = prepare(g, P, 32, 4, kT, vT, nullptr, &L);
-    if (rc) return rc;
-    L.a.scale = scale; L.a.c0 = q; L.a.c1 = dy; L.a.cs0 = stats; L.a.cs1 = D; L.a.o0 = dq;
-    CA_DIST_CPE(dq_tiled_kernel, dist, g.cpe, L, st);
-    CA_CHECK_LAUNCH("tiled dq kernel");
-    return CA_OK;
-}
-
-static int run_dkdv(const Geo& g, const Padded& P, float scale, int dist, const float* k, const float* v,
-                    const float* qT, const float* dyT, const float* planes, float* dk, float* dv,
-                    cudaStream_t st) {
-    Launch L{};
-    int rc = prepare(g, P, 16, 8, qT, dyT, planes, &L);
-    if (rc) return rc;
-    L.a.scale = scale; L.a.c0 = k; L.a.c1 = v; L.a.o0 = dk; L.a.o1 = dv;
-    CA_DIST_CPE(dkdv_tiled_kernel, dist, g.cpe, L, st);
-    CA_CHECK_LAUNCH("tiled dk/dv kernel");
-    return CA_OK;
-}
-
 int tiled_attention_bwd_dq(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                            const float* dy, const float* stats, const float* D, float* dq, void* workspace,
                            cudaStream_t st) {
     if (!tiled_shape_ok(g)) return CA_ERR_UNSUPPORTED;
     if (!workspace) { set_error("workspace of ca_attention_bwd_stage_workspace() bytes is NULL"); return CA_ERR_NULL; }
     const Padded P = padded_of(g);
-    float* kT = static_cast<float*>(workspace);
-    float* vT = kT + P.tensor_floats;
+    float* kv = static_cast<float*>(workspace);
     PackArgs pa{};
-    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.nt = 2;
-    pa.src[0] = k; pa.src[1] = v; pa.dst[0] = kT; pa.dst[1] = vT;
+    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1;
+    pa.src[0] = k; pa.src[1] = v; pa.dst[0] = kv;
     int rc = launch_pack(pa, st);
     if (rc) return rc;
-    return run_dq(g, P, scale, dist, q, dy, stats, D, kT, vT, dq, st);
+    return run_dq(g, P, scale, dist, q, dy, stats, D, kv, dq, st);
 }
 
 int tiled_attention_bwd_dkdv(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
@@ -945,39 +1090,36 @@ int tiled_attention_bwd_dkdv(const Geo& g, float scale, int dist, const float* q
     if (!tiled_shape_ok(g)) return CA_ERR_UNSUPPORTED;
     if (!workspace) { set_error("workspace of ca_attention_bwd_stage_workspace() bytes is NULL"); return CA_ERR_NULL; }
     const Padded P = padded_of(g);
-    float* qT = static_cast<float*>(workspace);
-    float* dyT = qT + P.tensor_floats;
-    float* planes = dyT + P.tensor_floats;
+    float* qdy = static_cast<float*>(workspace);
+    float* planes = qdy + P.pair_floats;
     PackArgs pa{};
-    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.nt = 2;
-    pa.src[0] = q; pa.src[1] = dy; pa.dst[0] = qT; pa.dst[1] = dyT;
+    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1;
+    pa.src[0] = q; pa.src[1] = dy; pa.dst[0] = qdy;
     pa.planes = planes; pa.stats = stats; pa.Din = D;
     int rc = launch_pack(pa, st);
     if (rc) return rc;
-    return run_dkdv(g, P, scale, dist, k, v, qT, dyT, planes, dk, dv, st);
+    return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st);
 }
 
-// Whole backward in three launches: pack (all four tensors, D, planes), dq, dk/dv.
+// Whole backward in three launches: pack (both pairs, D, planes), dq, dk/dv.
 int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                         const float* y, const float* dy, const float* stats, float* D, float* dq, float* dk,
                         float* dv, void* workspace, cudaStream_t st) {
     if (!tiled_shape_ok(g) || g.Wk != g.W) return CA_ERR_UNSUPPORTED;
     if (!workspace) { set_error("workspace is NULL"); return CA_ERR_NULL; }
     const Padded P = padded_of(g);
-    float* kT = static_cast<float*>(workspace);
-    float* vT = kT + P.tensor_floats;
-    float* qT = vT + P.tensor_floats;
-    float* dyT = qT + P.tensor_floats;
-    float* planes = dyT + P.tensor_floats;
+    float* kv = static_cast<float*>(workspace);
+    float* qdy = kv + P.pair_floats;
+    float* planes = qdy + P.pair_floats;
     PackArgs pa{};
-    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.nt = 4;
+    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 2;
     pa.src[0] = k; pa.src[1] = v; pa.src[2] = q; pa.src[3] = dy;
-    pa.dst[0] = kT; pa.dst[1] = vT; pa.dst[2] = qT; pa.dst[3] = dyT;
+    pa.dst[0] = kv; pa.dst[1] = qdy;
     pa.planes = planes; pa.stats = stats; pa.y = y; pa.dy = dy; pa.Dout = D;
     int rc = launch_pack(pa, st);
     if (rc) return rc;
-    if ((rc = run_dq(g, P, scale, dist, q, dy, stats, D, kT, vT, dq, st))) return rc;
-    return run_dkdv(g, P, scale, dist, k, v, qT, dyT, planes, dk, dv, st);
+    if ((rc = run_dq(g, P, scale, dist, q, dy, stats, D, kv, dq, st))) return rc;
+    return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st);
 }
 
 int tiled_apply(const Geo&, const float*, const float*, float*, cudaStream_t) { return CA_ERR_UNSUPPORTED; }

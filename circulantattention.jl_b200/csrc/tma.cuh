@@ -64,6 +64,6 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
 // Encodes a tiled FP32 tensor map; `dims` innermost first, `strides_bytes` for
 // dims 1..rank-1.  Returns CA_OK or CA_ERR_CUDA with the error text set.
 int encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle64);
+                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
 
 }  // namespace ca
