@@ -54,6 +54,8 @@ PROTOTYPES = {
     "ca_apply": (C.c_int, [_D, _p, _p, _p, _i32, _i32, _i32, _p]),
     "ca_attention_fwd_workspace": (C.c_size_t, [_D, _i32]),
     "ca_attention_fwd": (C.c_int, [_D, _p, _p, _p, _p, _p, _p, _p, _p]),
+    "ca_static_scratch_bytes": (C.c_size_t, []),
+    "ca_attention_fwd_static": (C.c_int, [_D, _p, _p, _p, _p, _p, _p, _p]),
     "ca_attention_bwd_workspace": (C.c_size_t, [_D]),
     "ca_attention_bwd": (C.c_int, [_D] + [_p] * 13),
     "ca_attention_bwd_pre": (C.c_int, [_D] + [_p] * 10),

@@ -126,6 +126,22 @@ size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz);
 int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void* v,
                      void* y, float* nz, float* stats, void* workspace, void* stream);
 
+/* The same forward for callers that cannot allocate device memory (code that
+ * runs inside somebody else's memory pool, fixed-budget real-time loops,
+ * plugins that only ever receive pointers).  It has no counterpart in the
+ * reference.  The workspace is a fixed array of ca_static_scratch_bytes()
+ * (64 MiB) inside the library's device image: every GPU that loads the library
+ * holds it until the process exits.  Problems whose workspace
+ * (ca_attention_fwd_workspace) is larger are rejected with CA_ERR_TOO_LARGE.
+ * All calls on a GPU share that array and it keeps the last call's contents,
+ * so calls that overlap on the GPU race with each other; nothing in it needs
+ * clearing between calls.  The first call on each device resolves the array's
+ * address on the host; make it before beginning any stream capture.  The call
+ * performs no cudaMalloc / cudaFree and calls no allocating library routine. */
+size_t ca_static_scratch_bytes(void);
+int ca_attention_fwd_static(const ca_desc* d, const void* q, const void* k, const void* v,
+                            void* y, float* nz, float* stats, void* stream);
+
 /* Gradient of the above (the composition of the reference's rrules for
  * similarity, softmax and apply: src/rrules.jl:1-72).  `dA` (nullable) is the
  * cotangent arriving on the returned A (CSR order); when it is given, `nz`
