@@ -267,3 +267,52 @@ def sum_cols(nz, spatial, ws):
     with torch.cuda.device(nz.device):
         check(lib.ca_sum_cols(m.desc(), ptr(nz), ptr(out), _stream()))
     return out
+
+
+# ------------------------------------------------------------------ backward stages (band split)
+def _stage_ws(d, device):
+    n = lib.ca_attention_bwd_stage_workspace(d)
+    return torch.empty(max(n, 16), dtype=torch.uint8, device=device) if n else None
+
+
+def attention_bwd_pre(kind, normalizer, q, k, v, y, dy, stats, ws, scale=None):
+    """D of ca_attention_bwd_pre for band-local tensors (no A cotangent)."""
+    q, k, v, y, dy = (_dense_ok(t) for t in (q, k, v, y, dy))
+    m = meta_of(q, ws)
+    scale = 1.0 / math.sqrt(m.channels) if scale is None else scale
+    d = m.desc(similarity=kind, normalizer=normalizer, scale=scale)
+    D = jl.empty((m.Np, m.units), torch.float32, q.device)
+    with torch.cuda.device(q.device):
+        check(lib.ca_attention_bwd_pre(d, ptr(q), ptr(k), ptr(v), ptr(y), ptr(dy), ptr(stats), None, None, ptr(D),
+                                       _stream()))
+    return D
+
+
+def attention_bwd_dq(kind, normalizer, q, k, v, dy, stats, D, ws, scale=None, band=None):
+    """dq stage; in band mode k, v carry Wk = W + 2p columns."""
+    q, k, v, dy = (_dense_ok(t) for t in (q, k, v, dy))
+    m = meta_of(q, ws)
+    scale = 1.0 / math.sqrt(m.channels) if scale is None else scale
+    Wk, wk_off = band if band else (0, 0)
+    d = m.desc(similarity=kind, normalizer=normalizer, scale=scale, Wk=Wk, wk_off=wk_off)
+    dq = jl.empty(q.shape, q.dtype, q.device)
+    wsb = _stage_ws(d, q.device)
+    with torch.cuda.device(q.device):
+        check(lib.ca_attention_bwd_dq(d, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(stats), ptr(D), None, ptr(dq),
+                                      ptr(wsb), _stream()))
+    return dq
+
+
+def attention_bwd_dkdv(kind, normalizer, q, k, v, dy, stats, D, ws, scale=None, band=None):
+    """dk/dv stage; in band mode q, dy, stats, D carry Wk = W + 2p columns and k, v are band-local."""
+    q, k, v, dy = (_dense_ok(t) for t in (q, k, v, dy))
+    m = meta_of(k, ws)
+    scale = 1.0 / math.sqrt(m.channels) if scale is None else scale
+    Wk, wk_off = band if band else (0, 0)
+    d = m.desc(similarity=kind, normalizer=normalizer, scale=scale, Wk=Wk, wk_off=wk_off)
+    dk, dv = jl.empty(k.shape, k.dtype, k.device), jl.empty(k.shape, k.dtype, k.device)
+    wsb = _stage_ws(d, k.device)
+    with torch.cuda.device(k.device):
+        check(lib.ca_attention_bwd_dkdv(d, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(stats), ptr(D), None, ptr(dk),
+                                        ptr(dv), ptr(wsb), _stream()))
+    return dk, dv

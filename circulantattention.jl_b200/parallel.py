@@ -1,1 +1,149 @@
-"""Multi-GPU plumbing (filled in below)."""
+"""Multi-GPU plumbing: one process per GPU, `torch.distributed` for the only
+exchange the path has.
+
+Two ways to shard, neither of which exists in the reference (it is a
+single-device package):
+
+* batch x head units are independent in every kernel, so `shard_units` hands
+  each rank a contiguous range of units and nothing is communicated;
+* for images too large for one GPU the slow spatial axis W is cut into bands
+  (`BandPlan`).  A rank then needs `p = (ws-1)/2` columns of the key-side
+  tensors from its two neighbours `r-1` and `r+1` (mod R: the modulo is the
+  circular wrap of the window); `exchange_halo` does that with point-to-point
+  sends (NCCL over NVLink on GPUs, gloo on CPU ranks) into the rank's own halo
+  buffer, and the kernels run in band mode on the extended slab.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import jl, ops
+
+
+def shard_units(units: int, world: int, rank: int) -> Tuple[int, int]:
+    """(first unit, number of units) of `rank`: contiguous, the first `units % world`
+    ranks hold one more; ranks beyond `units` hold none."""
+    if units < 0 or world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad sharding request: units={units} world={world} rank={rank}")
+    base, extra = divmod(units, world)
+    count = base + (1 if rank < extra else 0)
+    start = rank * base + min(rank, extra)
+    return start, count
+
+
+def take_units(x: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """The shard of a head-split (spatial..., c, units) tensor that `rank` owns: a view,
+    because a unit is a contiguous block of the column-major array."""
+    start, count = shard_units(x.shape[-1], world, rank)
+    return x.narrow(x.ndim - 1, start, count)
+
+
+@dataclass(frozen=True)
+class BandPlan:
+    """Bands of columns of a (H, W, ...) image over `world` ranks for window `ws`."""
+    W: int
+    world: int
+    ws: int
+
+    def __post_init__(self):
+        if self.ws % 2 != 1:
+            raise AssertionError(f"filter size M={self.ws} must be odd.")
+        if self.world < 1:
+            raise ValueError("world must be positive")
+        if min(self.widths()) < max(self.p, 1):
+            raise ValueError(f"a band of {min(self.widths())} columns is narrower than the halo ({self.p}): "
+                             f"W={self.W} cannot be split over {self.world} ranks for window {self.ws}")
+
+    @property
+    def p(self) -> int:
+        return (self.ws - 1) // 2
+
+    def widths(self) -> List[int]:
+        return [shard_units(self.W, self.world, r)[1] for r in range(self.world)]
+
+    def band(self, rank: int) -> Tuple[int, int]:
+        """(first column, number of columns) of `rank`."""
+        return shard_units(self.W, self.world, rank)
+
+    def neighbours(self, rank: int) -> Tuple[int, int]:
+        """(left, right) = ranks holding the columns before / after this band, circularly."""
+        return (rank - 1) % self.world, (rank + 1) % self.world
+
+    def take(self, x: torch.Tensor, rank: int) -> torch.Tensor:
+        """Band of a (H, W, ...) tensor (column-major copy)."""
+        start, width = self.band(rank)
+        return jl.colmajor(x.narrow(1, start, width).clone())
+
+
+def _cview(x: torch.Tensor) -> torch.Tensor:
+    """C-contiguous view (..., W, H) of a column-major (H, W, ...) tensor."""
+    x = jl.colmajor(x)
+    return x.permute(tuple(range(x.ndim - 1, -1, -1)))
+
+
+def exchange_halo(x: torch.Tensor, p: int, group=None) -> torch.Tensor:
+    """Extended slab (H, Wb + 2p, ...) of the band-local (H, Wb, ...) tensor: `p` columns
+    from the left neighbour, the band, `p` columns from the right neighbour.  Without an
+    initialised process group (or world size 1) the band is the whole image and the halos are
+    its own wrapped columns."""
+    if x.ndim < 2:
+        raise ValueError("expected a (H, W, ...) tensor")
+    Wb = x.shape[1]
+    if p < 1 or Wb < p:
+        raise ValueError(f"band of {Wb} columns cannot supply a halo of {p}")
+    t = _cview(x)                                            # (..., Wb, H)
+    ext = torch.empty(t.shape[:-2] + (Wb + 2 * p, t.shape[-1]), dtype=t.dtype, device=t.device)
+    ext.narrow(-2, p, Wb).copy_(t)
+    left_halo, right_halo = ext.narrow(-2, 0, p), ext.narrow(-2, p + Wb, p)
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    if world == 1:
+        left_halo.copy_(t.narrow(-2, Wb - p, p))
+        right_halo.copy_(t.narrow(-2, 0, p))
+    else:
+        rank = dist.get_rank(group)
+        left, right = (rank - 1) % world, (rank + 1) % world
+        to_right = t.narrow(-2, Wb - p, p).contiguous()      # becomes the right neighbour's left halo
+        to_left = t.narrow(-2, 0, p).contiguous()            # becomes the left neighbour's right halo
+        from_left, from_right = torch.empty_like(to_right), torch.empty_like(to_left)
+        peer = lambda r: dist.get_global_rank(group, r) if group is not None else r
+        reqs = dist.batch_isend_irecv([
+            dist.P2POp(dist.isend, to_right, peer(right), group, tag=0),
+            dist.P2POp(dist.isend, to_left, peer(left), group, tag=1),
+            dist.P2POp(dist.irecv, from_left, peer(left), group, tag=0),
+            dist.P2POp(dist.irecv, from_right, peer(right), group, tag=1),
+        ])
+        for r in reqs:
+            r.wait()
+        left_halo.copy_(from_left)
+        right_halo.copy_(from_right)
+    return ext.permute(tuple(range(ext.ndim - 1, -1, -1)))
+
+
+def band_attention_fwd(kind, q, k, v, ws, group=None, normalizer=0):
+    """Forward on this rank's band of head-split (H, Wb, c, units) tensors.
+    Returns (y, stats, k_ext, v_ext); the extended slabs are reused by the backward."""
+    p = (ws - 1) // 2
+    k_ext, v_ext = exchange_halo(k, p, group), exchange_halo(v, p, group)
+    y, _, stats = ops.attention_fwd(kind, normalizer, q, k_ext, v_ext, ws, False, band=(k_ext.shape[1], p))
+    return y, stats, k_ext, v_ext
+
+
+def band_attention_bwd(kind, q, k, v, y, dy, stats, k_ext, v_ext, ws, group=None, normalizer=0):
+    """Backward on this rank's band.  One more exchange: q, dy, stats and D of the
+    neighbouring columns feed the key-owned dk/dv sweep."""
+    p = (ws - 1) // 2
+    Wb = q.shape[1]
+    D = ops.attention_bwd_pre(kind, normalizer, q, k, v, y, dy, stats, ws)
+    dq = ops.attention_bwd_dq(kind, normalizer, q, k_ext, v_ext, dy, stats, D, ws, band=(Wb + 2 * p, p))
+    H, units = q.shape[0], q.shape[-1]
+    q_ext, dy_ext = exchange_halo(q, p, group), exchange_halo(dy, p, group)
+    stats_ext = exchange_halo(jl.reshape(stats, (H, Wb, units)), p, group)
+    D_ext = exchange_halo(jl.reshape(D, (H, Wb, units)), p, group)
+    dk, dv = ops.attention_bwd_dkdv(kind, normalizer, q_ext, k, v, dy_ext,
+                                    jl.reshape(stats_ext, (H * (Wb + 2 * p), units)),
+                                    jl.reshape(D_ext, (H * (Wb + 2 * p), units)), ws, band=(Wb + 2 * p, p))
+    return dq, dk, dv
