@@ -1,5 +1,5 @@
 // TMA (cp.async.bulk.tensor) and mbarrier helpers for sm_100a, plus the host
-// side tensor-map encoder.  No multicast anywhere: every load is CTA-local.
+// side tensor-map encoder.  Every load is issued by and delivered to one CTA.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>

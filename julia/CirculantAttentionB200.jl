@@ -1,0 +1,298 @@
+# CirculantAttentionB200.jl -- drop-in host module for CirculantAttention.jl whose device
+# work is done by libcircatt_b200.so (C ABI: include/circatt_b200.h) instead of CUDA.jl
+# kernels, cuSPARSE and NNlib.
+#
+# STATUS: written without a Julia toolchain (none exists where this library is built), so it
+# has never been parsed or run.  It documents the binding precisely; the Python package next
+# to it is the binding that is tested.  Names, signatures and assertion messages follow the
+# reference (file:line citations are to CirculantAttention.jl v1.0.1).
+module CirculantAttentionB200
+
+const CircAtt = CirculantAttentionB200
+export CircAtt
+export Circulant, circulant
+export circulant_similarity, circulant_similarity!, DotSimilarity, DistanceSimilarity
+export circulant_adjacency, circulant_adjacency!
+export circulant_attention, circulant_mh_attention, circulant_mh_adjacency, ⊗, ⨷
+
+using CUDA, CUDA.CUSPARSE
+using LinearAlgebra
+using NNlib
+import ChainRulesCore as CRC
+import Zygote
+
+const LIB = get(ENV, "CIRCATT_B200_LIB", "libcircatt_b200")
+
+# ------------------------------------------------------------------ C ABI plumbing
+struct CaDesc                                   # ca_desc, include/circatt_b200.h
+    H::Int32; W::Int32; ndim::Int32; channels::Int32; units::Int32; ws::Int32
+    dtype::Int32; similarity::Int32; normalizer::Int32; Wk::Int32; wk_off::Int32; scale::Float32
+end
+
+abstract type AbstractSimilarity end
+struct DotSimilarity <: AbstractSimilarity end          # src/similarity.jl:15
+struct DistanceSimilarity <: AbstractSimilarity end     # src/similarity.jl:29
+simcode(::DotSimilarity) = Int32(0)
+simcode(::DistanceSimilarity) = Int32(1)
+
+lasterror() = unsafe_string(ccall((:ca_last_error, LIB), Cstring, ()))
+check(rc::Integer) = rc == 0 ? nothing : throw(ErrorException("circatt_b200 status $rc: $(lasterror())"))
+stream() = CUDA.stream().handle
+
+function desc(x::AnyCuArray{T,N}, ws::Integer; sim=Int32(0), norm=Int32(0), scale=1f0, units=size(x, N)) where {T,N}
+    sp = size(x)[1:N-2]
+    CaDesc(sp[1], N == 4 ? sp[2] : 1, N - 2, size(x, N - 1), units, ws,
+           T <: Complex ? Int32(1) : Int32(0), sim, norm, 0, 0, Float32(scale))
+end
+nzdesc(spatial::NTuple{S,Int}, ws, units; norm=Int32(0)) where S =
+    CaDesc(spatial[1], S == 2 ? spatial[2] : 1, S, 1, units, ws, 0, 0, norm, 0, 0, 1f0)
+
+# ------------------------------------------------------------------ Circulant (src/array.jl:1-64)
+struct Circulant{T, N, M, S, A<:AbstractArray{T, N}} <: AbstractArray{T, N}
+    data::A
+    kernel_length::Int
+    spatial_size::NTuple{S, Int}
+    Circulant(D::A, M::Int, spatsize::NTuple{S,Int}) where {T, N, S, A<:AbstractArray{T,N}} =
+        new{T, N, M, S, A}(D, M, spatsize)
+end
+
+# structure: one ccall instead of two kernels, three broadcasts and a repeat
+# (src/circulant.jl:64-106, src/array.jl:6-11); shared between Circulants of equal shape.
+const STRUCTURES = Dict{Any, Any}()
+function structure(M::Int, spatsize::NTuple{S,Int}, batchsize::Tuple) where S
+    @assert M % 2 == 1 "filter size M=$M must be odd."
+    get!(STRUCTURES, (M, spatsize, batchsize, CUDA.device())) do
+        Np, K = prod(spatsize), M^S
+        rowptr = CuArray{Int32}(undef, Np + 1, batchsize...)
+        colval = CuArray{Int32}(undef, Np * K, batchsize...)
+        check(ccall((:ca_structure, LIB), Cint,
+                    (Int32, Int32, Int32, Int32, Int64, CuPtr{Int32}, CuPtr{Int32}, Ptr{Cvoid}),
+                    spatsize[1], S == 2 ? spatsize[2] : 1, S, M, prod(batchsize), rowptr, colval, stream()))
+        (rowptr, colval)
+    end
+end
+
+function Circulant{T}(M::Int, dims::NTuple{N,Int}; nzval=nothing) where {T,N}
+    spatsize, batchsize = dims[1:N-2], dims[N-1:end]
+    Np, K = prod(spatsize), M^length(spatsize)
+    rowptr, colval = structure(M, spatsize, batchsize)
+    nz = nzval === nothing ? CUDA.ones(T, Np * K, batchsize...) : nzval
+    Circulant(CuSparseArrayCSR(rowptr, colval, nz, (Np, Np, batchsize...)), M, spatsize)
+end
+Circulant(M::Int, dims::NTuple{N,Int}) where N = Circulant{Float32}(M, dims)
+Circulant(A::Circulant) = A
+circulant(M::Int, x::AnyCuArray{T,N}) where {T,N} = Circulant{real(T)}(M, (size(x)[1:N-2]..., 1, size(x, N)))
+
+kernel_length(::Circulant{T,N,M}) where {T,N,M} = M
+spatial_dims(::Circulant{T,N,M,S}) where {T,N,M,S} = S
+spatial_size(A::Circulant) = A.spatial_size
+nzval(A::Circulant) = A.data.nzVal
+withnz(A::Circulant{T,N,M}, nz) where {T,N,M} =
+    Circulant(CuSparseArrayCSR(A.data.rowPtr, A.data.colVal, nz, size(A)), M, spatial_size(A))   # structure shared
+
+Base.eltype(::Circulant{T}) where T = T
+Base.size(A::Circulant) = size(A.data)
+Base.size(A::Circulant, i::Int) = size(A.data, i)
+Base.ndims(A::Circulant) = ndims(A.data)
+Base.getindex(A::Circulant, idxs...) = getindex(A.data, idxs...)
+Base.similar(A::Circulant) = withnz(A, similar(nzval(A)))
+Base.copy(A::Circulant) = withnz(A, copy(nzval(A)))
+CUDA.unsafe_free!(A::Circulant) = CUDA.unsafe_free!(nzval(A))
+function Base.show(io::IOContext, m::MIME"text/plain", A::Circulant{T,N,M}) where {T,N,M}
+    print(io, typeof(A), " with kernel-length $M, spatial-size $(spatial_size(A)), and data,\n")
+    show(io, m, A.data)
+end
+
+function Base.reshape(A::Circulant{T,N,M}, dims::Union{Colon,Int}...) where {T,N,M}
+    nz = reshape(nzval(A), size(nzval(A), 1), dims[3:end]...)
+    Circulant{T}(M, (spatial_size(A)..., size(nz)[2:end]...); nzval=nz)
+end
+_circulant_reshape(A::Circulant, dims...) = reshape(A, dims...)
+Base.repeat(A::Circulant{T,N,M}, dims::Int...) where {T,N,M} =
+    (nz = repeat(nzval(A), 1, dims[3:end]...); Circulant{T}(M, (spatial_size(A)..., size(nz)[2:end]...); nzval=nz))
+function Base.cat(As::Circulant{T,N,M}...; dims=3) where {T,N,M}      # works, unlike src/array.jl:62-64
+    nz = cat((nzval(A) for A in As)...; dims=dims - 1)
+    Circulant{T}(M, (spatial_size(As[1])..., size(nz)[2:end]...); nzval=nz)
+end
+
+# ------------------------------------------------------------------ similarity / normaliser (src/similarity.jl)
+function circulant_similarity!(A::Circulant, simfun::AbstractSimilarity, x::AnyCuArray{Tx,N}, y) where {Tx,N}
+    S = spatial_dims(A)
+    @assert S == N - 2 "spatial_dims ($(S)) of circulant matrix must match those of data signal ($(N-2))."
+    nb = prod(size(A)[3:end])
+    @assert nb == size(x, N) "batchdim of circulant matrix ($nb) must match that of x, y ($(size(x,N)))."
+    d = desc(x, kernel_length(A); sim=simcode(simfun))
+    check(ccall((:ca_similarity, LIB), Cint, (Ref{CaDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Float32}, Ptr{Cvoid}),
+                d, x, y, nzval(A), stream()))
+    return A
+end
+
+function circulant_similarity(simfun::AbstractSimilarity, x::AbstractArray{T,N}, y::AbstractArray{T,N}, W::Integer) where {T,N}
+    S = Circulant(Int(W), (size(x)[1:N-2]..., 1, size(x, N)))
+    circulant_similarity!(S, simfun, x, y)
+end
+
+function rownormalize!(Y::Circulant, X::Circulant, norm::Int32)
+    d = nzdesc(spatial_size(X), kernel_length(X), prod(size(X)[3:end]); norm=norm)
+    check(ccall((:ca_row_normalize, LIB), Cint, (Ref{CaDesc}, CuPtr{Float32}, CuPtr{Float32}, CuPtr{Float32}, Ptr{Cvoid}),
+                d, nzval(X), nzval(Y), CU_NULL, stream()))
+    return Y
+end
+NNlib.softmax!(A::Circulant{T,N,M}, B::Circulant{T,N,M}=A) where {T,N,M} = rownormalize!(A, B, Int32(0))
+NNlib.softmax(A::Circulant) = rownormalize!(similar(A), A, Int32(0))
+entmax15(A::Circulant) = rownormalize!(similar(A), A, Int32(1))           # not in the reference
+
+circulant_adjacency!(A::Circulant, simfun, x, y) = NNlib.softmax!(circulant_similarity!(A, simfun, x, y))
+circulant_adjacency(simfun::AbstractSimilarity, x, y, W::Integer) = NNlib.softmax(circulant_similarity(simfun, x, y, W))
+
+# ------------------------------------------------------------------ apply (src/attention.jl:53-103, src/batchedmul.jl)
+function apply!(y::AbstractArray{T,N}, A::Circulant, x::AbstractArray{T,N}, transpose::Bool) where {T,N}
+    @assert spatial_dims(A) == N - 2 "spatial-dims ($(spatial_dims(A)) of A must match spatial dims of x ($(N-2))"
+    ua, ux = prod(size(A)[3:end]), size(x, N)
+    units = max(ua, ux)
+    d = desc(x, kernel_length(A); units=units)
+    check(ccall((:ca_apply, LIB), Cint,
+                (Ref{CaDesc}, CuPtr{Float32}, CuPtr{Cvoid}, CuPtr{Cvoid}, Int32, Int32, Int32, Ptr{Cvoid}),
+                d, nzval(A), x, y, transpose, ua == 1 && units > 1, ux == 1 && units > 1, stream()))
+    return y
+end
+circulant_attention!(y, A::Circulant, x) = apply!(y, A, x, false)
+circulant_attention(A::Circulant, x) = circulant_attention!(similar(x), A, x)
+circulant_transposed_attention!(y, A::Circulant, x) = apply!(y, A, x, true)
+circulant_transposed_attention(A::Circulant, x) = circulant_transposed_attention!(similar(x), A, x)
+const ⊗ = circulant_attention
+
+splitheads(x::AbstractArray{T,N}, nheads) where {T,N} =
+    reshape(x, ntuple(i -> size(x, i), N - 2)..., size(x, N - 1) ÷ nheads, :)          # src/attention.jl:44
+
+function circulant_mh_attention(A::Circulant{Ta,4}, x::AbstractArray{T,N}) where {Ta,T,N}
+    reshape(A ⊗ splitheads(x, size(A, 3)), size(x)...)
+end
+const ⨷ = circulant_mh_attention
+circulant_mh_transposed_attention(A::Circulant{Ta,4}, x) where Ta =
+    reshape(circulant_transposed_attention(A, splitheads(x, size(A, 3))), size(x)...)
+
+function circulant_mh_adjacency(simfun, x::AbstractArray{T,N}, y, W::Integer, nheads::Int) where {T,N}
+    A = circulant_adjacency(simfun, splitheads(x, nheads), splitheads(y, nheads), W)
+    _circulant_reshape(A, :, :, nheads, size(x, N))
+end
+
+# ------------------------------------------------------------------ fused attention (src/attention.jl:19-44)
+function fused_forward(simfun, q::T, k::T, v::T, W::Int, nheads::Int, return_A::Bool) where {Tv,N,T<:AnyCuArray{Tv,N}}
+    @assert W % 2 == 1 "filter size M=$W must be odd."
+    qr, kr, vr = splitheads.((q, k, v), nheads)
+    d = desc(qr, W; sim=simcode(simfun), scale=1f0 / sqrt(Float32(size(kr, N - 1))))
+    y = similar(qr)
+    Np = prod(size(q)[1:N-2])
+    A = return_A ? Circulant(W, (size(q)[1:N-2]..., nheads, size(q, N))) : nothing
+    stats = CuArray{Float32}(undef, Np, size(qr, N))
+    wsz = ccall((:ca_attention_fwd_workspace, LIB), Csize_t, (Ref{CaDesc}, Int32), d, return_A)
+    work = CuVector{UInt8}(undef, max(wsz, 1))
+    check(ccall((:ca_attention_fwd, LIB), Cint,
+                (Ref{CaDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Float32}, CuPtr{Float32},
+                 CuPtr{Cvoid}, Ptr{Cvoid}),
+                d, qr, kr, vr, y, return_A ? nzval(A) : CU_NULL, stats, work, stream()))
+    return reshape(y, size(q)...), A, stats
+end
+
+function fused_backward(simfun, q::T, k::T, v::T, y, dy, stats, A, dA, W::Int, nheads::Int) where {Tv,N,T<:AnyCuArray{Tv,N}}
+    qr, kr, vr, yr, dyr = splitheads.((q, k, v, y, dy), nheads)
+    d = desc(qr, W; sim=simcode(simfun), scale=1f0 / sqrt(Float32(size(kr, N - 1))))
+    dq, dk, dv = similar(qr), similar(kr), similar(vr)
+    work = CuVector{UInt8}(undef, ccall((:ca_attention_bwd_workspace, LIB), Csize_t, (Ref{CaDesc},), d))
+    check(ccall((:ca_attention_bwd, LIB), Cint,
+                (Ref{CaDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Float32},
+                 CuPtr{Float32}, CuPtr{Float32}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, Ptr{Cvoid}),
+                d, qr, kr, vr, yr, dyr, stats, dA === nothing ? CU_NULL : nzval(A),
+                dA === nothing ? CU_NULL : nzval(dA), dq, dk, dv, work, stream()))
+    return reshape(dq, size(q)...), reshape(dk, size(k)...), reshape(dv, size(v)...)
+end
+
+function circulant_attention(simfun::AbstractSimilarity, q::T, k::T, v::T, W::Int) where {Tv,N,T<:AbstractArray{Tv,N}}
+    y, A, _ = fused_forward(simfun, q, k, v, W, 1, true)
+    return y, A
+end
+circulant_attention(q::T, k::T, v::T, W::Int) where T = circulant_attention(DotSimilarity(), q, k, v, W)
+
+# simfun is honoured (src/attention.jl:40 drops it) and the 5-argument form works (:43 does not).
+function circulant_mh_attention(simfun::AbstractSimilarity, q::T, k::T, v::T, W::Int, nheads::Int) where {Tv,N,T<:AbstractArray{Tv,N}}
+    y, A, _ = fused_forward(simfun, q, k, v, W, nheads, true)
+    return y, A
+end
+circulant_mh_attention(q::T, k::T, v::T, W::Int, nheads::Int) where T =
+    circulant_mh_attention(DotSimilarity(), q, k, v, W, nheads)
+
+# direct pullbacks = the composition of src/rrules.jl:1-72
+for (f, extra) in ((:circulant_attention, ()), (:circulant_mh_attention, (:nheads,)))
+    @eval function CRC.rrule(::typeof($f), simfun::AbstractSimilarity, q, k, v, W::Int, $(extra...))
+        nh = $(isempty(extra) ? 1 : :nheads)
+        y, A, stats = fused_forward(simfun, q, k, v, W, nh, true)
+        function attention_pullback(Δ)
+            dy, dA = CRC.unthunk(Δ[1]), CRC.unthunk(Δ[2])
+            dy = dy isa CRC.AbstractZero ? zero(y) : dy
+            dA = dA isa Circulant ? dA : nothing
+            dq, dk, dv = fused_backward(simfun, q, k, v, y, dy, stats, A, dA, W, nh)
+            return (CRC.NoTangent(), CRC.NoTangent(), dq, dk, dv, CRC.NoTangent(), $(map(_ -> :(CRC.NoTangent()), extra)...))
+        end
+        return (y, A), attention_pullback
+    end
+end
+
+# ------------------------------------------------------------------ algebra and sums (src/array.jl:66-189)
+function axpby(α, X::Circulant, β, Y::Union{Circulant,Nothing})
+    out = similar(nzval(X))
+    check(ccall((:ca_axpby, LIB), Cint, (Int64, Float32, CuPtr{Float32}, Float32, CuPtr{Float32}, CuPtr{Float32}, Ptr{Cvoid}),
+                length(out), α, nzval(X), β, Y === nothing ? CU_NULL : nzval(Y), out, stream()))
+    withnz(X, out)
+end
+Base.:(+)(X::Circulant, Y::Circulant) = axpby(1f0, X, 1f0, Y)
+Base.:(-)(X::Circulant, Y::Circulant) = axpby(1f0, X, -1f0, Y)
+Base.:(*)(c::Number, X::Circulant) = axpby(Float32(c), X, 0f0, nothing)
+Base.:(*)(X::Circulant, c::Number) = c * X
+Base.:(-)(X::Circulant) = -1 * X
+Zygote.accum(x::T, y::T) where T <: Circulant = x === nothing ? y : y === nothing ? x : x + y   # src/zygote.jl
+
+b12(t::Tuple) = (Int32(get(t, 1, 1)), Int32(get(t, 2, 1)))
+function scale(c::CuArray{Tc,N}, A::Circulant{Ta,N,M}) where {Tc,Ta,N,M}
+    @assert size(c, 1) == 1 && size(c, 2) == 1 "Scaling of non-batchdims of CuSparseArrayCSR not implemented"
+    (a1, a2), (c1, c2) = b12(size(A)[3:end]), b12(size(c)[3:end])
+    o1, o2 = max(a1, c1), max(a2, c2)
+    inner = size(nzval(A), 1)
+    out = CuArray{Float32}(undef, inner, (o1, o2)[1:N-2]...)
+    check(ccall((:ca_scale_batch, LIB), Cint,
+                (Int64, Int32, Int32, CuPtr{Float32}, Int32, Int32, CuPtr{Float32}, Int32, Int32, CuPtr{Float32}, Ptr{Cvoid}),
+                inner, o1, o2, nzval(A), a1, a2, c, c1, c2, out, stream()))
+    Circulant{Float32}(M, (spatial_size(A)..., size(out)[2:end]...); nzval=out)
+end
+Base.:(*)(c::CuArray, A::Circulant) = scale(c, A)
+Base.Broadcast.broadcasted(::typeof(*), c::CuArray, A::Circulant) = scale(c, A)      # `m .* A`
+
+function Base.sum(A::Circulant; dims=:)
+    nz = nzval(A)
+    Np, units = size(A, 1), prod(size(A)[3:end])
+    d = nzdesc(spatial_size(A), kernel_length(A), units)
+    if dims == 1 || dims == 2
+        out = CuArray{Float32}(undef, (dims == 1 ? (1, Np) : (Np, 1))..., size(A)[3:end]...)
+        f = dims == 1 ? :ca_sum_cols : :ca_sum_rows
+        check(ccall((f, LIB), Cint, (Ref{CaDesc}, CuPtr{Float32}, CuPtr{Float32}, Ptr{Cvoid}), d, nz, out, stream()))
+        return out
+    elseif dims != Colon() && all(dims .> 2)
+        b1, b2 = b12(size(A)[3:end])
+        s1, s2 = 3 in dims, 4 in dims
+        out = CuArray{Float32}(undef, size(nz, 1), (s1 ? 1 : b1, s2 ? 1 : b2)[1:ndims(A)-2]...)
+        check(ccall((:ca_sum_batch, LIB), Cint, (Int64, Int32, Int32, Int32, Int32, CuPtr{Float32}, CuPtr{Float32}, Ptr{Cvoid}),
+                    size(nz, 1), b1, b2, s1, s2, nz, out, stream()))
+        return Circulant{Float32}(kernel_length(A), (spatial_size(A)..., size(out)[2:end]...); nzval=out)
+    elseif dims == (1, 2) || dims == Colon()
+        b1, b2 = dims == Colon() ? (Int32(1), Int32(1)) : b12(size(A)[3:end])
+        inner = dims == Colon() ? length(nz) : size(nz, 1)
+        out = CuArray{Float32}(undef, b1, b2)
+        check(ccall((:ca_dot_batch, LIB), Cint,
+                    (Int64, Int32, Int32, CuPtr{Float32}, Int32, Int32, CuPtr{Float32}, Int32, Int32, CuPtr{Float32}, Ptr{Cvoid}),
+                    inner, b1, b2, nz, b1, b2, CU_NULL, 1, 1, out, stream()))
+        return dims == Colon() ? CUDA.@allowscalar(out[1]) : reshape(out, 1, 1, size(A)[3:end]...)
+    end
+    throw(ErrorException("dims=$dims not implemented."))
+end
+
+end # module
