@@ -94,6 +94,10 @@ struct TileArgs {
 
 constexpr int kStages = 3;
 
+#ifndef CA_FWD_MIN_BLOCKS
+#define CA_FWD_MIN_BLOCKS 2
+#endif
+
 // Number of CTAs that gave up waiting for a stage copy (stays 0 in a healthy run).
 __device__ int g_stage_timeouts = 0;
 
@@ -263,11 +267,15 @@ __device__ __forceinline__ void store_centre(float* dst, const Geo& g, int u, in
 // =====================================================================
 // Forward
 // =====================================================================
-// Scores are kept relative to the running maximum: the dot-product chain
-// starts at -m, so sc = s - m and p = 2^sc needs no subtraction.  The
-// maximum moves only when some relative score of the chunk is positive, which
-// the AND of the sign bits of the chunk reveals.
-template <int DC, bool DIST, int MASK>
+// Scores are kept relative to a running reference ref = (largest score seen when
+// the reference was last set) + kHeadroom: the dot-product chain starts at -ref,
+// so sc = s - ref and p = 2^sc needs no subtraction.  The reference moves only
+// when some relative score of the chunk is non-negative (a score jumped more than
+// kHeadroom log2 units above every earlier one), which the AND of the sign bits
+// of the chunk reveals; with O(1) scores that happens almost never after the
+// first key.  2^-kHeadroom only rescales p, l and acc together; it cancels in y.
+constexpr float kHeadroom = 12.f;
+template <int DC, bool DIST, int MASK, bool EXACT>
 __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[4][8],
                                           u64 (&acc)[4][8], u64 (&nm2)[4], float (&l)[4], const float (&bq)[4]) {
     for (int c0 = 0; c0 < ws; c0 += DC) {
@@ -275,7 +283,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
         float sc[4][DC];
 #pragma unroll
         for (int t = 0; t < DC; ++t) {
-            if (c0 + t < ws) {
+            if (EXACT || c0 + t < ws) {
                 u64 k2[8];
                 lds_vec16(cb + t * kRowBytes, 0, k2);
                 float bk = 0.f;
@@ -285,17 +293,33 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                     for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
                     bk = -0.5f * sl2 * hsum2(n);
                 }
+                if (MASK != 0) {
+                    // all four chains advance together (4 independent FMAs in flight)
+                    u64 sa[4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r)
-                    if (CA_ON(r)) {
-                        u64 sa = nm2[r];                          // (-m, 0)
-                        if (DIST) sa = add2(sa, pack2(bq[r] + bk, 0.f));
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) sa = fma2(q[r][i], k2[i], sa);
-                        sc[r][t] = hsum2(sa);
-                    } else {
-                        sc[r][t] = -INFINITY;
+                    for (int r = 0; r < 4; ++r) {
+                        sa[r] = nm2[r];                           // (-ref, 0)
+                        if (DIST) sa[r] = add2(sa[r], pack2(bq[r] + bk, 0.f));
                     }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) sa[r] = fma2(q[r][i], k2[i], sa[r]);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) sc[r][t] = hsum2(sa[r]);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        if (CA_ON(r)) {
+                            u64 sa = nm2[r];
+                            if (DIST) sa = add2(sa, pack2(bq[r] + bk, 0.f));
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) sa = fma2(q[r][i], k2[i], sa);
+                            sc[r][t] = hsum2(sa);
+                        } else {
+                            sc[r][t] = -INFINITY;
+                        }
+                }
             } else {
 #pragma unroll
                 for (int r = 0; r < 4; ++r) sc[r][t] = -INFINITY;
@@ -313,7 +337,8 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                 float cm = sc[r][0];
 #pragma unroll
                 for (int t = 1; t < DC; ++t) cm = fmaxf(cm, sc[r][t]);
-                if (cm > 0.f) {                 // raise the maximum of this row by cm
+                if (cm >= 0.f) {                // move the reference of this row up by cm + headroom
+                    cm += kHeadroom;
                     const float corr = fast_exp2(-cm);
                     float nm, zero;
                     unpack2(nm2[r], nm, zero);
@@ -329,7 +354,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
         }
 #pragma unroll
         for (int t = 0; t < DC; ++t) {
-            if (c0 + t < ws) {
+            if (EXACT || c0 + t < ws) {
                 u64 v2[8];
                 lds_vec16(cb + t * kRowBytes, 1, v2);
 #pragma unroll
@@ -366,7 +391,7 @@ __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float s
             u64 sa = 0ull;
 #pragma unroll
             for (int i = 0; i < 8; ++i) sa = fma2(q[r][i], k2[i], sa);
-            nm2[r] = pack2(-(hsum2(sa) + (DIST ? bq[r] + bk : 0.f)), 0.f);
+            nm2[r] = pack2(-(hsum2(sa) + (DIST ? bq[r] + bk : 0.f)) - kHeadroom, 0.f);
         }
 }
 
@@ -374,8 +399,8 @@ __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float s
     if ((mask) == (FULL)) { constexpr int MK = (FULL); CALL; }      \
     else { constexpr int MK = 0; CALL; }
 
-template <int DC, bool DIST, int CPE>
-__global__ void __launch_bounds__(128, 3) fwd_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+template <int DC, bool DIST, int CPE, bool EXACT>
+__global__ void __launch_bounds__(128, CA_FWD_MIN_BLOCKS) fwd_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                            const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
@@ -411,7 +436,7 @@ __global__ void __launch_bounds__(128, 3) fwd_tiled_kernel(TileArgs a, const __g
         // pixels whose first stage (of this part) is s
         const int init = (s == s_begin) ? mask : (mask & ~stage_mask<4>(s - 1, g.p));
         if (init) fwd_init_max<DIST>(rowbase, init, sl2, q, nm2, bq);
-        CA_MASK_SWITCH(15, mask, (fwd_stage<DC, DIST, MK>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq)));
+        CA_MASK_SWITCH(15, mask, (fwd_stage<DC, DIST, MK, EXACT>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq)));
     })
 
     float nm[4];
@@ -481,20 +506,32 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
     for (int di = 0; di < ws; ++di) {
         const uint32_t a0 = rowbase + di * kRowBytes;
         float dp[4];
+        u64 k2[8];
         {
             u64 v2[8];
             lds_vec16(a0, 1, v2);
+            lds_vec16(a0, 0, k2);
+            if (MASK != 0) {
+                u64 t[4];
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
-                if (CA_ON(r)) {
-                    u64 t = nD2[r];                               // (-D, 0)
+                for (int r = 0; r < 4; ++r) t[r] = nD2[r];        // (-D, 0)
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) t = fma2(dy[r][i], v2[i], t);
-                    dp[r] = hsum2(t);
-                }
+                for (int i = 0; i < 8; ++i)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) t[r] = fma2(dy[r][i], v2[i], t[r]);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) dp[r] = hsum2(t[r]);
+            } else {
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (CA_ON(r)) {
+                        u64 t = nD2[r];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) t = fma2(dy[r][i], v2[i], t);
+                        dp[r] = hsum2(t);
+                    }
+            }
         }
-        u64 k2[8];
-        lds_vec16(a0, 0, k2);
         float bk = 0.f;
         if (DIST) {
             u64 n = 0ull;
@@ -502,14 +539,35 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
             for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
             bk = -0.5f * sl2 * hsum2(n);
         }
+        float sv[4];
+        if (MASK != 0) {
+            u64 t[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                t[r] = nL2[r];                                    // (-L, 0), log2 domain
+                if (DIST) t[r] = add2(t[r], pack2(bq[r] + bk, 0.f));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) t[r] = fma2(q[r][i], k2[i], t[r]);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) sv[r] = hsum2(t[r]);
+        } else {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (CA_ON(r)) {
+                    u64 t = nL2[r];
+                    if (DIST) t = add2(t, pack2(bq[r] + bk, 0.f));
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) t = fma2(q[r][i], k2[i], t);
+                    sv[r] = hsum2(t);
+                }
+        }
 #pragma unroll
         for (int r = 0; r < 4; ++r)
             if (CA_ON(r)) {
-                u64 t = nL2[r];                                   // (-L, 0), log2 domain
-                if (DIST) t = add2(t, pack2(bq[r] + bk, 0.f));
-#pragma unroll
-                for (int i = 0; i < 8; ++i) t = fma2(q[r][i], k2[i], t);
-                const float ds = fast_exp2(hsum2(t)) * dp[r];
+                const float ds = fast_exp2(sv[r]) * dp[r];
                 if (DIST) sumds[r] += ds;
                 const u64 d2 = pack2(ds, ds);
 #pragma unroll
@@ -613,17 +671,31 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
         const float nLj = -Lb[row], nDj = -Db[row];
         u64 y2[8];
         lds_vec16(a0, 1, y2);
-        float dp[3];
-#pragma unroll
-        for (int r = 0; r < 3; ++r)
-            if (CA_ON(r)) {
-                u64 t = pack2(nDj, 0.f);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) t = fma2(v[r][i], y2[i], t);
-                dp[r] = hsum2(t);
-            }
         u64 q2[8];
         lds_vec16(a0, 0, q2);
+        float dp[3], sv[3];
+        {
+            // six chains (three dP, three score) advance together
+            u64 t[3], w[3];
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                t[r] = pack2(nDj, 0.f);
+                w[r] = pack2(nLj, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int r = 0; r < 3; ++r)
+                    if (CA_ON(r)) {
+                        t[r] = fma2(v[r][i], y2[i], t[r]);
+                        w[r] = fma2(k[r][i], q2[i], w[r]);
+                    }
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                dp[r] = hsum2(t[r]);
+                sv[r] = hsum2(w[r]);
+            }
+        }
         float bqj = 0.f;
         if (DIST) {
             u64 n = 0ull;
@@ -634,10 +706,7 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
 #pragma unroll
         for (int r = 0; r < 3; ++r)
             if (CA_ON(r)) {
-                u64 t = pack2(DIST ? nLj + bk[r] + bqj : nLj, 0.f);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) t = fma2(k[r][i], q2[i], t);
-                const float P = fast_exp2(hsum2(t));
+                const float P = fast_exp2(DIST ? sv[r] + bk[r] + bqj : sv[r]);
                 const float ds = P * dp[r];
                 if (DIST) sumds[r] += ds;
                 const u64 d2 = pack2(ds, ds), p2 = pack2(P, P);
@@ -1048,15 +1117,20 @@ int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, con
     if ((rc = prepare(g, P, 4, 72, "CIRCATT_FWD_WARPS", kv, nullptr, &L))) return rc;
     L.a.scale = scale; L.a.c0 = q; L.a.o0 = y; L.a.ostats = stats;
     const int dc = pick_dc(g.ws);
-#define CA_FWD(DCV)                                                                      \
+#define CA_FWD2(DCV, EX)                                                                 \
     do {                                                                                 \
         if (g.cpe == 1) {                                                                \
-            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 1>), L, st);          \
-            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 1>), L, st);              \
+            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 1, EX>), L, st);      \
+            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 1, EX>), L, st);          \
         } else {                                                                         \
-            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 2>), L, st);          \
-            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 2>), L, st);              \
+            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 2, EX>), L, st);      \
+            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 2, EX>), L, st);          \
         }                                                                                \
+    } while (0)
+#define CA_FWD(DCV)                                                                      \
+    do {                                                                                 \
+        if (g.ws % DCV == 0) CA_FWD2(DCV, true);                                         \
+        else CA_FWD2(DCV, false);                                                        \
     } while (0)
     switch (dc) {
         case 3: CA_FWD(3); break;
@@ -1064,6 +1138,7 @@ int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, con
         case 7: CA_FWD(7); break;
         default: CA_FWD(5); break;
     }
+#undef CA_FWD2
 #undef CA_FWD
     CA_CHECK_LAUNCH("tiled forward kernel");
     return CA_OK;
