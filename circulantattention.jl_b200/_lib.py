@@ -10,7 +10,7 @@ import ctypes as C
 import os
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libcircatt_b200.so")
+LIB_PATH = os.environ.get("CIRCATT_B200_LIB") or os.path.join(PKG_DIR, "libcircatt_b200.so")
 
 CA_F32, CA_C64 = 0, 1
 CA_DOT, CA_DISTANCE = 0, 1

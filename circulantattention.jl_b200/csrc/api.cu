@@ -261,7 +261,8 @@ size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {
     Geo g;
     if (make_geo(d, &g, true)) return 0;
     if (d->normalizer == CA_ENTMAX15) return want_nz ? 0 : (size_t)g.Np * g.K * g.units * sizeof(float);
-    return want_nz ? 0 : tiled_fwd_workspace(g);
+    const bool band = g.Wk != g.W;
+    return (want_nz && band) ? 0 : tiled_fwd_workspace(g);
 }
 
 int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void* v,

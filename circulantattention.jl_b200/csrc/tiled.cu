@@ -41,6 +41,7 @@
 #include "tiled.cuh"
 #include "tma.cuh"
 #include <stdlib.h>
+#include <mutex>
 
 namespace ca {
 namespace {
@@ -94,6 +95,11 @@ struct TileArgs {
 
 constexpr int kStages = 3;
 
+#ifdef CA_X_NOSYNC
+#define CA_X_SYNC(part, PT) __syncwarp()
+#else
+#define CA_X_SYNC(part, PT) part_sync(part, PT)
+#endif
 #ifndef CA_FWD_MIN_BLOCKS
 #define CA_FWD_MIN_BLOCKS 2
 #endif
@@ -208,7 +214,7 @@ struct StagePipe {
         const int buf = it % kStages;                                                                \
         if (!mbar_wait(&pipe.full[buf], (uint32_t)((it / kStages) & 1))) s_err = 1;                  \
         __VA_ARGS__                                                                                  \
-        part_sync(part, PT);                                                                         \
+        CA_X_SYNC(part, PT);                                                                         \
         if (s_err) break;                                                                            \
         if (lt == 0 && s + kStages < s_end) pipe.issue(g, s + kStages, buf);                         \
     }                                                                                                \
@@ -281,11 +287,17 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
     for (int c0 = 0; c0 < ws; c0 += DC) {
         const uint32_t cb = rowbase + c0 * kRowBytes;
         float sc[4][DC];
+        // one vector ahead: the next key (or the first v) is requested before this key's FMAs
+        u64 nxt[8];
+        lds_vec16(cb, 0, nxt);
 #pragma unroll
         for (int t = 0; t < DC; ++t) {
             if (EXACT || c0 + t < ws) {
                 u64 k2[8];
-                lds_vec16(cb + t * kRowBytes, 0, k2);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) k2[i] = nxt[i];
+                if (t + 1 < DC && (EXACT || c0 + t + 1 < ws)) lds_vec16(cb + (t + 1) * kRowBytes, 0, nxt);
+                else lds_vec16(cb, 1, nxt);
                 float bk = 0.f;
                 if (DIST) {
                     u64 n = 0ull;
@@ -331,7 +343,11 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
         for (int r = 0; r < 4; ++r)
 #pragma unroll
             for (int t = 0; t < DC; ++t) allneg &= __float_as_uint(sc[r][t]);
+#ifdef CA_X_NOVOTE
+        if (false) {
+#else
         if (__any_sync(0xffffffffu, allneg == 0u)) {
+#endif
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 float cm = sc[r][0];
@@ -356,11 +372,17 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
         for (int t = 0; t < DC; ++t) {
             if (EXACT || c0 + t < ws) {
                 u64 v2[8];
-                lds_vec16(cb + t * kRowBytes, 1, v2);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v2[i] = nxt[i];
+                if (t + 1 < DC && (EXACT || c0 + t + 1 < ws)) lds_vec16(cb + (t + 1) * kRowBytes, 1, nxt);
 #pragma unroll
                 for (int r = 0; r < 4; ++r)
                     if (CA_ON(r)) {
+#ifdef CA_X_NOEXP
+                        const float pt = sc[r][t] * 1e-3f;
+#else
                         const float pt = fast_exp2(sc[r][t]);
+#endif
                         l[r] += pt;
                         const u64 p2 = pack2(pt, pt);
 #pragma unroll
@@ -495,6 +517,102 @@ __global__ void __launch_bounds__(128, CA_FWD_MIN_BLOCKS) fwd_tiled_kernel(TileA
 }
 
 // =====================================================================
+// A in CSR order.  Second sweep over the same packed (k|v) stages: with the
+// saved log-sum-exp the normalised entry is P = 2^(q.k - L) directly.  A thread
+// produces, per stage, the ws entries of one (row, window column) run, which
+// are contiguous in the row's CSR segment; a warp stages its 32 rows x ws run
+// in shared memory and writes it out with consecutive lanes on consecutive
+// addresses, so the 4*K*heads bytes per pixel leave the SM in full sectors.
+// =====================================================================
+template <bool DIST, int CPE>
+__global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+                                                              const __grid_constant__ CUtensorMap msc) {
+    const Geo& g = a.g;
+    const int ROWS = a.TH + 2 * (g.p + a.roff);
+    const int NS = g.ws + 3;
+    const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
+    const float sl2 = a.scale * kLog2e;
+    CA_PIPE_PROLOGUE(false)
+    const int lr = lt, h = h0 + lr;
+    const bool active = h < g.H;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // per-warp staging tile [4][32][ws] after the stage buffers
+    float* tile = reinterpret_cast<float*>(smem_al + (size_t)a.nsplit * kStages * a.stage_bytes) + (size_t)warp * 128 * g.ws;
+
+    u64 q[4][8];
+    load_centre<CPE, 4>(a.c0, g, u, h, w0, active, sl2, q);
+    u64 nL2[4];
+    float bq[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const bool ok = active && (w0 + r < g.W);
+        nL2[r] = pack2(ok ? -__ldg(a.cs0 + (int64_t)u * g.Np + h + g.H * (w0 + r)) * kLog2e : 0.f, 0.f);
+        bq[r] = 0.f;
+        if (DIST) {
+            u64 n = 0ull;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) n = fma2(q[r][i], q[r][i], n);
+            bq[r] = -0.5f * hsum2(n) / sl2;
+        }
+    }
+    // position of window row offset di inside the sorted run of this thread's image row
+    const int hrot = (h < g.p) ? h - g.p + g.ws : (h >= g.H - g.p ? h - g.p - g.H + g.ws : 0);   // posh = (di + hrot) mod ws
+    const int64_t warp_row0 = (int64_t)u * g.Np + (h0 + (lr & ~31));
+
+    CA_PIPE_LOOP({
+        const int mask = stage_mask<4>(s, g.p);
+        const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes;
+#pragma unroll 1
+        for (int di = 0; di < g.ws; ++di) {
+            u64 k2[8];
+            lds_vec16(rowbase + di * kRowBytes, 0, k2);
+            float bk = 0.f;
+            if (DIST) {
+                u64 n = 0ull;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
+                bk = -0.5f * sl2 * hsum2(n);
+            }
+            int posh = di + hrot;
+            posh -= (posh >= g.ws) ? g.ws : 0;
+            u64 t[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                t[r] = nL2[r];
+                if (DIST) t[r] = add2(t[r], pack2(bq[r] + bk, 0.f));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) t[r] = fma2(q[r][i], k2[i], t[r]);
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (active) tile[(r * 32 + lane) * g.ws + posh] = fast_exp2(hsum2(t[r]));
+        }
+        __syncwarp();
+        // write the runs of this stage: row j, positions posw*ws .. posw*ws + ws - 1
+        const int rows_here = min(32, g.H - (h0 + (lr & ~31)));
+#pragma unroll 1
+        for (int r = 0; r < 4; ++r) {
+            if (!((mask >> r) & 1) || w0 + r >= g.W) continue;
+            const int posw = axis_pos(s - g.p - r, w0 + r, g.W, g.p, g.ws);
+            float* dst = a.o0 + ((warp_row0 + (int64_t)g.H * (w0 + r)) * g.K + posw * g.ws);
+            const float* src = tile + r * 32 * g.ws;
+            const int n = rows_here * g.ws;
+            int row = lane / g.ws, e = lane - row * g.ws;          // element idx = row*ws + e
+            const int drow = 32 / g.ws, de = 32 - drow * g.ws;
+            for (int idx = lane; idx < n; idx += 32) {
+                dst[(int64_t)row * g.K + e] = src[idx];
+                row += drow;
+                e += de;
+                if (e >= g.ws) { e -= g.ws; ++row; }
+            }
+        }
+        __syncwarp();
+    })
+}
+
+// =====================================================================
 // Backward, query-owned: dq.  The s chain starts at -L (log2 domain) and the
 // dP chain at -D, so P = 2^chain and dS = P * chain'.
 // =====================================================================
@@ -506,32 +624,20 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
     for (int di = 0; di < ws; ++di) {
         const uint32_t a0 = rowbase + di * kRowBytes;
         float dp[4];
-        u64 k2[8];
         {
             u64 v2[8];
             lds_vec16(a0, 1, v2);
-            lds_vec16(a0, 0, k2);
-            if (MASK != 0) {
-                u64 t[4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) t[r] = nD2[r];        // (-D, 0)
+            for (int r = 0; r < 4; ++r)
+                if (CA_ON(r)) {
+                    u64 t = nD2[r];                               // (-D, 0)
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) t[r] = fma2(dy[r][i], v2[i], t[r]);
-#pragma unroll
-                for (int r = 0; r < 4; ++r) dp[r] = hsum2(t[r]);
-            } else {
-#pragma unroll
-                for (int r = 0; r < 4; ++r)
-                    if (CA_ON(r)) {
-                        u64 t = nD2[r];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) t = fma2(dy[r][i], v2[i], t);
-                        dp[r] = hsum2(t);
-                    }
-            }
+                    for (int i = 0; i < 8; ++i) t = fma2(dy[r][i], v2[i], t);
+                    dp[r] = hsum2(t);
+                }
         }
+        u64 k2[8];
+        lds_vec16(a0, 0, k2);
         float bk = 0.f;
         if (DIST) {
             u64 n = 0ull;
@@ -539,35 +645,14 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
             for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
             bk = -0.5f * sl2 * hsum2(n);
         }
-        float sv[4];
-        if (MASK != 0) {
-            u64 t[4];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                t[r] = nL2[r];                                    // (-L, 0), log2 domain
-                if (DIST) t[r] = add2(t[r], pack2(bq[r] + bk, 0.f));
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) t[r] = fma2(q[r][i], k2[i], t[r]);
-#pragma unroll
-            for (int r = 0; r < 4; ++r) sv[r] = hsum2(t[r]);
-        } else {
-#pragma unroll
-            for (int r = 0; r < 4; ++r)
-                if (CA_ON(r)) {
-                    u64 t = nL2[r];
-                    if (DIST) t = add2(t, pack2(bq[r] + bk, 0.f));
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) t = fma2(q[r][i], k2[i], t);
-                    sv[r] = hsum2(t);
-                }
-        }
 #pragma unroll
         for (int r = 0; r < 4; ++r)
             if (CA_ON(r)) {
-                const float ds = fast_exp2(sv[r]) * dp[r];
+                u64 t = nL2[r];                                   // (-L, 0), log2 domain
+                if (DIST) t = add2(t, pack2(bq[r] + bk, 0.f));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t = fma2(q[r][i], k2[i], t);
+                const float ds = fast_exp2(hsum2(t)) * dp[r];
                 if (DIST) sumds[r] += ds;
                 const u64 d2 = pack2(ds, ds);
 #pragma unroll
@@ -671,31 +756,17 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
         const float nLj = -Lb[row], nDj = -Db[row];
         u64 y2[8];
         lds_vec16(a0, 1, y2);
+        float dp[3];
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+            if (CA_ON(r)) {
+                u64 t = pack2(nDj, 0.f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t = fma2(v[r][i], y2[i], t);
+                dp[r] = hsum2(t);
+            }
         u64 q2[8];
         lds_vec16(a0, 0, q2);
-        float dp[3], sv[3];
-        {
-            // six chains (three dP, three score) advance together
-            u64 t[3], w[3];
-#pragma unroll
-            for (int r = 0; r < 3; ++r) {
-                t[r] = pack2(nDj, 0.f);
-                w[r] = pack2(nLj, 0.f);
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int r = 0; r < 3; ++r)
-                    if (CA_ON(r)) {
-                        t[r] = fma2(v[r][i], y2[i], t[r]);
-                        w[r] = fma2(k[r][i], q2[i], w[r]);
-                    }
-#pragma unroll
-            for (int r = 0; r < 3; ++r) {
-                dp[r] = hsum2(t[r]);
-                sv[r] = hsum2(w[r]);
-            }
-        }
         float bqj = 0.f;
         if (DIST) {
             u64 n = 0ull;
@@ -706,7 +777,10 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
 #pragma unroll
         for (int r = 0; r < 3; ++r)
             if (CA_ON(r)) {
-                const float P = fast_exp2(DIST ? sv[r] + bk[r] + bqj : sv[r]);
+                u64 t = pack2(DIST ? nLj + bk[r] + bqj : nLj, 0.f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t = fma2(k[r][i], q2[i], t);
+                const float P = fast_exp2(hsum2(t));
                 const float ds = P * dp[r];
                 if (DIST) sumds[r] += ds;
                 const u64 d2 = pack2(ds, ds), p2 = pack2(P, P);
@@ -1081,7 +1155,7 @@ int encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint6
 // ---------------------------------------------------------------- entry points of this file
 size_t tiled_fwd_workspace(const Geo& g) {
     if (!tiled_shape_ok(g)) return 0;
-    return padded_of(g).pair_floats * sizeof(float);
+    return (padded_of(g).pair_floats + (size_t)g.Np * g.units) * sizeof(float);
 }
 
 size_t tiled_bwd_stage_workspace(const Geo& g) {
@@ -1102,12 +1176,16 @@ int tiled_stage_timeouts(int* count) {
     return CA_OK;
 }
 
+int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const float* stats, float* nz,
+                 void* workspace, cudaStream_t st);
+
 int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                         float* y, float* nz, float* stats, void* workspace, cudaStream_t st) {
-    if (!tiled_shape_ok(g) || nz) return CA_ERR_UNSUPPORTED;
+    if (!tiled_shape_ok(g) || (nz && g.Wk != g.W)) return CA_ERR_UNSUPPORTED;
     if (!workspace) { set_error("workspace of ca_attention_fwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
     const Padded P = padded_of(g);
     float* kv = static_cast<float*>(workspace);
+    if (nz && !stats) stats = kv + P.pair_floats;         // scratch statistics behind the packed pair
     PackArgs pa{};
     pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1;
     pa.src[0] = k; pa.src[1] = v; pa.dst[0] = kv;
@@ -1141,6 +1219,23 @@ int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, con
 #undef CA_FWD2
 #undef CA_FWD
     CA_CHECK_LAUNCH("tiled forward kernel");
+    if (nz) return tiled_emit_a(g, scale, dist, q, stats, nz, workspace, st);
+    return CA_OK;
+}
+
+// A's values in CSR order from q, the packed (k|v) pair left in `workspace` by
+// tiled_attention_fwd, and the row statistics.
+int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const float* stats, float* nz,
+                 void* workspace, cudaStream_t st) {
+    if (!tiled_shape_ok(g) || g.Wk != g.W) return CA_ERR_UNSUPPORTED;
+    const Padded P = padded_of(g);
+    Launch L{};
+    int rc = prepare(g, P, 4, 0, "CIRCATT_FWD_WARPS", static_cast<const float*>(workspace), nullptr, &L);
+    if (rc) return rc;
+    L.smem += (size_t)L.threads / 32 * 128 * g.ws * sizeof(float);
+    L.a.scale = scale; L.a.c0 = q; L.a.cs0 = stats; L.a.o0 = nz;
+    CA_DIST_CPE(emit_a_tiled_kernel, dist, g.cpe, L, st);
+    CA_CHECK_LAUNCH("tiled A kernel");
     return CA_OK;
 }
 
@@ -1176,6 +1271,32 @@ int tiled_attention_bwd_dkdv(const Geo& g, float scale, int dist, const float* q
     return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st);
 }
 
+// Helper stream (one per device) on which the dk/dv sweep of a small problem runs
+// next to the dq sweep: neither fills the GPU alone.  It is forked from and joined
+// back to the caller's stream with events, so the caller sees ordinary stream order.
+struct ForkJoin {
+    cudaStream_t side = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+static std::mutex g_fork_mutex;
+static ForkJoin g_fork[64];
+
+static ForkJoin* fork_join_for_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    ForkJoin& f = g_fork[dev];
+    if (!f.side) {
+        if (cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&f.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&f.join, cudaEventDisableTiming) != cudaSuccess) {
+            f.side = nullptr;
+            cudaGetLastError();
+            return nullptr;
+        }
+    }
+    return &f;
+}
+
 // Whole backward in three launches: pack (both pairs, D, planes), dq, dk/dv.
 int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                         const float* y, const float* dy, const float* stats, float* D, float* dq, float* dk,
@@ -1193,6 +1314,20 @@ int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, con
     pa.planes = planes; pa.stats = stats; pa.y = y; pa.dy = dy; pa.Dout = D;
     int rc = launch_pack(pa, st);
     if (rc) return rc;
+    const bool small = (long)g.Np * g.units < 2048L * sm_count();      // fewer than ~4 CTAs per SM per sweep
+    if (small && env_int("CIRCATT_CONCURRENT", 1)) {
+        std::lock_guard<std::mutex> lock(g_fork_mutex);
+        ForkJoin* f = fork_join_for_current_device();
+        if (f && cudaEventRecord(f->fork, st) == cudaSuccess && cudaStreamWaitEvent(f->side, f->fork, 0) == cudaSuccess) {
+            rc = run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, f->side);
+            int rc2 = run_dq(g, P, scale, dist, q, dy, stats, D, kv, dq, st);
+            cudaError_t e = cudaEventRecord(f->join, f->side);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(st, f->join, 0);
+            if (e != cudaSuccess) return cuda_fail(e, "joining the helper stream");
+            return rc ? rc : rc2;
+        }
+        cudaGetLastError();
+    }
     if ((rc = run_dq(g, P, scale, dist, q, dy, stats, D, kv, dq, st))) return rc;
     return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st);
 }

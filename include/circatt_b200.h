@@ -9,8 +9,11 @@
  * Conventions
  *  - All pointers are DEVICE pointers into memory owned by the caller.  The
  *    library never allocates or frees caller-visible memory, never
- *    synchronises the device, and launches only on the stream it is given
- *    (`stream` is a cudaStream_t passed as void*; NULL = legacy default).
+ *    synchronises the device, and orders all its work on the stream it is
+ *    given (`stream` is a cudaStream_t passed as void*; NULL = legacy
+ *    default).  ca_attention_bwd may run one of its sweeps on an internal
+ *    helper stream that is forked from and joined back to that stream with
+ *    events, which is invisible to stream-ordered callers.
  *  - Dense tensors use the Julia column-major layout of the reference:
  *    element (h, w, ch, u) of a (H, W, c, units) array sits at
  *    h + H*(w + W*(ch + c*u)); 1-D signals have W = 1.  `units` is the merged
