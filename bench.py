@@ -234,6 +234,18 @@ def main():
     }
     stage_s = {name: time_stage(fn)[0] for name, fn in stages.items()}
 
+    # ---- other configurations of the same shape (not the headline): A materialised, Distance, forward only
+    def time_variant(kind_v, want_nz):
+        def fn():
+            yv, nzv, stv = ops.attention_fwd(kind_v, norm, q, k, v, ws, want_nz)
+            ops.attention_bwd(kind_v, norm, q, k, v, yv, r, stv, ws)
+        return px_per_step / time_stage(fn, n=10)[0]
+    variants = {
+        "with_A_px_per_s": time_variant(0, True),
+        "distance_px_per_s": time_variant(1, False),
+        "fwd_only_px_per_s": px_per_step / stage_s["fwd"],
+    }
+
     # ---- FP32 FMA peak measured on this GPU (not in MEASURED_PEAKS.json)
     sink = torch.empty(148 * 8 * 256, dtype=torch.float32, device=dev)
     ffma_s, _ = time_stage(lambda: lib.ca_probe_ffma(148 * 8, 4096, P(sink), st()), n=10)
@@ -246,12 +258,17 @@ def main():
         pass
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     dom = max(("fwd", "bwd_dq", "bwd_dkdv"), key=lambda s: stage_s[s])
+    traffic = None
+    try:   # DRAM bytes per launch of each kernel, from the committed ncu capture of this command
+        traffic = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json"))).get(dom)
+    except (OSError, ValueError):
+        pass
     fl, by = algorithmic(wl, dom)
     achieved = fl * px_per_step / stage_s[dom] / 1e12
     fl_all, by_all = algorithmic(wl, "fwd+bwd")
     roofline = {
         "bound": "ffma", "kernel": dom, "achieved": achieved, "peak": ffma_tflops, "unit": "TFLOP/s",
-        "frac": achieved / ffma_tflops, "traffic": None,
+        "frac": achieved / ffma_tflops, "traffic": traffic,
         "peak_source": "FP32 FMA peak measured live by ca_probe_ffma (fma.rn.f32x2, 16 chains/thread); "
                        f"nominal {NOMINAL_FFMA_TFLOPS:.2f}",
         "hbm": {"achieved_gbs": by * px_per_step / stage_s[dom] / 1e9, "peak_gbs": hbm_peak,
@@ -306,7 +323,7 @@ def main():
                                    "softmax, flash mode (A not written)", **wl, "units_per_gpu": nheads * B,
                        "l2": "256 MB buffer written between timed steps (inputs are smaller than L2)",
                        "sharding": "batch x heads units per rank, no collective"},
-            "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "variants": variants,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 3 * nbytes + 4,
                     "steps": n_e2e, "timing": "wall clock around the steps, synchronised on both sides, max over ranks"},
             "gpu_launches": int(launches), "clocks": clocks,

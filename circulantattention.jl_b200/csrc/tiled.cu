@@ -95,11 +95,6 @@ struct TileArgs {
 
 constexpr int kStages = 3;
 
-#ifdef CA_X_NOSYNC
-#define CA_X_SYNC(part, PT) __syncwarp()
-#else
-#define CA_X_SYNC(part, PT) part_sync(part, PT)
-#endif
 #ifndef CA_FWD_MIN_BLOCKS
 #define CA_FWD_MIN_BLOCKS 2
 #endif
@@ -214,7 +209,7 @@ struct StagePipe {
         const int buf = it % kStages;                                                                \
         if (!mbar_wait(&pipe.full[buf], (uint32_t)((it / kStages) & 1))) s_err = 1;                  \
         __VA_ARGS__                                                                                  \
-        CA_X_SYNC(part, PT);                                                                         \
+        part_sync(part, PT);                                                                         \
         if (s_err) break;                                                                            \
         if (lt == 0 && s + kStages < s_end) pipe.issue(g, s + kStages, buf);                         \
     }                                                                                                \
@@ -343,11 +338,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
         for (int r = 0; r < 4; ++r)
 #pragma unroll
             for (int t = 0; t < DC; ++t) allneg &= __float_as_uint(sc[r][t]);
-#ifdef CA_X_NOVOTE
-        if (false) {
-#else
         if (__any_sync(0xffffffffu, allneg == 0u)) {
-#endif
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 float cm = sc[r][0];
@@ -378,11 +369,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
 #pragma unroll
                 for (int r = 0; r < 4; ++r)
                     if (CA_ON(r)) {
-#ifdef CA_X_NOEXP
-                        const float pt = sc[r][t] * 1e-3f;
-#else
                         const float pt = fast_exp2(sc[r][t]);
-#endif
                         l[r] += pt;
                         const u64 p2 = pack2(pt, pt);
 #pragma unroll
