@@ -381,3 +381,79 @@ def scale_pullback(c, nz, dB):
     if axes:
         dA = dA.sum(axis=axes, keepdims=True)
     return dc, dA
+
+
+# --------------------------------------------------------------------------
+# Sampled-pixel mode for sizes where the full oracle is too slow (2-D, real or
+# complex, softmax).  y[j] and dq[j] depend only on the window of j; dk[i] and
+# dv[i] only on the queries whose window contains i, each with its own window.
+# Same arithmetic as `attention` / `attention_pullback`, restricted to the
+# requested pixels.  q, k, v, dy: head-split (H, W, c, units) arrays.
+# --------------------------------------------------------------------------
+def _window_pixels(h, w, H, W, p):
+    d = np.arange(-p, p + 1)
+    hh = (h + d) % H
+    ww = (w + d) % W
+    return (hh[None, :] + H * ww[:, None]).reshape(-1)          # (K,) key pixels of query (h, w)
+
+
+def _row(kind, qj, Kwin, scale):
+    """scores of one query against its window keys: qj (c,), Kwin (K, c)."""
+    if kind == DOT:
+        return scale * np.real(Kwin.conj() @ qj)
+    return -0.5 * scale * (np.abs(qj[None, :] - Kwin) ** 2).sum(axis=1)
+
+
+def sampled_attention(kind, q, k, v, ws, pixels, unit):
+    """y at the given linear pixels of one unit -> (len(pixels), c)."""
+    Q, spatial = _flat(q); Kk, _ = _flat(k); V, _ = _flat(v)
+    H, W = spatial
+    c = Q.shape[1]
+    scale = 1.0 / np.sqrt(float(c))
+    p = (ws - 1) // 2
+    out = np.zeros((len(pixels), c), dtype=np.result_type(V.dtype, np.float64))
+    for n, j in enumerate(pixels):
+        win = _window_pixels(j % H, j // H, H, W, p)
+        s = _row(kind, Q[j, :, unit], Kk[win, :, unit], scale)
+        pr = np.exp(s - s.max()); pr /= pr.sum()
+        out[n] = pr @ V[win, :, unit]
+    return out
+
+
+def sampled_attention_pullback(kind, q, k, v, dy, ws, pixels, unit):
+    """(dq, dk, dv) rows at the given pixels of one unit, each (len(pixels), c)."""
+    Q, spatial = _flat(q); Kk, _ = _flat(k); V, _ = _flat(v); DY, _ = _flat(dy)
+    H, W = spatial
+    c = Q.shape[1]
+    scale = 1.0 / np.sqrt(float(c))
+    p = (ws - 1) // 2
+    cache = {}
+
+    def row_terms(j):
+        """window, P and dS of query row j."""
+        if j not in cache:
+            win = _window_pixels(j % H, j // H, H, W, p)
+            s = _row(kind, Q[j, :, unit], Kk[win, :, unit], scale)
+            P = np.exp(s - s.max()); P /= P.sum()
+            dP = np.real(V[win, :, unit].conj() @ DY[j, :, unit])
+            dS = P * (dP - (P * dP).sum())
+            cache[j] = (win, P, dS)
+        return cache[j]
+
+    dq = np.zeros((len(pixels), c), dtype=Q.dtype); dk = np.zeros_like(dq); dv = np.zeros_like(dq)
+    for n, j in enumerate(pixels):
+        win, P, dS = row_terms(j)
+        dq[n] = scale * (dS @ Kk[win, :, unit])
+        if kind == DISTANCE:
+            dq[n] -= scale * dS.sum() * Q[j, :, unit]
+        # as a key: every query whose window contains j (window symmetry: the same pixel set)
+        sum_ds = 0.0
+        for jq in win:
+            wq, Pq, dSq = row_terms(int(jq))
+            pos = int(np.nonzero(wq == j)[0][0])
+            dk[n] += scale * dSq[pos] * Q[jq, :, unit]
+            dv[n] += Pq[pos] * DY[jq, :, unit]
+            sum_ds += dSq[pos]
+        if kind == DISTANCE:
+            dk[n] -= scale * sum_ds * Kk[j, :, unit]
+    return dq, dk, dv

@@ -273,3 +273,22 @@ def test_sums():
     np.testing.assert_allclose(orc.sum_dims1(nz, spatial, ws), dense.sum(0), rtol=1e-12, atol=1e-14)
     assert orc.sum_batch(nz, (3,)).shape == (9, 30, 1, 3)
     assert orc.sum_batch(nz, (3, 4)).shape == (9, 30, 1, 1)
+
+
+def test_sampled_oracle_matches_full_oracle():
+    rng = np.random.default_rng(12)
+    shape, ws, nheads = (9, 8, 6, 2), 5, 2
+    q, k, v, dy = (randn(rng, shape) for _ in range(4))
+    qs, ks, vs, dys = (orc.splitheads(t, nheads) for t in (q, k, v, dy))
+    pixels = [0, 7, 8, 35, 71, 40]
+    for kind in (orc.DOT, orc.DISTANCE):
+        y, _ = orc.attention(kind, qs, ks, vs, ws)
+        dq, dk, dv = orc.attention_pullback(kind, qs, ks, vs, ws, dys)
+        Y, _ = orc._flat(y); DQ, _ = orc._flat(dq); DK, _ = orc._flat(dk); DV, _ = orc._flat(dv)
+        for unit in (0, 3):
+            ys = orc.sampled_attention(kind, qs, ks, vs, ws, pixels, unit)
+            sq, sk, sv = orc.sampled_attention_pullback(kind, qs, ks, vs, dys, ws, pixels, unit)
+            np.testing.assert_allclose(ys, Y[pixels, :, unit], rtol=1e-11, atol=1e-13)
+            np.testing.assert_allclose(sq, DQ[pixels, :, unit], rtol=1e-10, atol=1e-13)
+            np.testing.assert_allclose(sk, DK[pixels, :, unit], rtol=1e-10, atol=1e-13)
+            np.testing.assert_allclose(sv, DV[pixels, :, unit], rtol=1e-10, atol=1e-13)
