@@ -276,12 +276,12 @@ __device__ __forceinline__ void store_centre(float* dst, const Geo& g, int u, in
 // of the chunk reveals; with O(1) scores that happens almost never after the
 // first key.  2^-kHeadroom only rescales p, l and acc together; it cancels in y.
 constexpr float kHeadroom = 12.f;
-template <int DC, bool DIST, int MASK, bool EXACT>
-__device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[4][8],
-                                          u64 (&acc)[4][8], u64 (&nm2)[4], float (&l)[4], const float (&bq)[4]) {
+template <int DC, bool DIST, int MASK, bool EXACT, int NQ>
+__device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[NQ][8],
+                                          u64 (&acc)[NQ][8], u64 (&nm2)[NQ], float (&l)[NQ], const float (&bq)[NQ]) {
     for (int c0 = 0; c0 < ws; c0 += DC) {
         const uint32_t cb = rowbase + c0 * kRowBytes;
-        float sc[4][DC];
+        float sc[NQ][DC];
         // one vector ahead: the next key (or the first v) is requested before this key's FMAs
         u64 nxt[8];
         lds_vec16(cb, 0, nxt);
@@ -302,21 +302,21 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                 }
                 if (MASK != 0) {
                     // all four chains advance together (4 independent FMAs in flight)
-                    u64 sa[4];
+                    u64 sa[NQ];
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) {
+                    for (int r = 0; r < NQ; ++r) {
                         sa[r] = nm2[r];                           // (-ref, 0)
                         if (DIST) sa[r] = add2(sa[r], pack2(bq[r] + bk, 0.f));
                     }
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
 #pragma unroll
-                        for (int r = 0; r < 4; ++r) sa[r] = fma2(q[r][i], k2[i], sa[r]);
+                        for (int r = 0; r < NQ; ++r) sa[r] = fma2(q[r][i], k2[i], sa[r]);
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) sc[r][t] = hsum2(sa[r]);
+                    for (int r = 0; r < NQ; ++r) sc[r][t] = hsum2(sa[r]);
                 } else {
 #pragma unroll
-                    for (int r = 0; r < 4; ++r)
+                    for (int r = 0; r < NQ; ++r)
                         if (CA_ON(r)) {
                             u64 sa = nm2[r];
                             if (DIST) sa = add2(sa, pack2(bq[r] + bk, 0.f));
@@ -329,18 +329,18 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                 }
             } else {
 #pragma unroll
-                for (int r = 0; r < 4; ++r) sc[r][t] = -INFINITY;
+                for (int r = 0; r < NQ; ++r) sc[r][t] = -INFINITY;
             }
         }
         // any relative score >= 0 ?  (sign bit clear)
         uint32_t allneg = 0x80000000u;
 #pragma unroll
-        for (int r = 0; r < 4; ++r)
+        for (int r = 0; r < NQ; ++r)
 #pragma unroll
             for (int t = 0; t < DC; ++t) allneg &= __float_as_uint(sc[r][t]);
         if (__any_sync(0xffffffffu, allneg == 0u)) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
+            for (int r = 0; r < NQ; ++r) {
                 float cm = sc[r][0];
 #pragma unroll
                 for (int t = 1; t < DC; ++t) cm = fmaxf(cm, sc[r][t]);
@@ -367,7 +367,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                 for (int i = 0; i < 8; ++i) v2[i] = nxt[i];
                 if (t + 1 < DC && (EXACT || c0 + t + 1 < ws)) lds_vec16(cb + (t + 1) * kRowBytes, 1, nxt);
 #pragma unroll
-                for (int r = 0; r < 4; ++r)
+                for (int r = 0; r < NQ; ++r)
                     if (CA_ON(r)) {
                         const float pt = fast_exp2(sc[r][t]);
                         l[r] += pt;
@@ -382,9 +382,9 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
 
 // First score of each centre pixel that starts in this stage: the reference
 // point of its running maximum.
-template <bool DIST>
-__device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float sl2, const u64 (&q)[4][8],
-                                             u64 (&nm2)[4], const float (&bq)[4]) {
+template <bool DIST, int NQ>
+__device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float sl2, const u64 (&q)[NQ][8],
+                                             u64 (&nm2)[NQ], const float (&bq)[NQ]) {
     u64 k2[8];
     lds_vec16(rowbase, 0, k2);
     float bk = 0.f;
@@ -395,7 +395,7 @@ __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float s
         bk = -0.5f * sl2 * hsum2(n);
     }
 #pragma unroll
-    for (int r = 0; r < 4; ++r)
+    for (int r = 0; r < NQ; ++r)
         if ((init >> r) & 1) {
             u64 sa = 0ull;
 #pragma unroll
@@ -408,24 +408,24 @@ __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float s
     if ((mask) == (FULL)) { constexpr int MK = (FULL); CALL; }      \
     else { constexpr int MK = 0; CALL; }
 
-template <int DC, bool DIST, int CPE, bool EXACT>
-__global__ void __launch_bounds__(128, CA_FWD_MIN_BLOCKS) fwd_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+template <int DC, bool DIST, int CPE, bool EXACT, int NQ>
+__global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                            const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NS = g.ws + 3;
-    const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
+    const int NS = g.ws + NQ - 1;
+    const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
     const int lr = lt, h = h0 + lr;
     const bool active = h < g.H;
 
-    u64 q[4][8], acc[4][8];
-    load_centre<CPE, 4>(a.c0, g, u, h, w0, active, sl2, q);
-    u64 nm2[4];
-    float l[4], bq[4];
+    u64 q[NQ][8], acc[NQ][8];
+    load_centre<CPE, NQ>(a.c0, g, u, h, w0, active, sl2, q);
+    u64 nm2[NQ];
+    float l[NQ], bq[NQ];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < NQ; ++r) {
         nm2[r] = pack2(INFINITY, 0.f);           // (-m, 0); running maximum -inf: no key seen yet
         l[r] = 0.f;
         bq[r] = 0.f;
@@ -440,17 +440,17 @@ __global__ void __launch_bounds__(128, CA_FWD_MIN_BLOCKS) fwd_tiled_kernel(TileA
     }
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask<4>(s, g.p);
+        const int mask = stage_mask<NQ>(s, g.p);
         const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes;
         // pixels whose first stage (of this part) is s
-        const int init = (s == s_begin) ? mask : (mask & ~stage_mask<4>(s - 1, g.p));
-        if (init) fwd_init_max<DIST>(rowbase, init, sl2, q, nm2, bq);
-        CA_MASK_SWITCH(15, mask, (fwd_stage<DC, DIST, MK, EXACT>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq)));
+        const int init = (s == s_begin) ? mask : (mask & ~stage_mask<NQ>(s - 1, g.p));
+        if (init) fwd_init_max<DIST, NQ>(rowbase, init, sl2, q, nm2, bq);
+        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (fwd_stage<DC, DIST, MK, EXACT, NQ>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq)));
     })
 
-    float nm[4];
+    float nm[NQ];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < NQ; ++r) {
         float zero;
         unpack2(nm2[r], nm[r], zero);
     }
@@ -459,7 +459,7 @@ __global__ void __launch_bounds__(128, CA_FWD_MIN_BLOCKS) fwd_tiled_kernel(TileA
         float* xch = reinterpret_cast<float*>(smem_al);
         if (part == 1) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
+            for (int r = 0; r < NQ; ++r) {
                 xch[(r * 18 + 0) * PT + lt] = nm[r];
                 xch[(r * 18 + 1) * PT + lt] = l[r];
 #pragma unroll
@@ -474,7 +474,7 @@ __global__ void __launch_bounds__(128, CA_FWD_MIN_BLOCKS) fwd_tiled_kernel(TileA
         __syncthreads();
         if (part == 1) return;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < NQ; ++r) {
             const float nm1 = xch[(r * 18 + 0) * PT + lt], l1 = xch[(r * 18 + 1) * PT + lt];
             const float nmn = fminf(nm[r], nm1);           // -max(m0, m1)
             const float c0 = (nm[r] == INFINITY) ? 0.f : fast_exp2(nmn - nm[r]);
@@ -490,7 +490,7 @@ __global__ void __launch_bounds__(128, CA_FWD_MIN_BLOCKS) fwd_tiled_kernel(TileA
         }
     }
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < NQ; ++r) {
         const float inv = 1.f / l[r];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -603,19 +603,19 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
 // Backward, query-owned: dq.  The s chain starts at -L (log2 domain) and the
 // dP chain at -D, so P = 2^chain and dS = P * chain'.
 // =====================================================================
-template <bool DIST, int MASK>
-__device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[4][8],
-                                         const u64 (&dy)[4][8], u64 (&dq)[4][8], const u64 (&nL2)[4],
-                                         const u64 (&nD2)[4], const float (&bq)[4], float (&sumds)[4]) {
+template <bool DIST, int MASK, int NQ>
+__device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[NQ][8],
+                                         const u64 (&dy)[NQ][8], u64 (&dq)[NQ][8], const u64 (&nL2)[NQ],
+                                         const u64 (&nD2)[NQ], const float (&bq)[NQ], float (&sumds)[NQ]) {
 #pragma unroll 1
     for (int di = 0; di < ws; ++di) {
         const uint32_t a0 = rowbase + di * kRowBytes;
-        float dp[4];
+        float dp[NQ];
         {
             u64 v2[8];
             lds_vec16(a0, 1, v2);
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
+            for (int r = 0; r < NQ; ++r)
                 if (CA_ON(r)) {
                     u64 t = nD2[r];                               // (-D, 0)
 #pragma unroll
@@ -633,7 +633,7 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
             bk = -0.5f * sl2 * hsum2(n);
         }
 #pragma unroll
-        for (int r = 0; r < 4; ++r)
+        for (int r = 0; r < NQ; ++r)
             if (CA_ON(r)) {
                 u64 t = nL2[r];                                   // (-L, 0), log2 domain
                 if (DIST) t = add2(t, pack2(bq[r] + bk, 0.f));
@@ -648,25 +648,25 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
     }
 }
 
-template <bool DIST, int CPE>
-__global__ void __launch_bounds__(128, 2) dq_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+template <bool DIST, int CPE, int NQ>
+__global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                           const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NS = g.ws + 3;
-    const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
+    const int NS = g.ws + NQ - 1;
+    const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
     const int lr = lt, h = h0 + lr;
     const bool active = h < g.H;
 
-    u64 q[4][8], dy[4][8], dq[4][8];
-    load_centre<CPE, 4>(a.c0, g, u, h, w0, active, sl2, q);
-    load_centre<CPE, 4>(a.c1, g, u, h, w0, active, 1.f, dy);
-    u64 nL2[4], nD2[4];
-    float bq[4], sumds[4];
+    u64 q[NQ][8], dy[NQ][8], dq[NQ][8];
+    load_centre<CPE, NQ>(a.c0, g, u, h, w0, active, sl2, q);
+    load_centre<CPE, NQ>(a.c1, g, u, h, w0, active, 1.f, dy);
+    u64 nL2[NQ], nD2[NQ];
+    float bq[NQ], sumds[NQ];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < NQ; ++r) {
         const bool ok = active && (w0 + r < g.W);
         const int64_t o = (int64_t)u * g.Np + h + g.H * (w0 + r);
         nL2[r] = pack2(ok ? -__ldg(a.cs0 + o) * kLog2e : 0.f, 0.f);
@@ -684,8 +684,8 @@ __global__ void __launch_bounds__(128, 2) dq_tiled_kernel(TileArgs a, const __gr
     }
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask<4>(s, g.p);
-        CA_MASK_SWITCH(15, mask, (dq_stage<DIST, MK>(smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes, g.ws, mask,
+        const int mask = stage_mask<NQ>(s, g.p);
+        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dq_stage<DIST, MK, NQ>(smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes, g.ws, mask,
                                                      sl2, q, dy, dq, nL2, nD2, bq, sumds)));
     })
 
@@ -693,7 +693,7 @@ __global__ void __launch_bounds__(128, 2) dq_tiled_kernel(TileArgs a, const __gr
         float* xch = reinterpret_cast<float*>(smem_al);
         if (part == 1) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
+            for (int r = 0; r < NQ; ++r) {
                 xch[(r * 17 + 16) * PT + lt] = sumds[r];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -707,7 +707,7 @@ __global__ void __launch_bounds__(128, 2) dq_tiled_kernel(TileArgs a, const __gr
         __syncthreads();
         if (part == 1) return;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < NQ; ++r) {
             sumds[r] += xch[(r * 17 + 16) * PT + lt];
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -716,7 +716,7 @@ __global__ void __launch_bounds__(128, 2) dq_tiled_kernel(TileArgs a, const __gr
     }
     // dq = scale * (sum ds*k - [distance] sum(ds) * q);  q registers hold q*scale*log2(e)
 #pragma unroll
-    for (int r = 0; r < 4; ++r)
+    for (int r = 0; r < NQ; ++r)
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             float x, y, qx, qy;
@@ -732,10 +732,10 @@ __global__ void __launch_bounds__(128, 2) dq_tiled_kernel(TileArgs a, const __gr
 // Backward, key-owned: dk and dv of three key pixels per thread.  The stage
 // rows carry (q | dy) of the query pixels plus their L and D.
 // =====================================================================
-template <bool DIST, int MASK>
+template <bool DIST, int MASK, int NQ>
 __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const float* Db, int row0, int ws, int rm,
-                                           float sl2, const u64 (&k)[3][8], const u64 (&v)[3][8], u64 (&dk)[3][8],
-                                           u64 (&dv)[3][8], const float (&bk)[3], float (&sumds)[3]) {
+                                           float sl2, const u64 (&k)[NQ][8], const u64 (&v)[NQ][8], u64 (&dk)[NQ][8],
+                                           u64 (&dv)[NQ][8], const float (&bk)[NQ], float (&sumds)[NQ]) {
 #pragma unroll 1
     for (int di = 0; di < ws; ++di) {
         const int row = row0 + di;
@@ -743,9 +743,9 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
         const float nLj = -Lb[row], nDj = -Db[row];
         u64 y2[8];
         lds_vec16(a0, 1, y2);
-        float dp[3];
+        float dp[NQ];
 #pragma unroll
-        for (int r = 0; r < 3; ++r)
+        for (int r = 0; r < NQ; ++r)
             if (CA_ON(r)) {
                 u64 t = pack2(nDj, 0.f);
 #pragma unroll
@@ -762,7 +762,7 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
             bqj = -0.5f * sl2 * hsum2(n);
         }
 #pragma unroll
-        for (int r = 0; r < 3; ++r)
+        for (int r = 0; r < NQ; ++r)
             if (CA_ON(r)) {
                 u64 t = pack2(DIST ? nLj + bk[r] + bqj : nLj, 0.f);
 #pragma unroll
@@ -780,24 +780,24 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
     }
 }
 
-template <bool DIST, int CPE>
-__global__ void __launch_bounds__(128, 2) dkdv_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+template <bool DIST, int CPE, int NQ>
+__global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                             const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NS = g.ws + 2;
-    const int w0 = blockIdx.x * 3, h0 = blockIdx.y * a.TH, u = blockIdx.z;
+    const int NS = g.ws + NQ - 1;
+    const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(true)
     const int lr = lt, h = h0 + lr;
     const bool active = h < g.H;
 
-    u64 k[3][8], v[3][8], dk[3][8], dv[3][8];
-    load_centre<CPE, 3>(a.c0, g, u, h, w0, active, sl2, k);
-    load_centre<CPE, 3>(a.c1, g, u, h, w0, active, 1.f, v);
-    float bk[3], sumds[3];
+    u64 k[NQ][8], v[NQ][8], dk[NQ][8], dv[NQ][8];
+    load_centre<CPE, NQ>(a.c0, g, u, h, w0, active, sl2, k);
+    load_centre<CPE, NQ>(a.c1, g, u, h, w0, active, 1.f, v);
+    float bk[NQ], sumds[NQ];
 #pragma unroll
-    for (int r = 0; r < 3; ++r) {
+    for (int r = 0; r < NQ; ++r) {
         sumds[r] = 0.f;
         bk[r] = 0.f;
         if (DIST) {
@@ -814,8 +814,8 @@ __global__ void __launch_bounds__(128, 2) dkdv_tiled_kernel(TileArgs a, const __
     }
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask<3>(s, g.p);
-        CA_MASK_SWITCH(7, mask, (dkdv_stage<DIST, MK>(smem_u32(pipe.vec(buf)), pipe.sc0(buf), pipe.sc1(buf),
+        const int mask = stage_mask<NQ>(s, g.p);
+        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dkdv_stage<DIST, MK, NQ>(smem_u32(pipe.vec(buf)), pipe.sc0(buf), pipe.sc1(buf),
                                                       lr + a.roff, g.ws, mask, sl2, k, v, dk, dv, bk, sumds)));
     })
 
@@ -823,7 +823,7 @@ __global__ void __launch_bounds__(128, 2) dkdv_tiled_kernel(TileArgs a, const __
         float* xch = reinterpret_cast<float*>(smem_al);
         if (part == 1) {
 #pragma unroll
-            for (int r = 0; r < 3; ++r) {
+            for (int r = 0; r < NQ; ++r) {
                 xch[(r * 33 + 32) * PT + lt] = sumds[r];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -840,7 +840,7 @@ __global__ void __launch_bounds__(128, 2) dkdv_tiled_kernel(TileArgs a, const __
         __syncthreads();
         if (part == 1) return;
 #pragma unroll
-        for (int r = 0; r < 3; ++r) {
+        for (int r = 0; r < NQ; ++r) {
             sumds[r] += xch[(r * 33 + 32) * PT + lt];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -851,7 +851,7 @@ __global__ void __launch_bounds__(128, 2) dkdv_tiled_kernel(TileArgs a, const __
     }
     // dk = scale * (sum ds*q - [distance] sum(ds) * k);  k registers hold k*scale*log2(e)
 #pragma unroll
-    for (int r = 0; r < 3; ++r)
+    for (int r = 0; r < NQ; ++r)
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             float x, y, kx, ky, vx, vy;
@@ -1019,7 +1019,7 @@ int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* e
     if (warps > 4) warps = 4;
     const long cols = (g.W + nq - 1) / nq;
     const long ctas4 = cols * ((g.H + 32 * warps - 1) / (32 * warps)) * g.units;
-    int nsplit = (ctas4 * warps < 8L * sm_count()) ? 2 : 1;
+    int nsplit = (ctas4 * warps < 6L * sm_count()) ? 2 : 1;
     nsplit = env_int("CIRCATT_SPLIT", nsplit);
     if (nsplit == 2 && warps > 2) warps = 2;
     warps = env_int(env_warps, warps);
@@ -1083,13 +1083,35 @@ int set_smem(K kernel, size_t bytes) {
         }                                                                             \
     } while (0)
 
+#define CA_DIST_CPE_NQ(KERNEL_T, dist, cpe, NQV, L, st)                               \
+    do {                                                                              \
+        if ((cpe) == 1) {                                                             \
+            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 1, NQV>), L, st);               \
+            else CA_LAUNCH_TILED((KERNEL_T<false, 1, NQV>), L, st);                   \
+        } else {                                                                      \
+            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 2, NQV>), L, st);               \
+            else CA_LAUNCH_TILED((KERNEL_T<false, 2, NQV>), L, st);                   \
+        }                                                                             \
+    } while (0)
+
+// Centre pixels per thread.  Large problems use the widest tile the registers allow (least
+// shared-memory traffic per FMA); problems too small to fill the GPU use narrower tiles, which
+// means more, shorter-lived warps.
+int pick_nq(const Geo& g, int wide, int narrow, const char* env) {
+    const long tasks = ((long)(g.W + wide - 1) / wide) * ((g.H + 31) / 32) * g.units;     // warps at the wide tile
+    const int nq = tasks < 12L * sm_count() ? narrow : wide;
+    return env_int(env, nq);
+}
+
 int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q, const float* dy, const float* stats,
            const float* D, const float* kv, float* dq, cudaStream_t st) {
     Launch L{};
-    int rc = prepare(g, P, 4, 68, "CIRCATT_DQ_WARPS", kv, nullptr, &L);
+    const int nq = pick_nq(g, 4, 2, "CIRCATT_DQ_NQ");
+    int rc = prepare(g, P, nq, 17 * nq, "CIRCATT_DQ_WARPS", kv, nullptr, &L);
     if (rc) return rc;
     L.a.scale = scale; L.a.c0 = q; L.a.c1 = dy; L.a.cs0 = stats; L.a.cs1 = D; L.a.o0 = dq;
-    CA_DIST_CPE(dq_tiled_kernel, dist, g.cpe, L, st);
+    if (nq == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 2, L, st);
+    else CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, L, st);
     CA_CHECK_LAUNCH("tiled dq kernel");
     return CA_OK;
 }
@@ -1097,10 +1119,13 @@ int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q,
 int run_dkdv(const Geo& g, const Padded& P, float scale, int dist, const float* k, const float* v, const float* qdy,
              const float* planes, float* dk, float* dv, cudaStream_t st) {
     Launch L{};
-    int rc = prepare(g, P, 3, 99, "CIRCATT_DKDV_WARPS", qdy, planes, &L);
+    const int nq = pick_nq(g, 3, 3, "CIRCATT_DKDV_NQ");
+    int rc = prepare(g, P, nq, 33 * nq, "CIRCATT_DKDV_WARPS", qdy, planes, &L);
     if (rc) return rc;
     L.a.scale = scale; L.a.c0 = k; L.a.c1 = v; L.a.o0 = dk; L.a.o1 = dv;
-    CA_DIST_CPE(dkdv_tiled_kernel, dist, g.cpe, L, st);
+    if (nq == 1) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 1, L, st);
+    else if (nq == 2) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 2, L, st);
+    else CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, L, st);
     CA_CHECK_LAUNCH("tiled dk/dv kernel");
     return CA_OK;
 }
@@ -1179,23 +1204,29 @@ int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, con
     int rc = launch_pack(pa, st);
     if (rc) return rc;
     Launch L{};
-    if ((rc = prepare(g, P, 4, 72, "CIRCATT_FWD_WARPS", kv, nullptr, &L))) return rc;
+    const int nq = pick_nq(g, 4, 2, "CIRCATT_FWD_NQ");
+    if ((rc = prepare(g, P, nq, 18 * nq, "CIRCATT_FWD_WARPS", kv, nullptr, &L))) return rc;
     L.a.scale = scale; L.a.c0 = q; L.a.o0 = y; L.a.ostats = stats;
     const int dc = pick_dc(g.ws);
-#define CA_FWD2(DCV, EX)                                                                 \
+#define CA_FWD2(DCV, EX, NQV)                                                               \
     do {                                                                                 \
         if (g.cpe == 1) {                                                                \
-            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 1, EX>), L, st);      \
-            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 1, EX>), L, st);          \
+            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 1, EX, NQV>), L, st); \
+            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 1, EX, NQV>), L, st);     \
         } else {                                                                         \
-            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 2, EX>), L, st);      \
-            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 2, EX>), L, st);          \
+            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 2, EX, NQV>), L, st); \
+            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 2, EX, NQV>), L, st);     \
         }                                                                                \
     } while (0)
 #define CA_FWD(DCV)                                                                      \
     do {                                                                                 \
-        if (g.ws % DCV == 0) CA_FWD2(DCV, true);                                         \
-        else CA_FWD2(DCV, false);                                                        \
+        if (nq == 2) {                                                                   \
+            if (g.ws % DCV == 0) CA_FWD2(DCV, true, 2);                                  \
+            else CA_FWD2(DCV, false, 2);                                                 \
+        } else {                                                                         \
+            if (g.ws % DCV == 0) CA_FWD2(DCV, true, 4);                                  \
+            else CA_FWD2(DCV, false, 4);                                                 \
+        }                                                                                \
     } while (0)
     switch (dc) {
         case 3: CA_FWD(3); break;
