@@ -28,9 +28,11 @@
 // conflict free without any address swizzle and every chunk of every row of a
 // window column is the thread's row base plus a compile-time constant.
 //
-// Arithmetic: FP32 on the FMA pipe, issued as packed fma.rn.f32x2 (a
-// 16-channel dot product or axpy is 8 instructions); softmax in the log2
-// domain with ex2.approx.  The running maximum (forward) or the saved row
+// Arithmetic: FP32 on the FMA pipe.  Channel pairs are carried as two-element
+// values; whether a pair operation is one packed fma.rn.f32x2 or two scalar FMAs
+// is a build switch (CA_PACKED_FMA) decided by measurement (scalar is the
+// default: the register file cannot feed packed FMAs with two fresh 64-bit
+// operands at full rate).  Softmax in the log2 domain with ex2.approx.  The running maximum (forward) or the saved row
 // statistic (backward) is folded into the initial value of the dot-product
 // chain, and the forward only touches the maximum when the sign bits of a chunk
 // of relative scores say that one of them is positive.
@@ -46,8 +48,18 @@
 namespace ca {
 namespace {
 
-typedef unsigned long long u64;
+// Two-channel arithmetic.  CA_PACKED_FMA = 1 issues packed fma.rn.f32x2 on 64-bit register
+// pairs; CA_PACKED_FMA = 0 (default) issues two scalar FMAs.  The choice is measured, not
+// assumed: a packed FMA needs its multiplicands re-used between consecutive instructions to
+// run at full rate, and the dot-product / outer-product patterns below have two fresh 64-bit
+// operands per instruction, which the register file delivers at one FFMA2 per ~3.5 cycles,
+// against ~1.33 cycles per scalar FFMA (csrc/probe/ffma_operands.cu).
+#ifndef CA_PACKED_FMA
+#define CA_PACKED_FMA 0
+#endif
 
+#if CA_PACKED_FMA
+typedef unsigned long long u64;
 __device__ __forceinline__ u64 pack2(float a, float b) {
     u64 r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
@@ -71,6 +83,22 @@ __device__ __forceinline__ u64 add2(u64 a, u64 b) {
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
+__device__ __forceinline__ u64 zero2() { return 0ull; }
+__device__ __forceinline__ void lds128(uint32_t addr, u64& lo, u64& hi) {
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(addr));
+}
+#else
+struct u64 { float x, y; };                       // a channel pair in two ordinary registers
+__device__ __forceinline__ u64 pack2(float a, float b) { return u64{a, b}; }
+__device__ __forceinline__ void unpack2(u64 v, float& a, float& b) { a = v.x; b = v.y; }
+__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) { return u64{fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)}; }
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) { return u64{a.x * b.x, a.y * b.y}; }
+__device__ __forceinline__ u64 add2(u64 a, u64 b) { return u64{a.x + b.x, a.y + b.y}; }
+__device__ __forceinline__ u64 zero2() { return u64{0.f, 0.f}; }
+__device__ __forceinline__ void lds128(uint32_t addr, u64& lo, u64& hi) {
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(lo.x), "=f"(lo.y), "=f"(hi.x), "=f"(hi.y) : "r"(addr));
+}
+#endif
 __device__ __forceinline__ float hsum2(u64 v) {
     float a, b;
     unpack2(v, a, b);
@@ -104,10 +132,6 @@ __device__ int g_stage_timeouts = 0;
 
 constexpr int kRowFloats = 36;                 // 16 + 16 + 4 padding
 constexpr int kRowBytes = kRowFloats * 4;      // 144
-
-__device__ __forceinline__ void lds128(uint32_t addr, u64& lo, u64& hi) {
-    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(addr));
-}
 
 // 16-channel vector `which` (0: first tensor, 1: second) of the pixel row at
 // shared-space byte address `a0`, as eight packed pairs.
@@ -295,7 +319,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                 else lds_vec16(cb, 1, nxt);
                 float bk = 0.f;
                 if (DIST) {
-                    u64 n = 0ull;
+                    u64 n = zero2();
 #pragma unroll
                     for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
                     bk = -0.5f * sl2 * hsum2(n);
@@ -389,7 +413,7 @@ __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float s
     lds_vec16(rowbase, 0, k2);
     float bk = 0.f;
     if (DIST) {
-        u64 n = 0ull;
+        u64 n = zero2();
 #pragma unroll
         for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
         bk = -0.5f * sl2 * hsum2(n);
@@ -397,7 +421,7 @@ __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float s
 #pragma unroll
     for (int r = 0; r < NQ; ++r)
         if ((init >> r) & 1) {
-            u64 sa = 0ull;
+            u64 sa = zero2();
 #pragma unroll
             for (int i = 0; i < 8; ++i) sa = fma2(q[r][i], k2[i], sa);
             nm2[r] = pack2(-(hsum2(sa) + (DIST ? bq[r] + bk : 0.f)) - kHeadroom, 0.f);
@@ -430,13 +454,13 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
         l[r] = 0.f;
         bq[r] = 0.f;
         if (DIST) {
-            u64 n = 0ull;
+            u64 n = zero2();
 #pragma unroll
             for (int i = 0; i < 8; ++i) n = fma2(q[r][i], q[r][i], n);
             bq[r] = -0.5f * hsum2(n) / sl2;      // q is pre-scaled by sl2
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[r][i] = 0ull;
+        for (int i = 0; i < 8; ++i) acc[r][i] = zero2();
     }
 
     CA_PIPE_LOOP({
@@ -536,7 +560,7 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
         nL2[r] = pack2(ok ? -__ldg(a.cs0 + (int64_t)u * g.Np + h + g.H * (w0 + r)) * kLog2e : 0.f, 0.f);
         bq[r] = 0.f;
         if (DIST) {
-            u64 n = 0ull;
+            u64 n = zero2();
 #pragma unroll
             for (int i = 0; i < 8; ++i) n = fma2(q[r][i], q[r][i], n);
             bq[r] = -0.5f * hsum2(n) / sl2;
@@ -555,7 +579,7 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
             lds_vec16(rowbase + di * kRowBytes, 0, k2);
             float bk = 0.f;
             if (DIST) {
-                u64 n = 0ull;
+                u64 n = zero2();
 #pragma unroll
                 for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
                 bk = -0.5f * sl2 * hsum2(n);
@@ -627,7 +651,7 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
         lds_vec16(a0, 0, k2);
         float bk = 0.f;
         if (DIST) {
-            u64 n = 0ull;
+            u64 n = zero2();
 #pragma unroll
             for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
             bk = -0.5f * sl2 * hsum2(n);
@@ -674,13 +698,13 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
         sumds[r] = 0.f;
         bq[r] = 0.f;
         if (DIST) {
-            u64 n = 0ull;
+            u64 n = zero2();
 #pragma unroll
             for (int i = 0; i < 8; ++i) n = fma2(q[r][i], q[r][i], n);
             bq[r] = -0.5f * hsum2(n) / sl2;
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dq[r][i] = 0ull;
+        for (int i = 0; i < 8; ++i) dq[r][i] = zero2();
     }
 
     CA_PIPE_LOOP({
@@ -756,7 +780,7 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
         lds_vec16(a0, 0, q2);
         float bqj = 0.f;
         if (DIST) {
-            u64 n = 0ull;
+            u64 n = zero2();
 #pragma unroll
             for (int i = 0; i < 8; ++i) n = fma2(q2[i], q2[i], n);
             bqj = -0.5f * sl2 * hsum2(n);
@@ -801,15 +825,15 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
         sumds[r] = 0.f;
         bk[r] = 0.f;
         if (DIST) {
-            u64 n = 0ull;
+            u64 n = zero2();
 #pragma unroll
             for (int i = 0; i < 8; ++i) n = fma2(k[r][i], k[r][i], n);
             bk[r] = -0.5f * hsum2(n) / sl2;
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            dk[r][i] = 0ull;
-            dv[r][i] = 0ull;
+            dk[r][i] = zero2();
+            dv[r][i] = zero2();
         }
     }
 
