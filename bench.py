@@ -55,7 +55,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -198,7 +198,6 @@ def main():
         b.record()
     barrier()
     launches = (lib.ca_probe_launch_count() - n0) // steps
-    clocks = sampler.stop()
     t_steps = [a.elapsed_time(b) * 1e-3 for a, b in ev]
     total = torch.tensor([sum(t_steps)], dtype=torch.float64, device=dev)
     if world > 1:
@@ -233,6 +232,7 @@ def main():
         "bwd_dkdv": lambda: lib.ca_attention_bwd_dkdv(d, P(q), P(k), P(v), P(r), P(stats), P(D), None, P(dk), P(dv), P(sws), st()),
     }
     stage_s = {name: time_stage(fn)[0] for name, fn in stages.items()}
+    clocks = sampler.stop()      # sampled over the timed steps and the per-kernel timing loops
 
     # ---- other configurations of the same shape (not the headline): A materialised, Distance, forward only
     def time_variant(kind_v, want_nz):

@@ -893,7 +893,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
 // Pack kernel: two tensors in the reference layout -> [unit][column][row'][32]
 // with the circular halo along h unrolled, plus (optionally) the two scalar
 // planes [2*unit + {0: stats*log2(e), 1: D}][column][row'].
-// One thread per (row', column, unit, tensor pair).
+// One thread per (row', column, unit, tensor) plus one per (row', column, unit) for the planes.
 // =====================================================================
 struct PackArgs {
     Geo g;
@@ -915,17 +915,17 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
     const Geo& g = a.g;
     const int rr = blockIdx.x * blockDim.x + threadIdx.x;
     const int w = blockIdx.y;
-    const int u = blockIdx.z / a.npairs, pair = blockIdx.z % a.npairs;
+    // z slot: 2*npairs tensor copies per unit, plus one slot for the scalar planes
+    const int slots = 2 * a.npairs + (a.planes ? 1 : 0);
+    const int u = blockIdx.z / slots, slot = blockIdx.z % slots;
     if (rr >= a.Hp) return;
     const bool real_row = rr < g.H + 2 * a.pp;
     const int hs = real_row ? (rr - a.pp + g.H) % g.H : 0;
     const int pix = hs + g.H * w;
     const int64_t orow = ((int64_t)u * g.Wk + w) * a.Hp + rr;
-    float4* dp = reinterpret_cast<float4*>(a.dst[pair] + orow * kRowFloats);
-    dp[8] = make_float4(0.f, 0.f, 0.f, 0.f);                     // padding
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        const float* src = a.src[2 * pair + t];
+    if (slot < 2 * a.npairs) {
+        const int pair = slot >> 1, t = slot & 1;
+        const float* src = a.src[slot];
         float4 c[4];
         if (real_row) {
             if (CPE == 1) {
@@ -947,29 +947,34 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) c[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
+        float4* dp = reinterpret_cast<float4*>(a.dst[pair] + orow * kRowFloats);
 #pragma unroll
         for (int i = 0; i < 4; ++i) dp[4 * t + i] = c[i];
+        if (t == 1) dp[8] = make_float4(0.f, 0.f, 0.f, 0.f);         // padding
+        return;
     }
-    if (a.planes && pair == a.npairs - 1) {
-        float L = 0.f, D = 0.f;
-        if (real_row) {
-            const int64_t so = (int64_t)u * g.Npk + pix;
-            L = __ldg(a.stats + so) * kLog2e;
-            if (a.Din) {
-                D = __ldg(a.Din + so);
-            } else {
+    float L = 0.f, D = 0.f;
+    if (real_row) {
+        const int64_t so = (int64_t)u * g.Npk + pix;
+        L = __ldg(a.stats + so) * kLog2e;
+        if (a.Din) {
+            D = __ldg(a.Din + so);
+        } else {
+            float dyv[16], yv[16];
 #pragma unroll
-                for (int cc = 0; cc < 16; ++cc) {
-                    const int64_t o = goff<CPE>(u, cc, g.Npk, pix);
-                    D = fmaf(__ldg(a.dy + o), __ldg(a.y + o), D);
-                }
-                if (a.Dout && rr >= a.pp && rr < a.pp + g.H) a.Dout[so] = D;
+            for (int cc = 0; cc < 16; ++cc) {
+                const int64_t o = goff<CPE>(u, cc, g.Npk, pix);
+                dyv[cc] = __ldg(a.dy + o);
+                yv[cc] = __ldg(a.y + o);
             }
+#pragma unroll
+            for (int cc = 0; cc < 16; ++cc) D = fmaf(dyv[cc], yv[cc], D);
+            if (a.Dout && rr >= a.pp && rr < a.pp + g.H) a.Dout[so] = D;
         }
-        const int64_t plane = (int64_t)g.Wk * a.Hp;
-        a.planes[(2 * (int64_t)u) * plane + (int64_t)w * a.Hp + rr] = L;
-        a.planes[(2 * (int64_t)u + 1) * plane + (int64_t)w * a.Hp + rr] = D;
     }
+    const int64_t plane = (int64_t)g.Wk * a.Hp;
+    a.planes[(2 * (int64_t)u) * plane + (int64_t)w * a.Hp + rr] = L;
+    a.planes[(2 * (int64_t)u + 1) * plane + (int64_t)w * a.Hp + rr] = D;
 }
 
 // ---------------------------------------------------------------- host side
@@ -1007,7 +1012,7 @@ int pick_dc(int ws) {
 }
 
 int launch_pack(const PackArgs& a, cudaStream_t st) {
-    dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * a.npairs);
+    dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * (2 * a.npairs + (a.planes ? 1 : 0)));
     if (a.g.cpe == 1) pack_kernel<1><<<grid, 128, 0, st>>>(a);
     else pack_kernel<2><<<grid, 128, 0, st>>>(a);
     CA_CHECK_LAUNCH("pack kernel");
