@@ -47,11 +47,12 @@ PROTOTYPES = {
     "ca_version": (C.c_int, []),
     "ca_last_error": (C.c_char_p, []),
     "ca_structure": (C.c_int, [_i32, _i32, _i32, _i32, _i64, _p, _p, _p]),
-    "ca_similarity": (C.c_int, [_D, _p, _p, _p, _p]),
-    "ca_similarity_bwd": (C.c_int, [_D, _p, _p, _p, _p, _p, _p]),
+    "ca_operator_workspace": (C.c_size_t, [_D]),
+    "ca_similarity": (C.c_int, [_D, _p, _p, _p, _p, _p]),
+    "ca_similarity_bwd": (C.c_int, [_D, _p, _p, _p, _p, _p, _p, _p]),
     "ca_row_normalize": (C.c_int, [_D, _p, _p, _p, _p]),
     "ca_row_normalize_bwd": (C.c_int, [_D, _p, _p, _p, _p]),
-    "ca_apply": (C.c_int, [_D, _p, _p, _p, _i32, _i32, _i32, _p]),
+    "ca_apply": (C.c_int, [_D, _p, _p, _p, _i32, _i32, _i32, _p, _p]),
     "ca_attention_fwd_workspace": (C.c_size_t, [_D, _i32]),
     "ca_attention_fwd": (C.c_int, [_D, _p, _p, _p, _p, _p, _p, _p, _p]),
     "ca_static_scratch_bytes": (C.c_size_t, []),

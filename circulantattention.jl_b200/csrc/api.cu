@@ -197,24 +197,36 @@ int ca_structure(int32_t H, int32_t W, int32_t ndim, int32_t ws, int64_t nbatch,
     return CA_OK;
 }
 
-int ca_similarity(const ca_desc* d, const void* x, const void* y, float* nz, void* stream) {
+size_t ca_operator_workspace(const ca_desc* d) {
+    Geo g;
+    if (make_geo(d, &g, false)) return 0;
+    return tiled_operator_workspace(g);
+}
+
+int ca_similarity(const ca_desc* d, const void* x, const void* y, float* nz, void* workspace, void* stream) {
     Geo g;
     int rc = make_geo(d, &g, false);
     if (rc) return rc;
     if (!x || !y || !nz) { set_error("x/y/nz is NULL"); return CA_ERR_NULL; }
     if ((rc = check_nnz(g))) return rc;
+    rc = tiled_similarity(g, d->scale, d->similarity == CA_DISTANCE, (const float*)x, (const float*)y, nz, workspace,
+                          as_stream(stream));
+    if (rc != CA_ERR_UNSUPPORTED) return rc;
     return launch_similarity(g, d->scale, d->similarity == CA_DISTANCE, (const float*)x, (const float*)y, nz,
                              as_stream(stream));
 }
 
 int ca_similarity_bwd(const ca_desc* d, const void* x, const void* y, const float* dS,
-                      void* dx, void* dy, void* stream) {
+                      void* dx, void* dy, void* workspace, void* stream) {
     Geo g;
     int rc = make_geo(d, &g, false);
     if (rc) return rc;
     if (!x || !y || !dS) { set_error("x/y/dS is NULL"); return CA_ERR_NULL; }
     const bool dist = d->similarity == CA_DISTANCE;
     cudaStream_t st = as_stream(stream);
+    rc = tiled_similarity_bwd(g, d->scale, dist, (const float*)x, (const float*)y, dS, (float*)dx, (float*)dy,
+                              workspace, st);
+    if (rc != CA_ERR_UNSUPPORTED) return rc;
     if (dx && (rc = launch_apply(g, dS, (const float*)y, dist ? (const float*)x : nullptr, (float*)dx,
                                  d->scale, 0, 0, 0, st))) return rc;
     if (dy && (rc = launch_apply(g, dS, (const float*)x, dist ? (const float*)y : nullptr, (float*)dy,
@@ -244,23 +256,31 @@ int ca_row_normalize_bwd(const ca_desc* d, const float* p, const float* dp, floa
 }
 
 int ca_apply(const ca_desc* d, const float* nz, const void* v, void* out,
-             int32_t transpose, int32_t a_bcast, int32_t v_bcast, void* stream) {
+             int32_t transpose, int32_t a_bcast, int32_t v_bcast, void* workspace, void* stream) {
     Geo g;
     int rc = make_geo(d, &g, false);
     if (rc) return rc;
     if (!nz || !v || !out) { set_error("nz/v/out is NULL"); return CA_ERR_NULL; }
-    if (!a_bcast && !v_bcast && !transpose) {
-        rc = tiled_apply(g, nz, (const float*)v, (float*)out, as_stream(stream));
+    if (!a_bcast && !v_bcast) {
+        rc = tiled_apply(g, nz, (const float*)v, (float*)out, 1.f, transpose != 0, workspace, as_stream(stream));
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
     return launch_apply(g, nz, (const float*)v, nullptr, (float*)out, 1.f, transpose, a_bcast, v_bcast,
                         as_stream(stream));
 }
 
+static size_t score_bytes(const Geo& g) {
+    return (((size_t)g.Np * g.K * g.units * sizeof(float)) + 255) & ~(size_t)255;
+}
+
 size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {
     Geo g;
     if (make_geo(d, &g, true)) return 0;
-    if (d->normalizer == CA_ENTMAX15) return want_nz ? 0 : (size_t)g.Np * g.K * g.units * sizeof(float);
+    if (d->normalizer == CA_ENTMAX15) {
+        // scores (unless they are written to nz) followed by the packed operand of the tiled operators
+        const bool band = g.Wk != g.W;
+        return (want_nz ? 0 : score_bytes(g)) + (band ? 0 : tiled_operator_workspace(g));
+    }
     const bool band = g.Wk != g.W;
     return (want_nz && band) ? 0 : tiled_fwd_workspace(g);
 }
@@ -283,9 +303,14 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
         if ((rc = check_nnz(g))) return rc;
         float* sbuf = nz ? nz : (float*)workspace;
         if (!sbuf) { set_error("entmax without nz needs a workspace of ca_attention_fwd_workspace() bytes"); return CA_ERR_NULL; }
-        if ((rc = launch_similarity(g, d->scale, dist, (const float*)q, (const float*)k, sbuf, st))) return rc;
+        void* opws = (workspace && tiled_operator_workspace(g))
+                         ? (void*)((char*)workspace + (nz ? 0 : score_bytes(g))) : nullptr;
+        rc = tiled_similarity(g, d->scale, dist, (const float*)q, (const float*)k, sbuf, opws, st);
+        if (rc == CA_ERR_UNSUPPORTED)
+            rc = launch_similarity(g, d->scale, dist, (const float*)q, (const float*)k, sbuf, st);
+        if (rc) return rc;
         if ((rc = launch_row_normalize((int64_t)g.Np * g.units, g.K, 1, sbuf, sbuf, stats, st))) return rc;
-        rc = tiled_apply(g, sbuf, (const float*)v, (float*)y, st);
+        rc = tiled_apply(g, sbuf, (const float*)v, (float*)y, 1.f, 0, opws, st);
         if (rc != CA_ERR_UNSUPPORTED) return rc;
         return launch_apply(g, sbuf, (const float*)v, nullptr, (float*)y, 1.f, 0, 0, 0, st);
     }

@@ -112,6 +112,7 @@ struct TileArgs {
     int roff;               // p' - p: first window row inside a stage buffer
     int stage_bytes;        // bytes of one stage buffer (multiple of 1024)
     int nsplit;             // 1 or 2 groups of warps sharing the stages of a tile
+    int which;              // half of the packed pair a single-tensor kernel streams (0 or 1)
     const float* c0;        // centre tensors (reference layout)
     const float* c1;
     const float* cs0;       // centre scalars (dq kernel: stats, D)
@@ -529,7 +530,9 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
 
 // =====================================================================
 // A in CSR order.  Second sweep over the same packed (k|v) stages: with the
-// saved log-sum-exp the normalised entry is P = 2^(q.k - L) directly.  A thread
+// saved log-sum-exp the normalised entry is P = 2^(q.k - L) directly; without
+// row statistics (cs0 == NULL) the kernel writes the scaled scores themselves,
+// which is the stand-alone similarity operator.  A thread
 // produces, per stage, the ws entries of one (row, window column) run, which
 // are contiguous in the row's CSR segment; a warp stages its 32 rows x ws run
 // in shared memory and writes it out with consecutive lanes on consecutive
@@ -550,6 +553,7 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
     // per-warp staging tile [4][32][ws] after the stage buffers
     float* tile = reinterpret_cast<float*>(smem_al + (size_t)a.nsplit * kStages * a.stage_bytes) + (size_t)warp * 128 * g.ws;
 
+    const bool raw = a.cs0 == nullptr;
     u64 q[4][8];
     load_centre<CPE, 4>(a.c0, g, u, h, w0, active, sl2, q);
     u64 nL2[4];
@@ -557,7 +561,7 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
         const bool ok = active && (w0 + r < g.W);
-        nL2[r] = pack2(ok ? -__ldg(a.cs0 + (int64_t)u * g.Np + h + g.H * (w0 + r)) * kLog2e : 0.f, 0.f);
+        nL2[r] = pack2((ok && !raw) ? -__ldg(a.cs0 + (int64_t)u * g.Np + h + g.H * (w0 + r)) * kLog2e : 0.f, 0.f);
         bq[r] = 0.f;
         if (DIST) {
             u64 n = zero2();
@@ -598,7 +602,10 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
                 for (int r = 0; r < 4; ++r) t[r] = fma2(q[r][i], k2[i], t[r]);
 #pragma unroll
             for (int r = 0; r < 4; ++r)
-                if (active) tile[(r * 32 + lane) * g.ws + posh] = fast_exp2(hsum2(t[r]));
+                if (active) {
+                    const float sc = hsum2(t[r]);
+                    tile[(r * 32 + lane) * g.ws + posh] = raw ? sc * kLn2 : fast_exp2(sc);
+                }
         }
         __syncwarp();
         // write the runs of this stage: row j, positions posw*ws .. posw*ws + ws - 1
@@ -621,6 +628,162 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
         }
         __syncwarp();
     })
+}
+
+// =====================================================================
+// A (x) V and A^T (x) V from stored values.  The dense operand is streamed as
+// packed column stages exactly like the keys of the forward; the values of A
+// that pair with a stage are, for every centre column r, one run of ws
+// consecutive entries per CSR row (window column fixed, window rows varying),
+// which a warp copies into shared memory before the stage's FMAs:
+//   plain     : rows = the warp's own 32 pixels, run at posw(s - p - r; w0 + r);
+//   transposed: rows = the 32 + 2p pixels of the streamed column around the warp
+//               (by window symmetry A[j, i] sits in row j at offset i - j), run at
+//               posw(r + p - s; streamed column).
+// out = alpha * (sum_e a_e v_e - (sum_e a_e) * centre) with centre optional: the
+// second term is the Distance similarity pullback.
+// =====================================================================
+// Four-byte asynchronous copy global -> shared (the runs of A are only 4-byte aligned).
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int CPE, bool TRANS>
+__global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+                                                             const __grid_constant__ CUtensorMap msc) {
+    const Geo& g = a.g;
+    const int ROWS = a.TH + 2 * (g.p + a.roff);
+    const int NS = g.ws + 3;
+    const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
+    CA_PIPE_PROLOGUE(false)
+    const int lr = lt, h = h0 + lr;
+    const bool active = h < g.H;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int TR = 32 + (TRANS ? 2 * g.p : 0);                 // CSR rows staged per warp and centre column
+    const int tile_floats = 4 * TR * g.ws;                     // one buffer: [4 centre columns][TR][ws]
+    // per warp: two tile buffers and the table of element offsets (row * K + e) inside a run block
+    float* wbase = reinterpret_cast<float*>(smem_al + (size_t)kStages * a.stage_bytes) +
+                   (size_t)warp * (2 * tile_floats + TR * g.ws);
+    int* offs = reinterpret_cast<int*>(wbase + 2 * tile_floats);
+    const int hw0 = h0 + (lr & ~31);                           // first image row of this warp
+    const float* nzu = a.cs0 + (int64_t)u * g.Np * g.K;
+    const int nrows = hw0 >= g.H ? 0 : (TRANS ? TR : min(32, g.H - hw0));
+    const int n = nrows * g.ws;
+    for (int idx = lane; idx < n; idx += 32) {
+        const int row = idx / g.ws, e = idx - row * g.ws;
+        int gr = hw0 + row - (TRANS ? g.p : 0);
+        gr %= g.H;
+        if (gr < 0) gr += g.H;
+        offs[idx] = gr * g.K + e;
+    }
+    __syncwarp();
+
+    // starts the copies of the runs that pair with stage s into tile buffer tb
+    auto fetch_runs = [&](int s, int tb) {
+        const int mask = stage_mask<4>(s, g.p);
+        const int wc = stage_column(g, w0, s);
+        float* tbuf = wbase + tb * tile_floats;
+#pragma unroll 1
+        for (int r = 0; r < 4; ++r) {
+            if (!((mask >> r) & 1) || w0 + r >= g.W) continue;
+            const int posw = TRANS ? axis_pos(r + g.p - s, wc, g.W, g.p, g.ws)
+                                   : axis_pos(s - g.p - r, w0 + r, g.W, g.p, g.ws);
+            const float* src = nzu + (int64_t)g.H * (TRANS ? wc : w0 + r) * g.K + posw * g.ws;
+            float* dst = tbuf + r * TR * g.ws;
+#pragma unroll 4
+            for (int idx = lane; idx < n; idx += 32) cp_async4(dst + idx, src + offs[idx]);
+        }
+        cp_async_commit();
+    };
+
+    u64 acc[4][8];
+    float asum[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        asum[r] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[r][i] = zero2();
+    }
+    const int hrot = (h < g.p) ? h - g.p + g.ws : (h >= g.H - g.p ? h - g.p - g.H + g.ws : 0);
+    fetch_runs(s_begin, 0);
+
+    CA_PIPE_LOOP({
+        const int mask = stage_mask<4>(s, g.p);
+        if (s + 1 < s_end) {
+            fetch_runs(s + 1, (it + 1) & 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        const float* tile = wbase + (it & 1) * tile_floats;
+        const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes;
+        // operands of window row di: the streamed vector and the four values of A; fetched one
+        // row ahead of the FMAs that use them
+        auto fetch_row = [&](int di, u64 (&vv)[8], float (&aa)[4]) {
+            lds_vec16(rowbase + di * kRowBytes, a.which, vv);
+            int posh, trow;
+            if (!TRANS) {
+                posh = di + hrot;
+                posh -= (posh >= g.ws) ? g.ws : 0;
+                trow = lane;
+            } else {
+                int hj = (active ? h : g.H - 1) + di - g.p;        // the row pixel of the entry (lanes past the image stay in range)
+                hj += (hj < 0) ? g.H : 0;
+                hj -= (hj >= g.H) ? g.H : 0;
+                posh = axis_pos(g.p - di, hj, g.H, g.p, g.ws);
+                trow = lane + di;
+            }
+            const float* ap = tile + trow * g.ws + posh;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) aa[r] = ((mask >> r) & 1) ? ap[r * TR * g.ws] : 0.f;
+        };
+        u64 vn[8];
+        float an[4];
+        fetch_row(0, vn, an);
+#pragma unroll 2
+        for (int di = 0; di < g.ws; ++di) {
+            u64 v2[8];
+            float av[4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v2[i] = vn[i];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) av[r] = an[r];
+            if (di + 1 < g.ws) fetch_row(di + 1, vn, an);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                if ((mask >> r) & 1) {
+                    asum[r] += av[r];
+                    const u64 a2 = pack2(av[r], av[r]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[r][i] = fma2(a2, v2[i], acc[r][i]);
+                }
+            }
+        }
+        __syncwarp();
+    })
+
+    if (a.c0) {
+        u64 ctr[4][8];
+        load_centre<CPE, 4>(a.c0, g, u, h, w0, active, 1.f, ctr);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const u64 ns = pack2(-asum[r], -asum[r]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[r][i] = fma2(ns, ctr[r][i], acc[r][i]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float x, y;
+            unpack2(acc[r][i], x, y);
+            store_centre<CPE>(a.o0, g, u, h, w0, active, r, i, a.scale * x, a.scale * y);
+        }
 }
 
 // =====================================================================
@@ -1043,13 +1206,14 @@ int sm_count() {
 // thread for the merge of a split tile.  CTAs have at most 128 threads: four
 // warps of rows, or two warps of rows times two stage groups on small grids.
 int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* env_warps, const float* pair,
-            const float* planes, Launch* L) {
+            const float* planes, Launch* L, bool allow_split = true, int max_warps = 4) {
     int warps = (g.H + 31) / 32;
-    if (warps > 4) warps = 4;
+    if (warps > max_warps) warps = max_warps;
     const long cols = (g.W + nq - 1) / nq;
     const long ctas4 = cols * ((g.H + 32 * warps - 1) / (32 * warps)) * g.units;
     int nsplit = (ctas4 * warps < 6L * sm_count()) ? 2 : 1;
     nsplit = env_int("CIRCATT_SPLIT", nsplit);
+    if (!allow_split) nsplit = 1;
     if (nsplit == 2 && warps > 2) warps = 2;
     warps = env_int(env_warps, warps);
     if (warps * nsplit > 4) warps = 4 / nsplit;
@@ -1379,6 +1543,72 @@ int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, con
     return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st);
 }
 
-int tiled_apply(const Geo&, const float*, const float*, float*, cudaStream_t) { return CA_ERR_UNSUPPORTED; }
+// ---------------------------------------------------------------- stand-alone operators
+size_t tiled_operator_workspace(const Geo& g) {
+    if (!tiled_shape_ok(g) || g.Wk != g.W) return 0;
+    return padded_of(g).pair_floats * sizeof(float);
+}
+
+static int pack_pair(const Geo& g, const Padded& P, const float* first, const float* second, float* dst,
+                     cudaStream_t st) {
+    PackArgs pa{};
+    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1;
+    pa.src[0] = first; pa.src[1] = second; pa.dst[0] = dst;
+    return launch_pack(pa, st);
+}
+
+// Scaled similarity scores in CSR order: x indexes the row pixel, y the column pixel.
+int tiled_similarity(const Geo& g, float scale, int dist, const float* x, const float* y, float* nz,
+                     void* workspace, cudaStream_t st) {
+    if (!workspace || !tiled_operator_workspace(g)) return CA_ERR_UNSUPPORTED;
+    int rc = pack_pair(g, padded_of(g), y, y, static_cast<float*>(workspace), st);
+    if (rc) return rc;
+    return tiled_emit_a(g, scale, dist, x, nullptr, nz, workspace, st);
+}
+
+static int run_apply(const Geo& g, const Padded& P, const float* nz, const float* pair, int which,
+                     const float* centre, float* out, float alpha, int transposed, cudaStream_t st) {
+    Launch L{};
+    int rc = prepare(g, P, 4, 0, "CIRCATT_APPLY_WARPS", pair, nullptr, &L, false, 2);
+    if (rc) return rc;
+    const int TR = 32 + (transposed ? 2 * g.p : 0);
+    L.smem += (size_t)L.threads / 32 * 9 * TR * g.ws * sizeof(float);     // two tile buffers + offsets per warp
+    if (L.smem > 200 * 1024) return CA_ERR_UNSUPPORTED;
+    L.a.scale = alpha; L.a.which = which; L.a.c0 = centre; L.a.cs0 = nz; L.a.o0 = out;
+    if (g.cpe == 1) {
+        if (transposed) CA_LAUNCH_TILED((apply_tiled_kernel<1, true>), L, st);
+        else CA_LAUNCH_TILED((apply_tiled_kernel<1, false>), L, st);
+    } else {
+        if (transposed) CA_LAUNCH_TILED((apply_tiled_kernel<2, true>), L, st);
+        else CA_LAUNCH_TILED((apply_tiled_kernel<2, false>), L, st);
+    }
+    CA_CHECK_LAUNCH("tiled apply kernel");
+    return CA_OK;
+}
+
+// out = alpha * (A (x) v) or alpha * (A^T (x) v) from the values of A in CSR order.
+int tiled_apply(const Geo& g, const float* nz, const float* v, float* out, float alpha, int transposed,
+                void* workspace, cudaStream_t st) {
+    if (!workspace || !tiled_operator_workspace(g)) return CA_ERR_UNSUPPORTED;
+    const Padded P = padded_of(g);
+    float* pair = static_cast<float*>(workspace);
+    int rc = pack_pair(g, P, v, v, pair, st);
+    if (rc) return rc;
+    return run_apply(g, P, nz, pair, 0, nullptr, out, alpha, transposed, st);
+}
+
+// Pullback of the similarity: dx[j] = scale * sum_i dS[j,i] y[i], dy[i] = scale * sum_j dS[j,i] x[j]
+// (Distance: minus the sum of the dS involved times the pixel's own vector).
+int tiled_similarity_bwd(const Geo& g, float scale, int dist, const float* x, const float* y, const float* dS,
+                         float* dx, float* dy, void* workspace, cudaStream_t st) {
+    if (!workspace || !tiled_operator_workspace(g)) return CA_ERR_UNSUPPORTED;
+    const Padded P = padded_of(g);
+    float* pair = static_cast<float*>(workspace);
+    int rc = pack_pair(g, P, y, x, pair, st);
+    if (rc) return rc;
+    if (dx && (rc = run_apply(g, P, dS, pair, 0, dist ? x : nullptr, dx, scale, 0, st))) return rc;
+    if (dy && (rc = run_apply(g, P, dS, pair, 1, dist ? y : nullptr, dy, scale, 1, st))) return rc;
+    return CA_OK;
+}
 
 }  // namespace ca

@@ -25,6 +25,15 @@ int tiled_attention_bwd_dkdv(const Geo& g, float scale, int dist, const float* q
                              void* workspace, cudaStream_t st);
 // Copies the count of stage-copy timeouts to the host (synchronises the device).
 int tiled_stage_timeouts(int* count);
-int tiled_apply(const Geo& g, const float* nz, const float* v, float* out, cudaStream_t st);
+
+// Stand-alone operators on the tiled kernels.  `workspace` holds one packed
+// tensor pair (tiled_operator_workspace bytes, 0 when the shape is not covered).
+size_t tiled_operator_workspace(const Geo& g);
+int tiled_similarity(const Geo& g, float scale, int dist, const float* x, const float* y, float* nz,
+                     void* workspace, cudaStream_t st);
+int tiled_apply(const Geo& g, const float* nz, const float* v, float* out, float alpha, int transposed,
+                void* workspace, cudaStream_t st);
+int tiled_similarity_bwd(const Geo& g, float scale, int dist, const float* x, const float* y, const float* dS,
+                         float* dx, float* dy, void* workspace, cudaStream_t st);
 
 }  // namespace ca

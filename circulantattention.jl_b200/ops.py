@@ -83,6 +83,12 @@ def structure(spatial, ws, batch, device):
     return rowptr, colval
 
 
+def _operator_workspace(d, device):
+    """Scratch of ca_operator_workspace() bytes, or None when the shape runs on the generic kernels."""
+    n = lib.ca_operator_workspace(d)
+    return torch.empty(n, dtype=torch.uint8, device=device) if n else None
+
+
 def similarity(kind, x, y, ws, scale=1.0):
     require_cuda(x, y)
     x, y = _dense_ok(x), _dense_ok(y)
@@ -90,7 +96,8 @@ def similarity(kind, x, y, ws, scale=1.0):
     nz = jl.empty((m.Np * m.K, m.units), torch.float32, x.device)
     d = m.desc(similarity=kind, scale=scale)
     with torch.cuda.device(x.device):
-        check(lib.ca_similarity(d, ptr(x), ptr(y), ptr(nz), _stream()))
+        ws_buf = _operator_workspace(d, x.device)
+        check(lib.ca_similarity(d, ptr(x), ptr(y), ptr(nz), ptr(ws_buf), _stream()))
     return nz
 
 
@@ -101,7 +108,8 @@ def similarity_bwd(kind, x, y, ws, dS, scale=1.0):
     dx, dy = jl.empty(x.shape, x.dtype, x.device), jl.empty(y.shape, y.dtype, y.device)
     d = m.desc(similarity=kind, scale=scale)
     with torch.cuda.device(x.device):
-        check(lib.ca_similarity_bwd(d, ptr(x), ptr(y), ptr(dS), ptr(dx), ptr(dy), _stream()))
+        ws_buf = _operator_workspace(d, x.device)
+        check(lib.ca_similarity_bwd(d, ptr(x), ptr(y), ptr(dS), ptr(dx), ptr(dy), ptr(ws_buf), _stream()))
     return dx, dy
 
 
@@ -146,8 +154,9 @@ def apply(nz, v, ws, transpose=False, out=None):
         out = jl.empty(tuple(v.shape[:-1]) + (units,), v.dtype, v.device)
     d = m.desc(units=units)
     with torch.cuda.device(v.device):
+        ws_buf = _operator_workspace(d, v.device)
         check(lib.ca_apply(d, ptr(nz), ptr(v), ptr(out), int(transpose), int(ua == 1 and units > 1),
-                           int(m.units == 1 and units > 1), _stream()))
+                           int(m.units == 1 and units > 1), ptr(ws_buf), _stream()))
     return out
 
 

@@ -83,17 +83,25 @@ const char* ca_last_error(void);
 int ca_structure(int32_t H, int32_t W, int32_t ndim, int32_t ws, int64_t nbatch,
                  int32_t* rowptr, int32_t* colval, void* stream);
 
+/* ---------------------------------------------------------------- operator workspace
+ * Bytes of caller-owned scratch with which ca_similarity, ca_similarity_bwd and
+ * ca_apply run on the tiled TMA kernels (2-D, 16 real channels per unit); 0 when
+ * the shape is only covered by the generic kernels.  The three calls accept
+ * workspace == NULL and then always use the generic kernels.  No reference
+ * counterpart (the reference's operators allocate through CUDA.jl's pool). */
+size_t ca_operator_workspace(const ca_desc* d);
+
 /* ---------------------------------------------------------------- similarity
  * nz = scale * simfun(x[row pixel], y[column pixel]) for every stored entry.
  * Replaces circulant_similarity_kernel! (src/similarity.jl:55-103) and its
  * launcher (src/similarity.jl:36-53). */
-int ca_similarity(const ca_desc* d, const void* x, const void* y, float* nz, void* stream);
+int ca_similarity(const ca_desc* d, const void* x, const void* y, float* nz, void* workspace, void* stream);
 
 /* Pullback of ca_similarity (src/rrules.jl:1-32):
  *   Dot:      dx = scale * dS Y               dy = scale * dS^T X
  *   Distance: dx = scale * (dS Y - rowsum(dS) X)   dy = scale * (dS^T X - colsum(dS) Y) */
 int ca_similarity_bwd(const ca_desc* d, const void* x, const void* y, const float* dS,
-                      void* dx, void* dy, void* stream);
+                      void* dx, void* dy, void* workspace, void* stream);
 
 /* ---------------------------------------------------------------- row normaliser
  * Row softmax (src/similarity.jl:105-126; NNlib.softmax! over each row's K
@@ -113,7 +121,7 @@ int ca_row_normalize_bwd(const ca_desc* d, const float* p, const float* dp, floa
  * src/batchedmul.jl:43-80).  a_bcast / v_bcast != 0 mean that A / v hold one
  * unit that is shared by all d->units outputs. */
 int ca_apply(const ca_desc* d, const float* nz, const void* v, void* out,
-             int32_t transpose, int32_t a_bcast, int32_t v_bcast, void* stream);
+             int32_t transpose, int32_t a_bcast, int32_t v_bcast, void* workspace, void* stream);
 
 /* ---------------------------------------------------------------- fused attention
  * y = rownormalize(scale * simfun(q, k)) (x) v  in one pass

@@ -116,14 +116,21 @@ function Base.cat(As::Circulant{T,N,M}...; dims=3) where {T,N,M}      # works, u
 end
 
 # ------------------------------------------------------------------ similarity / normaliser (src/similarity.jl)
+# Scratch with which the stand-alone operators run on the tiled kernels (an empty buffer, i.e. a
+# NULL device pointer, selects the generic kernels).
+operator_workspace(d::CaDesc) = CuArray{UInt8}(undef, Int(ccall((:ca_operator_workspace, LIB), Csize_t, (Ref{CaDesc},), d)))
+
 function circulant_similarity!(A::Circulant, simfun::AbstractSimilarity, x::AnyCuArray{Tx,N}, y) where {Tx,N}
     S = spatial_dims(A)
     @assert S == N - 2 "spatial_dims ($(S)) of circulant matrix must match those of data signal ($(N-2))."
     nb = prod(size(A)[3:end])
     @assert nb == size(x, N) "batchdim of circulant matrix ($nb) must match that of x, y ($(size(x,N)))."
     d = desc(x, kernel_length(A); sim=simcode(simfun))
-    check(ccall((:ca_similarity, LIB), Cint, (Ref{CaDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Float32}, Ptr{Cvoid}),
-                d, x, y, nzval(A), stream()))
+    ws = operator_workspace(d)
+    check(ccall((:ca_similarity, LIB), Cint,
+                (Ref{CaDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Float32}, CuPtr{Cvoid}, Ptr{Cvoid}),
+                d, x, y, nzval(A), ws, stream()))
+    CUDA.unsafe_free!(ws)
     return A
 end
 
@@ -151,9 +158,11 @@ function apply!(y::AbstractArray{T,N}, A::Circulant, x::AbstractArray{T,N}, tran
     ua, ux = prod(size(A)[3:end]), size(x, N)
     units = max(ua, ux)
     d = desc(x, kernel_length(A); units=units)
+    ws = operator_workspace(d)
     check(ccall((:ca_apply, LIB), Cint,
-                (Ref{CaDesc}, CuPtr{Float32}, CuPtr{Cvoid}, CuPtr{Cvoid}, Int32, Int32, Int32, Ptr{Cvoid}),
-                d, nzval(A), x, y, transpose, ua == 1 && units > 1, ux == 1 && units > 1, stream()))
+                (Ref{CaDesc}, CuPtr{Float32}, CuPtr{Cvoid}, CuPtr{Cvoid}, Int32, Int32, Int32, CuPtr{Cvoid}, Ptr{Cvoid}),
+                d, nzval(A), x, y, transpose, ua == 1 && units > 1, ux == 1 && units > 1, ws, stream()))
+    CUDA.unsafe_free!(ws)
     return y
 end
 circulant_attention!(y, A::Circulant, x) = apply!(y, A, x, false)

@@ -62,14 +62,14 @@ def test_bad_descriptors_are_rejected_on_the_host(ca, kw, code, msg):
     from circatt_b200._lib import lib, last_error
     d = _desc(ca, **kw)
     one = C.c_void_p(16)        # never dereferenced: validation comes first
-    rc = lib.ca_similarity(d, one, one, one, None)
+    rc = lib.ca_similarity(d, one, one, one, None, None)
     assert rc == code
     assert msg in last_error()
 
 
 def test_null_pointers_are_rejected(ca):
     from circatt_b200._lib import lib, last_error
-    assert lib.ca_similarity(_desc(ca), None, None, None, None) == -3
+    assert lib.ca_similarity(_desc(ca), None, None, None, None, None) == -3
     assert "NULL" in last_error()
     assert lib.ca_attention_bwd_workspace(_desc(ca)) == 8 * 8 * 2 * 4
     assert lib.ca_attention_fwd_workspace(_desc(ca, normalizer=1), 0) == 64 * 25 * 2 * 4

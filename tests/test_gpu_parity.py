@@ -152,7 +152,8 @@ def test_deterministic_gradients(ca):
 
 # ------------------------------------------------------------------ entmax (no reference counterpart)
 @pytest.mark.parametrize("want_A", [True, False])
-@pytest.mark.parametrize("shape,ws,nheads,simname", [((64, 16, 2), 15, 2, "distance"), ((12, 11, 8, 1), 5, 2, "dot")])
+@pytest.mark.parametrize("shape,ws,nheads,simname", [((64, 16, 2), 15, 2, "distance"), ((12, 11, 8, 1), 5, 2, "dot"),
+                                                     ((40, 24, 32, 1), 7, 2, "distance")])
 def test_entmax_attention(ca, shape, ws, nheads, simname, want_A):
     rng = np.random.default_rng(5)
     qn, kn, vn, rn = (randn(rng, shape, scale=1.5) for _ in range(4))
@@ -243,6 +244,52 @@ def test_apply_and_pullback(ca, spatial, transpose, cplx):
         dbo = orc.apply(nz64, up(dcn), ws, False)
     assert rel_err(ca.jl.to_numpy(A.nzVal.grad), dAo) < TOL
     assert rel_err(ca.jl.to_numpy(b.grad), dbo) < TOL
+
+
+TILED_OPERATOR_CASES = [
+    # (spatial, ws, channels, units, cplx): 16 real channels per unit -> the TMA-tiled operator kernels
+    ((37, 29), 9, 16, 2, False),        # ragged tiles
+    ((40, 21), 7, 8, 2, True),          # 8 complex channels
+    ((16, 9), 9, 16, 1, False),         # smallest tile, extent == window along w
+    ((128, 24), 21, 16, 1, False),      # full-height tile, window 21
+    ((70, 10), 5, 16, 3, False),        # three warps of rows, W not a multiple of the four-column tile
+    ((64, 48), 15, 16, 4, False),       # quarter-size BASELINE config 2
+]
+
+
+@pytest.mark.parametrize("simname", ["dot", "distance"])
+@pytest.mark.parametrize("spatial,ws,c,units,cplx", TILED_OPERATOR_CASES)
+def test_tiled_similarity_and_pullback(ca, spatial, ws, c, units, cplx, simname):
+    """R3/R4 and their rrules (src/similarity.jl:55-103, src/rrules.jl:1-32) on the tiled kernels."""
+    rng = np.random.default_rng(21)
+    shape = spatial + (c, units)
+    xn, yn = randn(rng, shape, cplx), randn(rng, shape, cplx)
+    x, y = ca.jl.from_numpy(xn), ca.jl.from_numpy(yn)
+    m = ca.ops.meta_of(x, ws)
+    assert ca._lib.lib.ca_operator_workspace(m.desc()) > 0           # the shape is covered by the tiled kernels
+    scale = 0.37
+    S = ca.ops.similarity(KIND[simname], x, y, ws, scale)
+    So = scale * orc.similarity(KIND[simname], up(xn), up(yn), ws)
+    assert rel_err(ca.jl.to_numpy(S), So.reshape(S.shape, order="F")) < TOL
+    dSn = np.asfortranarray(rng.standard_normal(tuple(S.shape)).astype(np.float32))
+    dx, dy = ca.ops.similarity_bwd(KIND[simname], x, y, ws, ca.jl.from_numpy(dSn), scale)
+    dxo, dyo = orc.similarity_pullback(KIND[simname], up(xn), up(yn), ws,
+                                       scale * dSn.astype(np.float64).reshape(So.shape, order="F"))
+    assert rel_err(ca.jl.to_numpy(dx), dxo) < TOL
+    assert rel_err(ca.jl.to_numpy(dy), dyo) < TOL
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+@pytest.mark.parametrize("spatial,ws,c,units,cplx", TILED_OPERATOR_CASES)
+def test_tiled_apply(ca, spatial, ws, c, units, cplx, transpose):
+    """R6 (src/batchedmul.jl:82-150 as used by src/attention.jl:53-80) on the tiled kernels."""
+    rng = np.random.default_rng(22)
+    K, Np = ws ** 2, int(np.prod(spatial))
+    nzn = np.asfortranarray(rng.standard_normal((Np * K, units)).astype(np.float32))
+    vn = randn(rng, spatial + (c, units), cplx)
+    out = ca.ops.apply(ca.jl.from_numpy(nzn), ca.jl.from_numpy(vn), ws, transpose)
+    oo = orc.apply(nzn.astype(np.float64).reshape((K, Np, units), order="F"), up(vn), ws, transpose)
+    assert rel_err(ca.jl.to_numpy(out), oo) < TOL
 
 
 def test_readme_identity_and_mh_apply(ca):
