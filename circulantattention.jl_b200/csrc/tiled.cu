@@ -113,6 +113,7 @@ struct TileArgs {
     int stage_bytes;        // bytes of one stage buffer (multiple of 1024)
     int nsplit;             // 1 or 2 groups of warps sharing the stages of a tile
     int which;              // half of the packed pair a single-tensor kernel streams (0 or 1)
+    int row_bytes;          // bytes of one packed pixel row: 144 per 16-channel slab
     const float* c0;        // centre tensors (reference layout)
     const float* c1;
     const float* cs0;       // centre scalars (dq kernel: stats, D)
@@ -144,11 +145,28 @@ __device__ __forceinline__ void lds_vec16(uint32_t a0, int which, u64 (&v)[8]) {
     lds128(b + 48, v[6], v[7]);
 }
 
-// Global offset of real channel cc of unit u at pixel pix (npix pixels per plane).
-template <int CPE>
+// Units with 16*NS real channels ("slabs" of 16) pack a pixel row as 36*NS words: the first
+// tensor's channels, then the second's, then 4*NS words of padding.  Inside a tensor's part the
+// order is [4-channel chunk][slab][4]: chunk c of slab s sits 16*(c*NS + s) bytes in, so the NS
+// lanes that share a pixel read consecutive 16-byte pieces, and the row stride (144*NS bytes:
+// 16, 32 or 64 bytes past a multiple of 128) spreads the 8/NS pixels of a 128-bit load phase over
+// distinct bank groups.  NS = 1 is the plain channel order.
+// 16-channel slab `slab` of tensor `which` of the pixel row at shared-space byte address `a0`.
+template <int NS>
+__device__ __forceinline__ void lds_slab16(uint32_t a0, int which, int slab, u64 (&v)[8]) {
+    const uint32_t b = a0 + which * (64 * NS) + slab * 16;
+    lds128(b, v[0], v[1]);
+    lds128(b + 16 * NS, v[2], v[3]);
+    lds128(b + 32 * NS, v[4], v[5]);
+    lds128(b + 48 * NS, v[6], v[7]);
+}
+
+// Global offset of real channel cc of unit u at pixel pix (npix pixels per plane, NCR real
+// channels per unit).
+template <int CPE, int NCR = 16>
 __device__ __forceinline__ int64_t goff(int u, int cc, int npix, int pix) {
-    if (CPE == 1) return ((int64_t)u * 16 + cc) * npix + pix;
-    return (((int64_t)u * 8 + (cc >> 1)) * npix + pix) * 2 + (cc & 1);
+    if (CPE == 1) return ((int64_t)u * NCR + cc) * npix + pix;
+    return (((int64_t)u * (NCR / 2) + (cc >> 1)) * npix + pix) * 2 + (cc & 1);
 }
 
 __device__ __forceinline__ int stage_column(const Geo& g, int w0, int s) {
@@ -182,17 +200,17 @@ struct StagePipe {
     unsigned char* base;     // kStages stage buffers of this part
     const CUtensorMap* mv;
     const CUtensorMap* msc;
-    int ROWS, stage_bytes, u, h0, w0;
+    int ROWS, stage_bytes, row_bytes, u, h0, w0;
 
     __device__ __forceinline__ unsigned char* vec(int buf) const { return base + (size_t)buf * stage_bytes; }
     __device__ __forceinline__ int sstride() const { return (ROWS * 4 + 127) & ~127; }
-    __device__ __forceinline__ int vbytes() const { return (ROWS * kRowBytes + 127) & ~127; }
+    __device__ __forceinline__ int vbytes() const { return (ROWS * row_bytes + 127) & ~127; }
     __device__ __forceinline__ float* sc0(int buf) const { return reinterpret_cast<float*>(vec(buf) + vbytes()); }
     __device__ __forceinline__ float* sc1(int buf) const { return reinterpret_cast<float*>(vec(buf) + vbytes() + sstride()); }
 
     __device__ __forceinline__ void issue(const Geo& g, int s, int buf) const {
         const int kc = stage_column(g, w0, s);
-        mbar_arrive_expect_tx(&full[buf], (uint32_t)(ROWS * kRowBytes + (NSC ? ROWS * 8 : 0)));
+        mbar_arrive_expect_tx(&full[buf], (uint32_t)(ROWS * row_bytes + (NSC ? ROWS * 8 : 0)));
         tma_load_4d(vec(buf), mv, 0, h0, kc, u, &full[buf]);
         if (NSC) {
             tma_load_3d(sc0(buf), msc, h0, kc, 2 * u, &full[buf]);
@@ -202,7 +220,7 @@ struct StagePipe {
 };
 
 // Declares the pipeline of this thread's part and starts the first copies.
-// Needs in scope: a (TileArgs), g, ROWS, u, h0, w0, NS (stages of the tile), mv, msc.
+// Needs in scope: a (TileArgs), g, ROWS, u, h0, w0, NSTAGES (stages of the tile), mv, msc.
 #define CA_PIPE_PROLOGUE(NSCV)                                                                       \
     extern __shared__ unsigned char smem_raw[];                                                      \
     __shared__ __align__(8) uint64_t full_bar[2 * kStages];                                          \
@@ -210,14 +228,15 @@ struct StagePipe {
     const int PT = blockDim.x / a.nsplit;          /* threads per part */                            \
     const int part = threadIdx.x / PT;                                                               \
     const int lt = threadIdx.x - part * PT;                                                          \
-    const int s_begin = part * (NS / a.nsplit);                                                      \
-    const int s_end = (part + 1 == a.nsplit) ? NS : (part + 1) * (NS / a.nsplit);                    \
+    const int s_begin = part * (NSTAGES / a.nsplit);                                                      \
+    const int s_end = (part + 1 == a.nsplit) ? NSTAGES : (part + 1) * (NSTAGES / a.nsplit);                    \
     unsigned char* smem_al = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);            \
     StagePipe<NSCV> pipe;                                                                            \
     pipe.full = full_bar + part * kStages;                                                           \
     pipe.base = smem_al + (size_t)part * kStages * a.stage_bytes;                                    \
     pipe.mv = &mv; pipe.msc = &msc;                                                                  \
-    pipe.ROWS = ROWS; pipe.stage_bytes = a.stage_bytes; pipe.u = u; pipe.h0 = h0; pipe.w0 = w0;      \
+    pipe.ROWS = ROWS; pipe.stage_bytes = a.stage_bytes; pipe.row_bytes = a.row_bytes;                \
+    pipe.u = u; pipe.h0 = h0; pipe.w0 = w0;                                                          \
     if (threadIdx.x == 0) {                                                                          \
         for (int i = 0; i < 2 * kStages; ++i) mbar_init(&full_bar[i], 1);                            \
         s_err = 0;                                                                                   \
@@ -248,9 +267,9 @@ struct StagePipe {
     }
 
 // Loads the 16-channel vectors of the NQ centre pixels of this thread, times `mul`.
-template <int CPE, int NQ>
+template <int CPE, int NQ, int NCR = 16>
 __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int u, int h, int w0, bool active,
-                                            float mul, u64 (&dst)[NQ][8]) {
+                                            float mul, u64 (&dst)[NQ][8], int ch0 = 0) {
 #pragma unroll
     for (int r = 0; r < NQ; ++r) {
         const bool ok = active && (w0 + r < g.W);
@@ -260,10 +279,10 @@ __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int 
             float x = 0.f, y = 0.f;
             if (ok) {
                 if (CPE == 1) {
-                    x = __ldg(src + goff<1>(u, 2 * i, g.Np, pix));
-                    y = __ldg(src + goff<1>(u, 2 * i + 1, g.Np, pix));
+                    x = __ldg(src + goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix));
+                    y = __ldg(src + goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix));
                 } else {
-                    const float2 t = __ldg(reinterpret_cast<const float2*>(src + goff<2>(u, 2 * i, g.Np, pix)));
+                    const float2 t = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, ch0 + 2 * i, g.Np, pix)));
                     x = t.x;
                     y = t.y;
                 }
@@ -273,16 +292,16 @@ __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int 
     }
 }
 
-template <int CPE>
+template <int CPE, int NCR = 16>
 __device__ __forceinline__ void store_centre(float* dst, const Geo& g, int u, int h, int w0, bool active, int r,
-                                             int i, float x, float y) {
+                                             int i, float x, float y, int ch0 = 0) {
     if (!(active && (w0 + r < g.W))) return;
     const int pix = h + g.H * (w0 + r);
     if (CPE == 1) {
-        dst[goff<1>(u, 2 * i, g.Np, pix)] = x;
-        dst[goff<1>(u, 2 * i + 1, g.Np, pix)] = y;
+        dst[goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix)] = x;
+        dst[goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix)] = y;
     } else {
-        *reinterpret_cast<float2*>(dst + goff<2>(u, 2 * i, g.Np, pix)) = make_float2(x, y);
+        *reinterpret_cast<float2*>(dst + goff<2, NCR>(u, ch0 + 2 * i, g.Np, pix)) = make_float2(x, y);
     }
 }
 
@@ -438,7 +457,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
                                                            const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NS = g.ws + NQ - 1;
+    const int NSTAGES = g.ws + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
@@ -538,29 +557,32 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
 // in shared memory and writes it out with consecutive lanes on consecutive
 // addresses, so the 4*K*heads bytes per pixel leave the SM in full sectors.
 // =====================================================================
-template <bool DIST, int CPE>
+template <bool DIST, int CPE, int NS>
 __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                               const __grid_constant__ CUtensorMap msc) {
+    constexpr int RW = 32 / NS;                                // pixel rows per warp: NS lanes share a pixel
+    constexpr int RB = kRowBytes * NS;
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NS = g.ws + 3;
+    const int NSTAGES = g.ws + 3;
     const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
-    const int lr = lt, h = h0 + lr;
-    const bool active = h < g.H;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // per-warp staging tile [4][32][ws] after the stage buffers
-    float* tile = reinterpret_cast<float*>(smem_al + (size_t)a.nsplit * kStages * a.stage_bytes) + (size_t)warp * 128 * g.ws;
+    const int slab = lane % NS, lrow = lane / NS;              // this lane's channel slab and row inside the warp
+    const int lr = (lt >> 5) * RW + lrow, h = h0 + lr;         // row inside the tile, image row
+    const bool active = h < g.H;
+    // per-warp staging tile [4][RW][ws] after the stage buffers
+    float* tile = reinterpret_cast<float*>(smem_al + (size_t)a.nsplit * kStages * a.stage_bytes) + (size_t)warp * 4 * RW * g.ws;
 
     const bool raw = a.cs0 == nullptr;
     u64 q[4][8];
-    load_centre<CPE, 4>(a.c0, g, u, h, w0, active, sl2, q);
+    load_centre<CPE, 4, 16 * NS>(a.c0, g, u, h, w0, active, sl2, q, 16 * slab);
     u64 nL2[4];
     float bq[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-        const bool ok = active && (w0 + r < g.W);
+        const bool ok = active && (w0 + r < g.W) && slab == 0;   // the row statistic enters the lane sum once
         nL2[r] = pack2((ok && !raw) ? -__ldg(a.cs0 + (int64_t)u * g.Np + h + g.H * (w0 + r)) * kLog2e : 0.f, 0.f);
         bq[r] = 0.f;
         if (DIST) {
@@ -572,15 +594,16 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
     }
     // position of window row offset di inside the sorted run of this thread's image row
     const int hrot = (h < g.p) ? h - g.p + g.ws : (h >= g.H - g.p ? h - g.p - g.H + g.ws : 0);   // posh = (di + hrot) mod ws
-    const int64_t warp_row0 = (int64_t)u * g.Np + (h0 + (lr & ~31));
+    const int hw0 = h0 + (lt >> 5) * RW;                       // first image row of this warp
+    const int64_t warp_row0 = (int64_t)u * g.Np + hw0;
 
     CA_PIPE_LOOP({
         const int mask = stage_mask<4>(s, g.p);
-        const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes;
+        const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * RB;
 #pragma unroll 1
         for (int di = 0; di < g.ws; ++di) {
             u64 k2[8];
-            lds_vec16(rowbase + di * kRowBytes, 0, k2);
+            lds_slab16<NS>(rowbase + di * RB, 0, slab, k2);
             float bk = 0.f;
             if (DIST) {
                 u64 n = zero2();
@@ -601,21 +624,22 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
 #pragma unroll
                 for (int r = 0; r < 4; ++r) t[r] = fma2(q[r][i], k2[i], t[r]);
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
-                if (active) {
-                    const float sc = hsum2(t[r]);
-                    tile[(r * 32 + lane) * g.ws + posh] = raw ? sc * kLn2 : fast_exp2(sc);
-                }
+            for (int r = 0; r < 4; ++r) {
+                float sc = hsum2(t[r]);
+#pragma unroll
+                for (int m = 1; m < NS; m <<= 1) sc += __shfl_xor_sync(0xffffffffu, sc, m);
+                if (active && slab == 0) tile[(r * RW + lrow) * g.ws + posh] = raw ? sc * kLn2 : fast_exp2(sc);
+            }
         }
         __syncwarp();
         // write the runs of this stage: row j, positions posw*ws .. posw*ws + ws - 1
-        const int rows_here = min(32, g.H - (h0 + (lr & ~31)));
+        const int rows_here = min(RW, g.H - hw0);
 #pragma unroll 1
         for (int r = 0; r < 4; ++r) {
             if (!((mask >> r) & 1) || w0 + r >= g.W) continue;
             const int posw = axis_pos(s - g.p - r, w0 + r, g.W, g.p, g.ws);
             float* dst = a.o0 + ((warp_row0 + (int64_t)g.H * (w0 + r)) * g.K + posw * g.ws);
-            const float* src = tile + r * 32 * g.ws;
+            const float* src = tile + r * RW * g.ws;
             const int n = rows_here * g.ws;
             int row = lane / g.ws, e = lane - row * g.ws;          // element idx = row*ws + e
             const int drow = 32 / g.ws, de = 32 - drow * g.ws;
@@ -651,26 +675,29 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int CPE, bool TRANS>
+template <int CPE, bool TRANS, int NS>
 __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                              const __grid_constant__ CUtensorMap msc) {
+    constexpr int RW = 32 / NS;                                // pixel rows per warp: NS lanes share a pixel
+    constexpr int RB = kRowBytes * NS;
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NS = g.ws + 3;
+    const int NSTAGES = g.ws + 3;
     const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     CA_PIPE_PROLOGUE(false)
-    const int lr = lt, h = h0 + lr;
-    const bool active = h < g.H;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int TR = 32 + (TRANS ? 2 * g.p : 0);                 // CSR rows staged per warp and centre column
+    const int slab = lane % NS, lrow = lane / NS;              // this lane's channel slab and row inside the warp
+    const int lr = (lt >> 5) * RW + lrow, h = h0 + lr;         // row inside the tile, image row
+    const bool active = h < g.H;
+    const int TR = RW + (TRANS ? 2 * g.p : 0);                 // CSR rows staged per warp and centre column
     const int tile_floats = 4 * TR * g.ws;                     // one buffer: [4 centre columns][TR][ws]
     // per warp: two tile buffers and the table of element offsets (row * K + e) inside a run block
     float* wbase = reinterpret_cast<float*>(smem_al + (size_t)kStages * a.stage_bytes) +
                    (size_t)warp * (2 * tile_floats + TR * g.ws);
     int* offs = reinterpret_cast<int*>(wbase + 2 * tile_floats);
-    const int hw0 = h0 + (lr & ~31);                           // first image row of this warp
+    const int hw0 = h0 + (lt >> 5) * RW;                       // first image row of this warp
     const float* nzu = a.cs0 + (int64_t)u * g.Np * g.K;
-    const int nrows = hw0 >= g.H ? 0 : (TRANS ? TR : min(32, g.H - hw0));
+    const int nrows = hw0 >= g.H ? 0 : (TRANS ? TR : min(RW, g.H - hw0));
     const int n = nrows * g.ws;
     for (int idx = lane; idx < n; idx += 32) {
         const int row = idx / g.ws, e = idx - row * g.ws;
@@ -720,22 +747,22 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
         }
         __syncwarp();
         const float* tile = wbase + (it & 1) * tile_floats;
-        const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes;
+        const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * RB;
         // operands of window row di: the streamed vector and the four values of A; fetched one
         // row ahead of the FMAs that use them
         auto fetch_row = [&](int di, u64 (&vv)[8], float (&aa)[4]) {
-            lds_vec16(rowbase + di * kRowBytes, a.which, vv);
+            lds_slab16<NS>(rowbase + di * RB, a.which, slab, vv);
             int posh, trow;
             if (!TRANS) {
                 posh = di + hrot;
                 posh -= (posh >= g.ws) ? g.ws : 0;
-                trow = lane;
+                trow = lrow;
             } else {
                 int hj = (active ? h : g.H - 1) + di - g.p;        // the row pixel of the entry (lanes past the image stay in range)
                 hj += (hj < 0) ? g.H : 0;
                 hj -= (hj >= g.H) ? g.H : 0;
                 posh = axis_pos(g.p - di, hj, g.H, g.p, g.ws);
-                trow = lane + di;
+                trow = lrow + di;
             }
             const float* ap = tile + trow * g.ws + posh;
 #pragma unroll
@@ -768,7 +795,7 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
 
     if (a.c0) {
         u64 ctr[4][8];
-        load_centre<CPE, 4>(a.c0, g, u, h, w0, active, 1.f, ctr);
+        load_centre<CPE, 4, 16 * NS>(a.c0, g, u, h, w0, active, 1.f, ctr, 16 * slab);
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             const u64 ns = pack2(-asum[r], -asum[r]);
@@ -782,7 +809,7 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
         for (int i = 0; i < 8; ++i) {
             float x, y;
             unpack2(acc[r][i], x, y);
-            store_centre<CPE>(a.o0, g, u, h, w0, active, r, i, a.scale * x, a.scale * y);
+            store_centre<CPE, 16 * NS>(a.o0, g, u, h, w0, active, r, i, a.scale * x, a.scale * y, 16 * slab);
         }
 }
 
@@ -840,7 +867,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
                                                           const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NS = g.ws + NQ - 1;
+    const int NSTAGES = g.ws + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
@@ -972,7 +999,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
                                                             const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NS = g.ws + NQ - 1;
+    const int NSTAGES = g.ws + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(true)
@@ -1073,8 +1100,9 @@ struct PackArgs {
     float* Dout;            // nullable: D in the reference layout (interior rows)
 };
 
-template <int CPE>
+template <int CPE, int NS>
 __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
+    constexpr int NCR = 16 * NS;
     const Geo& g = a.g;
     const int rr = blockIdx.x * blockDim.x + threadIdx.x;
     const int w = blockIdx.y;
@@ -1089,31 +1117,34 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
     if (slot < 2 * a.npairs) {
         const int pair = slot >> 1, t = slot & 1;
         const float* src = a.src[slot];
-        float4 c[4];
-        if (real_row) {
-            if (CPE == 1) {
-                const float* sp = src + goff<1>(u, 0, g.Npk, pix);
-                float v[16];
+        float4* dp = reinterpret_cast<float4*>(a.dst[pair] + orow * (kRowFloats * NS));
+#pragma unroll 1
+        for (int sl = 0; sl < NS; ++sl) {
+            float4 c[4];
+            if (real_row) {
+                if (CPE == 1) {
+                    const float* sp = src + goff<1, NCR>(u, 16 * sl, g.Npk, pix);
+                    float v[16];
 #pragma unroll
-                for (int cc = 0; cc < 16; ++cc) v[cc] = __ldg(sp + (int64_t)cc * g.Npk);
+                    for (int cc = 0; cc < 16; ++cc) v[cc] = __ldg(sp + (int64_t)cc * g.Npk);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) c[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    for (int i = 0; i < 4; ++i) c[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 lo = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, 16 * sl + 4 * i, g.Npk, pix)));
+                        const float2 hi = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, 16 * sl + 4 * i + 2, g.Npk, pix)));
+                        c[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                    }
+                }
             } else {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 lo = __ldg(reinterpret_cast<const float2*>(src + goff<2>(u, 4 * i, g.Npk, pix)));
-                    const float2 hi = __ldg(reinterpret_cast<const float2*>(src + goff<2>(u, 4 * i + 2, g.Npk, pix)));
-                    c[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
-                }
+                for (int i = 0; i < 4; ++i) c[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-        } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) c[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int i = 0; i < 4; ++i) dp[4 * NS * t + i * NS + sl] = c[i];      // [chunk][slab] order
+            if (t == 1) dp[8 * NS + sl] = make_float4(0.f, 0.f, 0.f, 0.f);        // padding
         }
-        float4* dp = reinterpret_cast<float4*>(a.dst[pair] + orow * kRowFloats);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dp[4 * t + i] = c[i];
-        if (t == 1) dp[8] = make_float4(0.f, 0.f, 0.f, 0.f);         // padding
         return;
     }
     float L = 0.f, D = 0.f;
@@ -1151,13 +1182,19 @@ Padded padded_of(const Geo& g) {
     Padded P;
     P.pp = (g.p + 1) & ~1;
     P.Hp = (g.H + 2 * P.pp + 3) & ~3;
-    P.pair_floats = (size_t)g.units * g.Wk * P.Hp * kRowFloats;
+    P.pair_floats = (size_t)g.units * g.Wk * P.Hp * kRowFloats * (g.cr / 16);
     P.plane_floats = (size_t)2 * g.units * g.Wk * P.Hp;
     return P;
 }
 
 bool tiled_shape_ok(const Geo& g) {
     return g.cr == 16 && g.wsw == g.ws && g.ws >= 3 && g.H >= 16 && g.ws <= 63;
+}
+
+// The stand-alone operator kernels also take 32 or 64 real channels per unit (2 or 4 lanes per pixel).
+bool tiled_operator_ok(const Geo& g) {
+    return (g.cr == 16 || g.cr == 32 || g.cr == 64) && g.wsw == g.ws && g.ws >= 3 && g.H >= 16 && g.ws <= 63 &&
+           g.Wk == g.W;
 }
 
 int env_int(const char* name, int dflt) {
@@ -1176,8 +1213,17 @@ int pick_dc(int ws) {
 
 int launch_pack(const PackArgs& a, cudaStream_t st) {
     dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * (2 * a.npairs + (a.planes ? 1 : 0)));
-    if (a.g.cpe == 1) pack_kernel<1><<<grid, 128, 0, st>>>(a);
-    else pack_kernel<2><<<grid, 128, 0, st>>>(a);
+    const int ns = a.g.cr / 16;
+    if (a.planes && ns != 1) { set_error("scalar planes are packed for 16-channel units only"); return CA_ERR_UNSUPPORTED; }
+#define CA_PACK(CPEV)                                                      \
+    do {                                                                   \
+        if (ns == 1) pack_kernel<CPEV, 1><<<grid, 128, 0, st>>>(a);        \
+        else if (ns == 2) pack_kernel<CPEV, 2><<<grid, 128, 0, st>>>(a);   \
+        else pack_kernel<CPEV, 4><<<grid, 128, 0, st>>>(a);                \
+    } while (0)
+    if (a.g.cpe == 1) CA_PACK(1);
+    else CA_PACK(2);
+#undef CA_PACK
     CA_CHECK_LAUNCH("pack kernel");
     return CA_OK;
 }
@@ -1206,11 +1252,13 @@ int sm_count() {
 // thread for the merge of a split tile.  CTAs have at most 128 threads: four
 // warps of rows, or two warps of rows times two stage groups on small grids.
 int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* env_warps, const float* pair,
-            const float* planes, Launch* L, bool allow_split = true, int max_warps = 4) {
-    int warps = (g.H + 31) / 32;
+            const float* planes, Launch* L, bool allow_split = true, int max_warps = 4, int ns = 1) {
+    const int rw = 32 / ns;                             // pixel rows per warp (ns lanes share a pixel)
+    const int rb = kRowBytes * ns, rf = kRowFloats * ns;
+    int warps = (g.H + rw - 1) / rw;
     if (warps > max_warps) warps = max_warps;
     const long cols = (g.W + nq - 1) / nq;
-    const long ctas4 = cols * ((g.H + 32 * warps - 1) / (32 * warps)) * g.units;
+    const long ctas4 = cols * ((g.H + rw * warps - 1) / (rw * warps)) * g.units;
     int nsplit = (ctas4 * warps < 6L * sm_count()) ? 2 : 1;
     nsplit = env_int("CIRCATT_SPLIT", nsplit);
     if (!allow_split) nsplit = 1;
@@ -1219,13 +1267,14 @@ int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* e
     if (warps * nsplit > 4) warps = 4 / nsplit;
     TileArgs& a = L->a;
     a.g = g;
-    a.TH = 32 * warps;
+    a.TH = rw * warps;
     a.roff = P.pp - g.p;
     a.nsplit = nsplit;
+    a.row_bytes = rb;
     const int ROWS = a.TH + 2 * P.pp;
     if (ROWS > 256) { set_error("tile of %d rows exceeds the TMA box limit", ROWS); return CA_ERR_UNSUPPORTED; }
     const int sstride = (ROWS * 4 + 127) & ~127;
-    const int vbytes = (ROWS * kRowBytes + 127) & ~127;
+    const int vbytes = (ROWS * rb + 127) & ~127;
     a.stage_bytes = (vbytes + (planes ? 2 * sstride : 0) + 1023) & ~1023;
     L->grid = dim3((unsigned)cols, (g.H + a.TH - 1) / a.TH, g.units);
     L->threads = 32 * warps * nsplit;
@@ -1233,9 +1282,9 @@ int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* e
     const size_t xch = (size_t)xch_floats * 32 * warps * sizeof(float);
     if (nsplit == 2 && xch > smem) smem = xch;
     L->smem = smem + 1024;
-    const uint64_t dims[4] = {(uint64_t)kRowFloats, (uint64_t)P.Hp, (uint64_t)g.Wk, (uint64_t)g.units};
-    const uint64_t strides[3] = {(uint64_t)kRowBytes, (uint64_t)P.Hp * kRowBytes, (uint64_t)P.Hp * kRowBytes * g.Wk};
-    const uint32_t box[4] = {(uint32_t)kRowFloats, (uint32_t)ROWS, 1, 1};
+    const uint64_t dims[4] = {(uint64_t)rf, (uint64_t)P.Hp, (uint64_t)g.Wk, (uint64_t)g.units};
+    const uint64_t strides[3] = {(uint64_t)rb, (uint64_t)P.Hp * rb, (uint64_t)P.Hp * rb * g.Wk};
+    const uint32_t box[4] = {(uint32_t)rf, (uint32_t)ROWS, 1, 1};
     int rc;
     if ((rc = encode_tensor_map(&L->mv, pair, 4, dims, strides, box, false))) return rc;
     if (planes) {
@@ -1438,14 +1487,28 @@ int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, con
 // tiled_attention_fwd, and the row statistics.
 int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const float* stats, float* nz,
                  void* workspace, cudaStream_t st) {
-    if (!tiled_shape_ok(g) || g.Wk != g.W) return CA_ERR_UNSUPPORTED;
+    if (!tiled_operator_ok(g)) return CA_ERR_UNSUPPORTED;
     const Padded P = padded_of(g);
+    const int ns = g.cr / 16;
     Launch L{};
-    int rc = prepare(g, P, 4, 0, "CIRCATT_FWD_WARPS", static_cast<const float*>(workspace), nullptr, &L);
+    int rc = prepare(g, P, 4, 0, "CIRCATT_FWD_WARPS", static_cast<const float*>(workspace), nullptr, &L, true, 4, ns);
     if (rc) return rc;
-    L.smem += (size_t)L.threads / 32 * 128 * g.ws * sizeof(float);
+    L.smem += (size_t)L.threads / 32 * 4 * (32 / ns) * g.ws * sizeof(float);
+#define CA_EMIT(NSV)                                                                  \
+    do {                                                                              \
+        if (g.cpe == 1) {                                                             \
+            if (dist) CA_LAUNCH_TILED((emit_a_tiled_kernel<true, 1, NSV>), L, st);    \
+            else CA_LAUNCH_TILED((emit_a_tiled_kernel<false, 1, NSV>), L, st);        \
+        } else {                                                                      \
+            if (dist) CA_LAUNCH_TILED((emit_a_tiled_kernel<true, 2, NSV>), L, st);    \
+            else CA_LAUNCH_TILED((emit_a_tiled_kernel<false, 2, NSV>), L, st);        \
+        }                                                                             \
+    } while (0)
     L.a.scale = scale; L.a.c0 = q; L.a.cs0 = stats; L.a.o0 = nz;
-    CA_DIST_CPE(emit_a_tiled_kernel, dist, g.cpe, L, st);
+    if (ns == 1) CA_EMIT(1);
+    else if (ns == 2) CA_EMIT(2);
+    else CA_EMIT(4);
+#undef CA_EMIT
     CA_CHECK_LAUNCH("tiled A kernel");
     return CA_OK;
 }
@@ -1545,7 +1608,7 @@ int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, con
 
 // ---------------------------------------------------------------- stand-alone operators
 size_t tiled_operator_workspace(const Geo& g) {
-    if (!tiled_shape_ok(g) || g.Wk != g.W) return 0;
+    if (!tiled_operator_ok(g)) return 0;
     return padded_of(g).pair_floats * sizeof(float);
 }
 
@@ -1569,19 +1632,27 @@ int tiled_similarity(const Geo& g, float scale, int dist, const float* x, const 
 static int run_apply(const Geo& g, const Padded& P, const float* nz, const float* pair, int which,
                      const float* centre, float* out, float alpha, int transposed, cudaStream_t st) {
     Launch L{};
-    int rc = prepare(g, P, 4, 0, "CIRCATT_APPLY_WARPS", pair, nullptr, &L, false, 2);
+    const int ns = g.cr / 16;
+    int rc = prepare(g, P, 4, 0, "CIRCATT_APPLY_WARPS", pair, nullptr, &L, false, ns == 1 ? 2 : 4, ns);
     if (rc) return rc;
-    const int TR = 32 + (transposed ? 2 * g.p : 0);
+    const int TR = 32 / ns + (transposed ? 2 * g.p : 0);
     L.smem += (size_t)L.threads / 32 * 9 * TR * g.ws * sizeof(float);     // two tile buffers + offsets per warp
     if (L.smem > 200 * 1024) return CA_ERR_UNSUPPORTED;
     L.a.scale = alpha; L.a.which = which; L.a.c0 = centre; L.a.cs0 = nz; L.a.o0 = out;
-    if (g.cpe == 1) {
-        if (transposed) CA_LAUNCH_TILED((apply_tiled_kernel<1, true>), L, st);
-        else CA_LAUNCH_TILED((apply_tiled_kernel<1, false>), L, st);
-    } else {
-        if (transposed) CA_LAUNCH_TILED((apply_tiled_kernel<2, true>), L, st);
-        else CA_LAUNCH_TILED((apply_tiled_kernel<2, false>), L, st);
-    }
+#define CA_APPLY(NSV)                                                                     \
+    do {                                                                                  \
+        if (g.cpe == 1) {                                                                 \
+            if (transposed) CA_LAUNCH_TILED((apply_tiled_kernel<1, true, NSV>), L, st);   \
+            else CA_LAUNCH_TILED((apply_tiled_kernel<1, false, NSV>), L, st);             \
+        } else {                                                                          \
+            if (transposed) CA_LAUNCH_TILED((apply_tiled_kernel<2, true, NSV>), L, st);   \
+            else CA_LAUNCH_TILED((apply_tiled_kernel<2, false, NSV>), L, st);             \
+        }                                                                                 \
+    } while (0)
+    if (ns == 1) CA_APPLY(1);
+    else if (ns == 2) CA_APPLY(2);
+    else CA_APPLY(4);
+#undef CA_APPLY
     CA_CHECK_LAUNCH("tiled apply kernel");
     return CA_OK;
 }

@@ -254,6 +254,11 @@ TILED_OPERATOR_CASES = [
     ((128, 24), 21, 16, 1, False),      # full-height tile, window 21
     ((70, 10), 5, 16, 3, False),        # three warps of rows, W not a multiple of the four-column tile
     ((64, 48), 15, 16, 4, False),       # quarter-size BASELINE config 2
+    ((37, 29), 9, 32, 2, False),        # 32 real channels: two lanes per pixel
+    ((33, 12), 7, 16, 2, True),         # 16 complex channels
+    ((24, 20), 5, 64, 2, False),        # 64 real channels: four lanes per pixel
+    ((40, 21), 7, 32, 1, True),         # 32 complex channels (BASELINE config 4's channel count)
+    ((16, 16), 3, 64, 3, False),        # smallest window, two warps of rows
 ]
 
 
