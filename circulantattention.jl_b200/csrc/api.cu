@@ -273,6 +273,16 @@ static size_t score_bytes(const Geo& g) {
     return (((size_t)g.Np * g.K * g.units * sizeof(float)) + 255) & ~(size_t)255;
 }
 
+// Attention as a chain of the tiled operators (similarity -> row normaliser -> apply, and the
+// reference's own pullback chain of src/rrules.jl backwards) with the scores in scratch memory.
+// Used where no fused tiled kernel exists: 32 or 64 real channels per unit, and entmax.  The
+// scratch is A-sized, so the chain is taken only while A fits Int32 indexing and 4 GiB.
+static bool composed_path(const ca_desc* d, const Geo& g) {
+    if (g.Wk != g.W || !tiled_operator_workspace(g)) return false;
+    if ((int64_t)g.Np * g.K > INT32_MAX || score_bytes(g) > ((size_t)4 << 30)) return false;
+    return d->normalizer == CA_ENTMAX15 || g.cr != 16;
+}
+
 size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {
     Geo g;
     if (make_geo(d, &g, true)) return 0;
@@ -281,6 +291,7 @@ size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {
         const bool band = g.Wk != g.W;
         return (want_nz ? 0 : score_bytes(g)) + (band ? 0 : tiled_operator_workspace(g));
     }
+    if (composed_path(d, g)) return (want_nz ? 0 : score_bytes(g)) + tiled_operator_workspace(g);
     const bool band = g.Wk != g.W;
     return (want_nz && band) ? 0 : tiled_fwd_workspace(g);
 }
@@ -297,8 +308,10 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
     cudaStream_t st = as_stream(stream);
     const int dist = d->similarity == CA_DISTANCE;
 
-    if (d->normalizer == CA_ENTMAX15) {
-        // scores -> threshold per row -> apply; the scores live in nz or in the workspace
+    const bool ent = d->normalizer == CA_ENTMAX15;
+    if (ent || (composed_path(d, g) && (nz || workspace))) {
+        // scores -> row normaliser (threshold or log-sum-exp per row) -> apply; the scores live in
+        // nz or in the workspace
         if (band) { set_error("entmax in band mode is not implemented"); return CA_ERR_UNSUPPORTED; }
         if ((rc = check_nnz(g))) return rc;
         float* sbuf = nz ? nz : (float*)workspace;
@@ -309,7 +322,7 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
         if (rc == CA_ERR_UNSUPPORTED)
             rc = launch_similarity(g, d->scale, dist, (const float*)q, (const float*)k, sbuf, st);
         if (rc) return rc;
-        if ((rc = launch_row_normalize((int64_t)g.Np * g.units, g.K, 1, sbuf, sbuf, stats, st))) return rc;
+        if ((rc = launch_row_normalize((int64_t)g.Np * g.units, g.K, ent, sbuf, sbuf, stats, st))) return rc;
         rc = tiled_apply(g, sbuf, (const float*)v, (float*)y, 1.f, 0, opws, st);
         if (rc != CA_ERR_UNSUPPORTED) return rc;
         return launch_apply(g, sbuf, (const float*)v, nullptr, (float*)y, 1.f, 0, 0, 0, st);
@@ -335,6 +348,7 @@ static size_t d_bytes(const Geo& g) { return (((size_t)g.Npk * g.units * sizeof(
 size_t ca_attention_bwd_workspace(const ca_desc* d) {
     Geo g;
     if (make_geo(d, &g, false)) return 0;
+    if (composed_path(d, g)) return d_bytes(g) + 2 * score_bytes(g) + tiled_operator_workspace(g);
     return d_bytes(g) + (d->normalizer == CA_SOFTMAX ? tiled_bwd_workspace(g) : 0);
 }
 
@@ -439,6 +453,31 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
     if (rc) return rc;
     if (!workspace) { set_error("workspace of ca_attention_bwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
     float* D = (float*)workspace;
+    if (composed_path(d, g)) {
+        // the pullback chain of src/rrules.jl:42-72 on the tiled operators:
+        //   P (saved, or recomputed from q, k) ; dv = P^T dy ; dP = Re(dy . conj(v)) on the window (+ dA) ;
+        //   dS = normaliser pullback ; (dq, dk) = similarity pullback
+        if (!q || !k || !v || !dy || !dq || !dk || !dv) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
+        cudaStream_t st = as_stream(stream);
+        const int dist = d->similarity == CA_DISTANCE, ent = d->normalizer == CA_ENTMAX15;
+        float* pbuf = (float*)((char*)workspace + d_bytes(g));
+        float* dpbuf = (float*)((char*)pbuf + score_bytes(g));
+        void* opws = (char*)dpbuf + score_bytes(g);
+        const int64_t rows = (int64_t)g.Np * g.units, nnz = rows * g.K;
+        const float* P = nz;
+        if (!P) {
+            if ((rc = tiled_similarity(g, d->scale, dist, (const float*)q, (const float*)k, pbuf, opws, st))) return rc;
+            if ((rc = launch_row_normalize(rows, g.K, ent, pbuf, pbuf, nullptr, st))) return rc;
+            P = pbuf;
+        }
+        if ((rc = tiled_apply(g, P, (const float*)dy, (float*)dv, 1.f, 1, opws, st))) return rc;
+        if ((rc = tiled_similarity(g, 1.f, 0, (const float*)dy, (const float*)v, dpbuf, opws, st))) return rc;
+        if (dA && (rc = ca_axpby(nnz, 1.f, dpbuf, 1.f, dA, dpbuf, stream))) return rc;
+        row_normalize_bwd_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(rows, g.K, ent, P, dpbuf, dpbuf);
+        CA_CHECK_LAUNCH("row normalize pullback kernel");
+        return tiled_similarity_bwd(g, d->scale, dist, (const float*)q, (const float*)k, dpbuf, (float*)dq,
+                                    (float*)dk, opws, st);
+    }
     if (d->normalizer == CA_SOFTMAX && !dA) {
         if (!q || !k || !v || !y || !dy || !stats || !dq || !dk || !dv) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
         rc = tiled_attention_bwd(g, d->scale, d->similarity == CA_DISTANCE, (const float*)q, (const float*)k,

@@ -134,6 +134,7 @@ __device__ int g_stage_timeouts = 0;
 
 constexpr int kRowFloats = 36;                 // 16 + 16 + 4 padding
 constexpr int kRowBytes = kRowFloats * 4;      // 144
+constexpr int kSingleFloats = 20;              // single-tensor rows: 16 + 4 padding (80 bytes, also conflict free)
 
 // 16-channel vector `which` (0: first tensor, 1: second) of the pixel row at
 // shared-space byte address `a0`, as eight packed pairs.
@@ -561,8 +562,8 @@ template <bool DIST, int CPE, int NS>
 __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                               const __grid_constant__ CUtensorMap msc) {
     constexpr int RW = 32 / NS;                                // pixel rows per warp: NS lanes share a pixel
-    constexpr int RB = kRowBytes * NS;
     const Geo& g = a.g;
+    const int RB = a.row_bytes;                                // packed row: pair (144*NS) or single tensor (80*NS)
     const int ROWS = a.TH + 2 * (g.p + a.roff);
     const int NSTAGES = g.ws + 3;
     const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
@@ -679,8 +680,8 @@ template <int CPE, bool TRANS, int NS>
 __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                              const __grid_constant__ CUtensorMap msc) {
     constexpr int RW = 32 / NS;                                // pixel rows per warp: NS lanes share a pixel
-    constexpr int RB = kRowBytes * NS;
     const Geo& g = a.g;
+    const int RB = a.row_bytes;                                // packed row: pair (144*NS) or single tensor (80*NS)
     const int ROWS = a.TH + 2 * (g.p + a.roff);
     const int NSTAGES = g.ws + 3;
     const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
@@ -1090,6 +1091,7 @@ struct PackArgs {
     int pp;                 // p' (even)
     int Hp;                 // padded rows per column: roundup4(H + 2p')
     int npairs;             // 1 or 2 tensor pairs
+    int single;             // 1: rows hold one tensor (src[0]) in 20 words per slab instead of a pair in 36
     const float* src[4];    // pair j = (src[2j], src[2j+1])
     float* dst[2];
     float* planes;          // nullable
@@ -1106,44 +1108,46 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
     const Geo& g = a.g;
     const int rr = blockIdx.x * blockDim.x + threadIdx.x;
     const int w = blockIdx.y;
-    // z slot: 2*npairs tensor copies per unit, plus one slot for the scalar planes
-    const int slots = 2 * a.npairs + (a.planes ? 1 : 0);
+    // z slot: one per tensor copy and unit, plus one slot for the scalar planes
+    const int nt = a.single ? 1 : 2;                      // tensors per packed row
+    const int slots = nt * a.npairs + (a.planes ? 1 : 0);
     const int u = blockIdx.z / slots, slot = blockIdx.z % slots;
     if (rr >= a.Hp) return;
     const bool real_row = rr < g.H + 2 * a.pp;
     const int hs = real_row ? (rr - a.pp + g.H) % g.H : 0;
     const int pix = hs + g.H * w;
     const int64_t orow = ((int64_t)u * g.Wk + w) * a.Hp + rr;
-    if (slot < 2 * a.npairs) {
-        const int pair = slot >> 1, t = slot & 1;
-        const float* src = a.src[slot];
-        float4* dp = reinterpret_cast<float4*>(a.dst[pair] + orow * (kRowFloats * NS));
-#pragma unroll 1
-        for (int sl = 0; sl < NS; ++sl) {
-            float4 c[4];
-            if (real_row) {
-                if (CPE == 1) {
-                    const float* sp = src + goff<1, NCR>(u, 16 * sl, g.Npk, pix);
-                    float v[16];
+    if (slot < nt * a.npairs) {
+        const int pair = slot / nt, t = slot % nt;
+        const float* src = a.src[2 * pair + t];
+        const int row_floats = (a.single ? kSingleFloats : kRowFloats) * NS;
+        float4* dp = reinterpret_cast<float4*>(a.dst[pair] + orow * row_floats) + 4 * NS * t;
+        // chunk-major: the NS slabs of a 4-channel chunk are adjacent, so each pass writes 16*NS
+        // contiguous bytes
 #pragma unroll
-                    for (int cc = 0; cc < 16; ++cc) v[cc] = __ldg(sp + (int64_t)cc * g.Npk);
+        for (int c = 0; c < 4; ++c) {
+            float4 vals[NS];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) c[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            for (int sl = 0; sl < NS; ++sl) {
+                const int cc = 16 * sl + 4 * c;
+                if (!real_row) {
+                    vals[sl] = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else if (CPE == 1) {
+                    const float* sp = src + goff<1, NCR>(u, cc, g.Npk, pix);
+                    vals[sl] = make_float4(__ldg(sp), __ldg(sp + g.Npk), __ldg(sp + 2 * (int64_t)g.Npk),
+                                           __ldg(sp + 3 * (int64_t)g.Npk));
                 } else {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 lo = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, 16 * sl + 4 * i, g.Npk, pix)));
-                        const float2 hi = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, 16 * sl + 4 * i + 2, g.Npk, pix)));
-                        c[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
-                    }
+                    const float2 lo = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, cc, g.Npk, pix)));
+                    const float2 hi = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, cc + 2, g.Npk, pix)));
+                    vals[sl] = make_float4(lo.x, lo.y, hi.x, hi.y);
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) c[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) dp[4 * NS * t + i * NS + sl] = c[i];      // [chunk][slab] order
-            if (t == 1) dp[8 * NS + sl] = make_float4(0.f, 0.f, 0.f, 0.f);        // padding
+            for (int sl = 0; sl < NS; ++sl) dp[c * NS + sl] = vals[sl];
+        }
+        if (t == nt - 1) {
+#pragma unroll
+            for (int sl = 0; sl < NS; ++sl) dp[4 * NS + sl] = make_float4(0.f, 0.f, 0.f, 0.f);    // padding
         }
         return;
     }
@@ -1175,6 +1179,7 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
 struct Padded {
     int pp, Hp;
     size_t pair_floats;     // one packed tensor pair
+    size_t single_floats;   // one packed single tensor
     size_t plane_floats;    // both scalar planes
 };
 
@@ -1183,6 +1188,7 @@ Padded padded_of(const Geo& g) {
     P.pp = (g.p + 1) & ~1;
     P.Hp = (g.H + 2 * P.pp + 3) & ~3;
     P.pair_floats = (size_t)g.units * g.Wk * P.Hp * kRowFloats * (g.cr / 16);
+    P.single_floats = (size_t)g.units * g.Wk * P.Hp * kSingleFloats * (g.cr / 16);
     P.plane_floats = (size_t)2 * g.units * g.Wk * P.Hp;
     return P;
 }
@@ -1212,7 +1218,7 @@ int pick_dc(int ws) {
 }
 
 int launch_pack(const PackArgs& a, cudaStream_t st) {
-    dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * (2 * a.npairs + (a.planes ? 1 : 0)));
+    dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * ((a.single ? 1 : 2) * a.npairs + (a.planes ? 1 : 0)));
     const int ns = a.g.cr / 16;
     if (a.planes && ns != 1) { set_error("scalar planes are packed for 16-channel units only"); return CA_ERR_UNSUPPORTED; }
 #define CA_PACK(CPEV)                                                      \
@@ -1252,9 +1258,10 @@ int sm_count() {
 // thread for the merge of a split tile.  CTAs have at most 128 threads: four
 // warps of rows, or two warps of rows times two stage groups on small grids.
 int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* env_warps, const float* pair,
-            const float* planes, Launch* L, bool allow_split = true, int max_warps = 4, int ns = 1) {
+            const float* planes, Launch* L, bool allow_split = true, int max_warps = 4, int ns = 1,
+            bool single = false) {
     const int rw = 32 / ns;                             // pixel rows per warp (ns lanes share a pixel)
-    const int rb = kRowBytes * ns, rf = kRowFloats * ns;
+    const int rf = (single ? kSingleFloats : kRowFloats) * ns, rb = rf * 4;
     int warps = (g.H + rw - 1) / rw;
     if (warps > max_warps) warps = max_warps;
     const long cols = (g.W + nq - 1) / nq;
@@ -1431,7 +1438,7 @@ int tiled_stage_timeouts(int* count) {
 }
 
 int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const float* stats, float* nz,
-                 void* workspace, cudaStream_t st);
+                 void* workspace, cudaStream_t st, bool single = false);
 
 int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                         float* y, float* nz, float* stats, void* workspace, cudaStream_t st) {
@@ -1486,12 +1493,13 @@ int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, con
 // A's values in CSR order from q, the packed (k|v) pair left in `workspace` by
 // tiled_attention_fwd, and the row statistics.
 int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const float* stats, float* nz,
-                 void* workspace, cudaStream_t st) {
+                 void* workspace, cudaStream_t st, bool single) {
     if (!tiled_operator_ok(g)) return CA_ERR_UNSUPPORTED;
     const Padded P = padded_of(g);
     const int ns = g.cr / 16;
     Launch L{};
-    int rc = prepare(g, P, 4, 0, "CIRCATT_FWD_WARPS", static_cast<const float*>(workspace), nullptr, &L, true, 4, ns);
+    int rc = prepare(g, P, 4, 0, "CIRCATT_FWD_WARPS", static_cast<const float*>(workspace), nullptr, &L, true, 4, ns,
+                     single);
     if (rc) return rc;
     L.smem += (size_t)L.threads / 32 * 4 * (32 / ns) * g.ws * sizeof(float);
 #define CA_EMIT(NSV)                                                                  \
@@ -1609,14 +1617,14 @@ int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, con
 // ---------------------------------------------------------------- stand-alone operators
 size_t tiled_operator_workspace(const Geo& g) {
     if (!tiled_operator_ok(g)) return 0;
-    return padded_of(g).pair_floats * sizeof(float);
+    return padded_of(g).single_floats * sizeof(float);
 }
 
-static int pack_pair(const Geo& g, const Padded& P, const float* first, const float* second, float* dst,
-                     cudaStream_t st) {
+// Packs one tensor as single-tensor rows.
+static int pack_single(const Geo& g, const Padded& P, const float* src, float* dst, cudaStream_t st) {
     PackArgs pa{};
-    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1;
-    pa.src[0] = first; pa.src[1] = second; pa.dst[0] = dst;
+    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1; pa.single = 1;
+    pa.src[0] = src; pa.dst[0] = dst;
     return launch_pack(pa, st);
 }
 
@@ -1624,21 +1632,21 @@ static int pack_pair(const Geo& g, const Padded& P, const float* first, const fl
 int tiled_similarity(const Geo& g, float scale, int dist, const float* x, const float* y, float* nz,
                      void* workspace, cudaStream_t st) {
     if (!workspace || !tiled_operator_workspace(g)) return CA_ERR_UNSUPPORTED;
-    int rc = pack_pair(g, padded_of(g), y, y, static_cast<float*>(workspace), st);
+    int rc = pack_single(g, padded_of(g), y, static_cast<float*>(workspace), st);
     if (rc) return rc;
-    return tiled_emit_a(g, scale, dist, x, nullptr, nz, workspace, st);
+    return tiled_emit_a(g, scale, dist, x, nullptr, nz, workspace, st, true);
 }
 
-static int run_apply(const Geo& g, const Padded& P, const float* nz, const float* pair, int which,
+static int run_apply(const Geo& g, const Padded& P, const float* nz, const float* packed,
                      const float* centre, float* out, float alpha, int transposed, cudaStream_t st) {
     Launch L{};
     const int ns = g.cr / 16;
-    int rc = prepare(g, P, 4, 0, "CIRCATT_APPLY_WARPS", pair, nullptr, &L, false, ns == 1 ? 2 : 4, ns);
+    int rc = prepare(g, P, 4, 0, "CIRCATT_APPLY_WARPS", packed, nullptr, &L, false, ns == 1 ? 2 : 4, ns, true);
     if (rc) return rc;
     const int TR = 32 / ns + (transposed ? 2 * g.p : 0);
     L.smem += (size_t)L.threads / 32 * 9 * TR * g.ws * sizeof(float);     // two tile buffers + offsets per warp
     if (L.smem > 200 * 1024) return CA_ERR_UNSUPPORTED;
-    L.a.scale = alpha; L.a.which = which; L.a.c0 = centre; L.a.cs0 = nz; L.a.o0 = out;
+    L.a.scale = alpha; L.a.which = 0; L.a.c0 = centre; L.a.cs0 = nz; L.a.o0 = out;
 #define CA_APPLY(NSV)                                                                     \
     do {                                                                                  \
         if (g.cpe == 1) {                                                                 \
@@ -1662,10 +1670,10 @@ int tiled_apply(const Geo& g, const float* nz, const float* v, float* out, float
                 void* workspace, cudaStream_t st) {
     if (!workspace || !tiled_operator_workspace(g)) return CA_ERR_UNSUPPORTED;
     const Padded P = padded_of(g);
-    float* pair = static_cast<float*>(workspace);
-    int rc = pack_pair(g, P, v, v, pair, st);
+    float* packed = static_cast<float*>(workspace);
+    int rc = pack_single(g, P, v, packed, st);
     if (rc) return rc;
-    return run_apply(g, P, nz, pair, 0, nullptr, out, alpha, transposed, st);
+    return run_apply(g, P, nz, packed, nullptr, out, alpha, transposed, st);
 }
 
 // Pullback of the similarity: dx[j] = scale * sum_i dS[j,i] y[i], dy[i] = scale * sum_j dS[j,i] x[j]
@@ -1674,11 +1682,16 @@ int tiled_similarity_bwd(const Geo& g, float scale, int dist, const float* x, co
                          float* dx, float* dy, void* workspace, cudaStream_t st) {
     if (!workspace || !tiled_operator_workspace(g)) return CA_ERR_UNSUPPORTED;
     const Padded P = padded_of(g);
-    float* pair = static_cast<float*>(workspace);
-    int rc = pack_pair(g, P, y, x, pair, st);
-    if (rc) return rc;
-    if (dx && (rc = run_apply(g, P, dS, pair, 0, dist ? x : nullptr, dx, scale, 0, st))) return rc;
-    if (dy && (rc = run_apply(g, P, dS, pair, 1, dist ? y : nullptr, dy, scale, 1, st))) return rc;
+    float* packed = static_cast<float*>(workspace);
+    int rc;
+    if (dx) {
+        if ((rc = pack_single(g, P, y, packed, st))) return rc;
+        if ((rc = run_apply(g, P, dS, packed, dist ? x : nullptr, dx, scale, 0, st))) return rc;
+    }
+    if (dy) {
+        if ((rc = pack_single(g, P, x, packed, st))) return rc;
+        if ((rc = run_apply(g, P, dS, packed, dist ? y : nullptr, dy, scale, 1, st))) return rc;
+    }
     return CA_OK;
 }
 

@@ -61,6 +61,9 @@ CASES = [
     ((50, 18, 32, 1), 11, 2, False),
     ((48, 16, 16, 2), 13, 1, False),
     ((16, 17, 16, 1), 3, 1, False),
+    ((37, 29, 64, 2), 9, 2, False),      # 32 channels per head: chain of tiled operators with scratch scores
+    ((24, 20, 32, 2), 5, 1, True),       # 32 complex = 64 real channels (BASELINE config 4's channel count)
+    ((33, 16, 64, 1), 7, 1, False),      # 64 real channels
 ]
 
 
@@ -105,17 +108,17 @@ def test_flash_mode_equals_materialised(ca, simname):
         assert rel_err(a, b.astype(np.float64)) < TOL
 
 
-def test_cotangent_on_returned_A(ca):
+@pytest.mark.parametrize("shape,ws,nheads", [((12, 10, 8, 2), 5, 2), ((20, 12, 64, 2), 5, 2)])
+def test_cotangent_on_returned_A(ca, shape, ws, nheads):
     """Loss uses both y and A (e.g. sparsity penalties): dA flows into the fused backward."""
     rng = np.random.default_rng(2)
-    shape, ws, nheads = (12, 10, 8, 2), 5, 2
     qn, kn, vn, rn = (randn(rng, shape) for _ in range(4))
     q, k, v = (ca.jl.from_numpy(t).requires_grad_(True) for t in (qn, kn, vn))
     y, A = ca.circulant_mh_attention(ca.DistanceSimilarity(), q, k, v, ws, nheads)
     dAn = np.asfortranarray(rng.standard_normal(tuple(A.nzVal.shape)).astype(np.float32))
     ((y * ca.jl.from_numpy(rn)).sum() + (A.nzVal * ca.jl.from_numpy(dAn)).sum()).backward()
     K = ws * ws
-    dA64 = dAn.astype(np.float64).reshape((K, 120, nheads * 2), order="F")
+    dA64 = dAn.astype(np.float64).reshape((K, shape[0] * shape[1], nheads * 2), order="F")
     dqo, dko, dvo = orc.mh_attention_pullback(orc.DISTANCE, up(qn), up(kn), up(vn), ws, nheads, up(rn), dA64)
     assert rel_err(ca.jl.to_numpy(q.grad), dqo) < TOL
     assert rel_err(ca.jl.to_numpy(k.grad), dko) < TOL
