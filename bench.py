@@ -60,6 +60,16 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def wait_first_sample(self, limit_s=5.0):
+        t0 = time.perf_counter()
+        while self.proc is not None and time.perf_counter() - t0 < limit_s:
+            try:
+                if os.path.getsize(self.path) > 0:
+                    return
+            except OSError:
+                pass
+            time.sleep(0.01)
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -180,14 +190,17 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # clock sampling runs from here to the end of the device work (timed steps, per-kernel timing
+    # loops, variants, end-to-end loop); wait for its first line so the timed steps are covered
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(warmup):
         step()
+    sampler.wait_first_sample()
     barrier()
 
     # ---- timed region: K steps, each bracketed by CUDA events on the launching stream;
     # L2 (126 MB) is flushed between steps because the 25 MB working set would stay resident.
-    sampler = ClockSampler(local)
-    sampler.start()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     n0 = lib.ca_probe_launch_count()
     barrier()
@@ -232,7 +245,6 @@ def main():
         "bwd_dkdv": lambda: lib.ca_attention_bwd_dkdv(d, P(q), P(k), P(v), P(r), P(stats), P(D), None, P(dk), P(dv), P(sws), st()),
     }
     stage_s = {name: time_stage(fn)[0] for name, fn in stages.items()}
-    clocks = sampler.stop()      # sampled over the timed steps and the per-kernel timing loops
 
     # ---- other configurations of the same shape (not the headline): A materialised, Distance, forward only
     def time_variant(kind_v, want_nz):
@@ -306,6 +318,7 @@ def main():
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_value = px_per_step * n_e2e * world / float(e2e_t.item())
     nbytes = qh.numel() * 4
+    clocks = sampler.stop()
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
