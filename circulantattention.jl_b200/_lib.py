@@ -71,6 +71,7 @@ PROTOTYPES = {
     "ca_sum_rows": (C.c_int, [_D, _p, _p, _p]),
     "ca_sum_cols": (C.c_int, [_D, _p, _p, _p]),
     "ca_probe_launch_count": (C.c_int64, []),
+    "ca_probe_tiled_launch_count": (C.c_int64, []),
     "ca_probe_ffma": (C.c_int, [_i32, _i32, _p, _p]),
 }
 

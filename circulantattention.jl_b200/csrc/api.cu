@@ -13,6 +13,8 @@ static thread_local char g_err[512] = "";
 static std::atomic<int64_t> g_launches{0};
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+static std::atomic<int64_t> g_tiled_launches{0};
+void count_tiled_launch() { g_tiled_launches.fetch_add(1, std::memory_order_relaxed); }
 
 // FP32 FMA peak probe: 16 independent packed-FMA chains per thread, registers only.
 __global__ void __launch_bounds__(256) ffma_probe_kernel(int iters, float* __restrict__ sink) {
@@ -140,7 +142,13 @@ static int launch_row_normalize(int64_t rows, int K, int entmax, const float* s,
                                 cudaStream_t st) {
     const int64_t blocks = (rows * 32 + 255) / 256;
     if (blocks > INT32_MAX) { set_error("too many rows"); return CA_ERR_TOO_LARGE; }
-    if (entmax) row_entmax15_kernel<<<(unsigned)blocks, 256, 0, st>>>(rows, K, s, p, stats);
+    if (entmax) {
+        if (K <= 64) row_entmax15_reg_kernel<2><<<(unsigned)blocks, 256, 0, st>>>(rows, K, s, p, stats);
+        else if (K <= 128) row_entmax15_reg_kernel<4><<<(unsigned)blocks, 256, 0, st>>>(rows, K, s, p, stats);
+        else if (K <= 256) row_entmax15_reg_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(rows, K, s, p, stats);
+        else if (K <= 512) row_entmax15_reg_kernel<16><<<(unsigned)blocks, 256, 0, st>>>(rows, K, s, p, stats);
+        else row_entmax15_kernel<<<(unsigned)blocks, 256, 0, st>>>(rows, K, s, p, stats);
+    }
     else row_softmax_kernel<<<(unsigned)blocks, 256, 0, st>>>(rows, K, s, p, stats);
     CA_CHECK_LAUNCH("row normalize kernel");
     return CA_OK;
@@ -168,6 +176,8 @@ extern "C" {
 int ca_version(void) { return 100; }
 
 int64_t ca_probe_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int64_t ca_probe_tiled_launch_count(void) { return g_tiled_launches.load(std::memory_order_relaxed); }
 
 int ca_probe_ffma(int32_t blocks, int32_t iters, float* sink, void* stream) {
     if (blocks < 1 || iters < 1) { set_error("blocks and iters must be positive"); return CA_ERR_BAD_DESC; }
@@ -277,8 +287,11 @@ static size_t score_bytes(const Geo& g) {
 // reference's own pullback chain of src/rrules.jl backwards) with the scores in scratch memory.
 // Used where no fused tiled kernel exists: 32 or 64 real channels per unit, and entmax.  The
 // scratch is A-sized, so the chain is taken only while A fits Int32 indexing and 4 GiB.
-static bool composed_path(const ca_desc* d, const Geo& g) {
+static bool composed_path(const ca_desc* d, const Geo& g, bool backward = false) {
     if (g.Wk != g.W || !tiled_operator_workspace(g)) return false;
+    // 1-D windows are long (the scores of a row do not stay in cache between the operators): the
+    // backward of narrow units is faster on the generic kernels, which recompute instead
+    if (backward && g.wsw == 1 && g.cr <= 16) return false;
     if ((int64_t)g.Np * g.K > INT32_MAX || score_bytes(g) > ((size_t)4 << 30)) return false;
     return d->normalizer == CA_ENTMAX15 || g.cr != 16;
 }
@@ -348,7 +361,7 @@ static size_t d_bytes(const Geo& g) { return (((size_t)g.Npk * g.units * sizeof(
 size_t ca_attention_bwd_workspace(const ca_desc* d) {
     Geo g;
     if (make_geo(d, &g, false)) return 0;
-    if (composed_path(d, g)) return d_bytes(g) + 2 * score_bytes(g) + tiled_operator_workspace(g);
+    if (composed_path(d, g, true)) return d_bytes(g) + 2 * score_bytes(g) + tiled_operator_workspace(g);
     return d_bytes(g) + (d->normalizer == CA_SOFTMAX ? tiled_bwd_workspace(g) : 0);
 }
 
@@ -453,7 +466,7 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
     if (rc) return rc;
     if (!workspace) { set_error("workspace of ca_attention_bwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
     float* D = (float*)workspace;
-    if (composed_path(d, g)) {
+    if (composed_path(d, g, true)) {
         // the pullback chain of src/rrules.jl:42-72 on the tiled operators:
         //   P (saved, or recomputed from q, k) ; dv = P^T dy ; dP = Re(dy . conj(v)) on the window (+ dA) ;
         //   dS = normaliser pullback ; (dq, dk) = similarity pullback

@@ -14,6 +14,7 @@ void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 
 void count_launch();
+void count_tiled_launch();     // launches of the TMA-tiled kernels only (tests use it to see which path ran)
 
 #define CA_CHECK_LAUNCH(what)                                        \
     do {                                                             \

@@ -126,6 +126,72 @@ __global__ void __launch_bounds__(256) row_entmax15_kernel(int64_t rows, int K,
     if (stats && lane == 0) stats[row] = tau + m;
 }
 
+// The same for rows of at most 32*R entries, held in registers (one global read, one write).  The
+// bisection stops as soon as no entry lies between the two ends of the bracket: the support is then
+// known, and the closed form gives tau.
+template <int R>
+__global__ void __launch_bounds__(256) row_entmax15_reg_kernel(int64_t rows, int K,
+                                                               const float* s,
+                                                               float* p,
+                                                               float* __restrict__ stats) {
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* sr = s + row * K;
+    float* pr = p + row * K;
+    float z[R];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int k = lane + 32 * i;
+        z[i] = k < K ? 0.5f * sr[k] : -INFINITY;
+        m = fmaxf(m, z[i]);
+    }
+    m = warp_max(m);
+#pragma unroll
+    for (int i = 0; i < R; ++i) z[i] -= m;                 // z - m in (-inf, 0]; tau' in [-1, 0)
+    float lo = -1.f, hi = 0.f;
+    int n_lo = 0, n_hi = 0;                                // entries above lo / above hi
+#pragma unroll
+    for (int i = 0; i < R; ++i) n_lo += z[i] > lo;
+    n_lo = __reduce_add_sync(0xffffffffu, n_lo);
+    for (int it = 0; it < 26 && n_lo != n_hi; ++it) {
+        const float mid = 0.5f * (lo + hi);
+        float f = 0.f;
+        int cnt = 0;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const float t = fmaxf(z[i] - mid, 0.f);
+            f = fmaf(t, t, f);
+            cnt += z[i] > mid;
+        }
+        f = warp_sum(f);
+        cnt = __reduce_add_sync(0xffffffffu, cnt);
+        if (f > 1.f) { lo = mid; n_lo = cnt; } else { hi = mid; n_hi = cnt; }
+    }
+    // support = entries above lo (equivalently above hi when the loop stopped early)
+    float n = 0.f, sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+        if (z[i] > lo) { n += 1.f; sum += z[i]; }
+    n = warp_sum(n);
+    sum = warp_sum(sum);
+    const float mean = sum / n;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+        if (z[i] > lo) ss = fmaf(z[i] - mean, z[i] - mean, ss);
+    ss = warp_sum(ss);
+    const float tau = mean - sqrtf(fmaxf((1.f - ss) / n, 0.f));
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int k = lane + 32 * i;
+        const float t = fmaxf(z[i] - tau, 0.f);
+        if (k < K) pr[k] = t * t;
+    }
+    if (stats && lane == 0) stats[row] = tau + m;
+}
+
 __global__ void __launch_bounds__(256) row_normalize_bwd_kernel(int64_t rows, int K, int entmax,
                                                                 const float* __restrict__ p,
                                                                 const float* dp,

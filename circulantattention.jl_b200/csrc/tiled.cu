@@ -43,6 +43,8 @@
 #include "tiled.cuh"
 #include "tma.cuh"
 #include <stdlib.h>
+#include <algorithm>
+#include <type_traits>
 #include <mutex>
 
 namespace ca {
@@ -134,6 +136,7 @@ __device__ int g_stage_timeouts = 0;
 
 constexpr int kRowFloats = 36;                 // 16 + 16 + 4 padding
 constexpr int kRowBytes = kRowFloats * 4;      // 144
+constexpr int kRunChunk = 32;                  // window rows whose entries of A are staged at a time
 constexpr int kSingleFloats = 20;              // single-tensor rows: 16 + 4 padding (80 bytes, also conflict free)
 
 // 16-channel vector `which` (0: first tensor, 1: second) of the pixel row at
@@ -170,10 +173,24 @@ __device__ __forceinline__ int64_t goff(int u, int cc, int npix, int pix) {
     return (((int64_t)u * (NCR / 2) + (cc >> 1)) * npix + pix) * 2 + (cc & 1);
 }
 
+// Window radius along w: p for 2-D windows, 0 for a folded 1-D signal (wsw == 1), whose window
+// runs along h only and continues into the neighbouring columns through the packed halo rows.
+__device__ __forceinline__ int radius_w(const Geo& g) { return (g.wsw - 1) >> 1; }
+
 __device__ __forceinline__ int stage_column(const Geo& g, int w0, int s) {
-    int kc = (w0 - g.p + s + g.wk_off) % g.Wk;
+    int kc = (w0 - radius_w(g) + s + g.wk_off) % g.Wk;
     return kc < 0 ? kc + g.Wk : kc;
 }
+
+// Rotation of the sorted run of a CSR row: the entry of window offset d sits at (d + p + rot) mod ws,
+// where the row's pixel has coordinate x on the window axis of length X (src/circulant.jl:11-15).
+__device__ __forceinline__ int run_rot(int x, int X, int p, int ws) {
+    return x < p ? x - p + ws : (x >= X - p ? x - p - X + ws : 0);
+}
+// Coordinate and length of the window axis for pixel (h, w): the image row in 2-D, the linear
+// index in a folded 1-D signal.
+__device__ __forceinline__ int axis_coord(const Geo& g, int h, int w) { return g.wsw == 1 ? h + g.H * w : h; }
+__device__ __forceinline__ int axis_len(const Geo& g) { return g.wsw == 1 ? g.Np : g.H; }
 
 template <int NQ>
 __device__ __forceinline__ int stage_mask(int s, int p) {
@@ -278,7 +295,7 @@ __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int 
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             float x = 0.f, y = 0.f;
-            if (ok) {
+            if (ok && (NCR >= 16 || 2 * i < NCR)) {         // units narrower than a slab are zero-extended
                 if (CPE == 1) {
                     x = __ldg(src + goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix));
                     y = __ldg(src + goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix));
@@ -297,6 +314,7 @@ template <int CPE, int NCR = 16>
 __device__ __forceinline__ void store_centre(float* dst, const Geo& g, int u, int h, int w0, bool active, int r,
                                              int i, float x, float y, int ch0 = 0) {
     if (!(active && (w0 + r < g.W))) return;
+    if (NCR < 16 && 2 * i >= NCR) return;
     const int pix = h + g.H * (w0 + r);
     if (CPE == 1) {
         dst[goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix)] = x;
@@ -458,7 +476,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
                                                            const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NSTAGES = g.ws + NQ - 1;
+    const int NSTAGES = g.wsw + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
@@ -485,10 +503,10 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
     }
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask<NQ>(s, g.p);
+        const int mask = stage_mask<NQ>(s, radius_w(g));
         const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes;
         // pixels whose first stage (of this part) is s
-        const int init = (s == s_begin) ? mask : (mask & ~stage_mask<NQ>(s - 1, g.p));
+        const int init = (s == s_begin) ? mask : (mask & ~stage_mask<NQ>(s - 1, radius_w(g)));
         if (init) fwd_init_max<DIST, NQ>(rowbase, init, sl2, q, nm2, bq);
         CA_MASK_SWITCH(((1 << NQ) - 1), mask, (fwd_stage<DC, DIST, MK, EXACT, NQ>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq)));
     })
@@ -558,27 +576,51 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
 // in shared memory and writes it out with consecutive lanes on consecutive
 // addresses, so the 4*K*heads bytes per pixel leave the SM in full sectors.
 // =====================================================================
-template <bool DIST, int CPE, int NS>
+// NCRT = real channels per unit: 8 (zero-extended to one slab), 16, 32 or 64.
+template <bool DIST, int CPE, int NCRT>
 __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                               const __grid_constant__ CUtensorMap msc) {
-    constexpr int RW = 32 / NS;                                // pixel rows per warp: NS lanes share a pixel
+    constexpr int NS = NCRT <= 16 ? 1 : NCRT / 16;             // 16-channel slabs = lanes per pixel
+    constexpr int RW = 32 / NS;                                // pixel rows per warp
     const Geo& g = a.g;
     const int RB = a.row_bytes;                                // packed row: pair (144*NS) or single tensor (80*NS)
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NSTAGES = g.ws + 3;
+    const int pw = radius_w(g);
     const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
+    const int NSTAGES = g.wsw + min(3, g.W - 1 - w0);          // no stages for centre columns past the image
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int slab = lane % NS, lrow = lane / NS;              // this lane's channel slab and row inside the warp
     const int lr = (lt >> 5) * RW + lrow, h = h0 + lr;         // row inside the tile, image row
     const bool active = h < g.H;
-    // per-warp staging tile [4][RW][ws] after the stage buffers
-    float* tile = reinterpret_cast<float*>(smem_al + (size_t)a.nsplit * kStages * a.stage_bytes) + (size_t)warp * 4 * RW * g.ws;
+    // per-warp staging tile [4][RW][CH] after the stage buffers: the entries of CH = min(ws, 32)
+    // consecutive window rows at a time, then the run rotations of the warp's rows [4][RW]
+    const int CH = min(g.ws, kRunChunk);
+    const int CHS = CH | 1;                                    // odd row stride: conflict-free column access
+    const int nslots = g.wsw == 1 ? 1 : 4;                     // folded 1-D: a stage pairs with one centre column
+    float* tile = reinterpret_cast<float*>(smem_al + (size_t)a.nsplit * kStages * a.stage_bytes) +
+                  (size_t)warp * (nslots * RW * CHS + 4 * RW + RW * CH);     // tile, rotations, offset table
+    int* rots = reinterpret_cast<int*>(tile + nslots * RW * CHS);
+    // 2-D windows that fit one piece: the destination offset of every tile element is the same
+    // for all stages and centre columns (row*K + sorted position) and comes from a table
+    const bool tabled = g.ws <= kRunChunk && g.wsw != 1;
+    int* etab = rots + 4 * RW;
+    const int hw0 = h0 + (lt >> 5) * RW;                       // first image row of this warp
+    for (int i = lane; i < 4 * RW; i += 32)
+        rots[i] = run_rot(axis_coord(g, hw0 + i % RW, w0 + i / RW), axis_len(g), g.p, g.ws);
+    if (tabled)
+        for (int idx = lane; idx < RW * g.ws; idx += 32) {
+            const int row = idx / g.ws, e = idx - row * g.ws;
+            int posh = e + run_rot(hw0 + row, g.H, g.p, g.ws);
+            posh -= (posh >= g.ws) ? g.ws : 0;
+            etab[idx] = row * g.K + posh;
+        }
+    __syncwarp();
 
     const bool raw = a.cs0 == nullptr;
     u64 q[4][8];
-    load_centre<CPE, 4, 16 * NS>(a.c0, g, u, h, w0, active, sl2, q, 16 * slab);
+    load_centre<CPE, 4, NCRT>(a.c0, g, u, h, w0, active, sl2, q, 16 * slab);
     u64 nL2[4];
     float bq[4];
 #pragma unroll
@@ -593,65 +635,90 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
             bq[r] = -0.5f * hsum2(n) / sl2;
         }
     }
-    // position of window row offset di inside the sorted run of this thread's image row
-    const int hrot = (h < g.p) ? h - g.p + g.ws : (h >= g.H - g.p ? h - g.p - g.H + g.ws : 0);   // posh = (di + hrot) mod ws
-    const int hw0 = h0 + (lt >> 5) * RW;                       // first image row of this warp
     const int64_t warp_row0 = (int64_t)u * g.Np + hw0;
+    const int rows_here = min(RW, g.H - hw0);
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask<4>(s, g.p);
+        const int mask = stage_mask<4>(s, pw);
         const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * RB;
+        for (int d0 = 0; d0 < g.ws; d0 += CH) {
+            const int len = min(CH, g.ws - d0);                // window rows d0 .. d0 + len - 1
+            // FULL: all four centre columns pair with this stage (compile-time), else per-column tests
+            auto sweep = [&](auto full_tag) {
+                constexpr bool FULL = decltype(full_tag)::value;
+                u64 kn[8];                                 // the next window row's vector, fetched one row ahead
+                lds_slab16<NS>(rowbase + d0 * RB, 0, slab, kn);
+#pragma unroll 2
+                for (int e = 0; e < len; ++e) {
+                    u64 k2[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) k2[i] = kn[i];
+                    if (e + 1 < len) lds_slab16<NS>(rowbase + (d0 + e + 1) * RB, 0, slab, kn);
+                    float bk = 0.f;
+                    if (DIST) {
+                        u64 n = zero2();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
+                        bk = -0.5f * sl2 * hsum2(n);
+                    }
+                    u64 t[4];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        t[r] = nL2[r];
+                        if (DIST) t[r] = add2(t[r], pack2(bq[r] + bk, 0.f));
+                    }
+                    if (FULL) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+#pragma unroll
+                            for (int r = 0; r < 4; ++r) t[r] = fma2(q[r][i], k2[i], t[r]);
+                    } else {
+#pragma unroll
+                        for (int r = 0; r < 4; ++r)
+                            if ((mask >> r) & 1) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) t[r] = fma2(q[r][i], k2[i], t[r]);
+                            }
+                    }
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        if (!FULL && !((mask >> r) & 1)) continue;
+                        float sc = hsum2(t[r]);
+#pragma unroll
+                        for (int m = 1; m < NS; m <<= 1) sc += __shfl_xor_sync(0xffffffffu, sc, m);
+                        if (slab == 0) tile[((nslots == 1 ? 0 : r) * RW + lrow) * CHS + e] = raw ? sc * kLn2 : fast_exp2(sc);
+                    }
+                }
+            };
+            if (mask == 15) sweep(std::true_type{});
+            else sweep(std::false_type{});
+            __syncwarp();
+            // write this piece of the runs of the stage: row j, positions posw*ws + (d + rot_j) mod ws
 #pragma unroll 1
-        for (int di = 0; di < g.ws; ++di) {
-            u64 k2[8];
-            lds_slab16<NS>(rowbase + di * RB, 0, slab, k2);
-            float bk = 0.f;
-            if (DIST) {
-                u64 n = zero2();
-#pragma unroll
-                for (int i = 0; i < 8; ++i) n = fma2(k2[i], k2[i], n);
-                bk = -0.5f * sl2 * hsum2(n);
-            }
-            int posh = di + hrot;
-            posh -= (posh >= g.ws) ? g.ws : 0;
-            u64 t[4];
-#pragma unroll
             for (int r = 0; r < 4; ++r) {
-                t[r] = nL2[r];
-                if (DIST) t[r] = add2(t[r], pack2(bq[r] + bk, 0.f));
+                if (!((mask >> r) & 1) || w0 + r >= g.W) continue;
+                const int posw = axis_pos(s - pw - r, w0 + r, g.W, pw, g.wsw);
+                float* dst = a.o0 + ((warp_row0 + (int64_t)g.H * (w0 + r)) * g.K + posw * g.ws);
+                const float* src = tile + (nslots == 1 ? 0 : r) * RW * CHS;
+                const int n = rows_here * len;
+                if (tabled) {                                      // CHS == len == ws: tile index == idx
+#pragma unroll 4
+                    for (int idx = lane; idx < n; idx += 32) dst[etab[idx]] = src[idx];
+                    continue;
+                }
+                int row = lane / len, e = lane - row * len;        // element idx = row*len + e
+                const int drow = 32 / len, de = 32 - drow * len;
+                for (int idx = lane; idx < n; idx += 32) {
+                    int posh = d0 + e + rots[r * RW + row];
+                    posh -= (posh >= g.ws) ? g.ws : 0;
+                    dst[(int64_t)row * g.K + posh] = src[row * CHS + e];
+                    row += drow;
+                    e += de;
+                    if (e >= len) { e -= len; ++row; }
+                }
             }
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) t[r] = fma2(q[r][i], k2[i], t[r]);
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                float sc = hsum2(t[r]);
-#pragma unroll
-                for (int m = 1; m < NS; m <<= 1) sc += __shfl_xor_sync(0xffffffffu, sc, m);
-                if (active && slab == 0) tile[(r * RW + lrow) * g.ws + posh] = raw ? sc * kLn2 : fast_exp2(sc);
-            }
+            __syncwarp();
         }
-        __syncwarp();
-        // write the runs of this stage: row j, positions posw*ws .. posw*ws + ws - 1
-        const int rows_here = min(RW, g.H - hw0);
-#pragma unroll 1
-        for (int r = 0; r < 4; ++r) {
-            if (!((mask >> r) & 1) || w0 + r >= g.W) continue;
-            const int posw = axis_pos(s - g.p - r, w0 + r, g.W, g.p, g.ws);
-            float* dst = a.o0 + ((warp_row0 + (int64_t)g.H * (w0 + r)) * g.K + posw * g.ws);
-            const float* src = tile + r * RW * g.ws;
-            const int n = rows_here * g.ws;
-            int row = lane / g.ws, e = lane - row * g.ws;          // element idx = row*ws + e
-            const int drow = 32 / g.ws, de = 32 - drow * g.ws;
-            for (int idx = lane; idx < n; idx += 32) {
-                dst[(int64_t)row * g.K + e] = src[idx];
-                row += drow;
-                e += de;
-                if (e >= g.ws) { e -= g.ws; ++row; }
-            }
-        }
-        __syncwarp();
     })
 }
 
@@ -676,53 +743,116 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int CPE, bool TRANS, int NS>
+template <int CPE, bool TRANS, int NCRT>
 __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                              const __grid_constant__ CUtensorMap msc) {
-    constexpr int RW = 32 / NS;                                // pixel rows per warp: NS lanes share a pixel
+    constexpr int NS = NCRT <= 16 ? 1 : NCRT / 16;             // 16-channel slabs = lanes per pixel
+    constexpr int RW = 32 / NS;                                // pixel rows per warp
     const Geo& g = a.g;
     const int RB = a.row_bytes;                                // packed row: pair (144*NS) or single tensor (80*NS)
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NSTAGES = g.ws + 3;
+    const int pw = radius_w(g);
+    const bool fold = g.wsw == 1;                              // folded 1-D signal: rows continue into neighbour columns
     const int w0 = blockIdx.x * 4, h0 = blockIdx.y * a.TH, u = blockIdx.z;
+    const int NSTAGES = g.wsw + min(3, g.W - 1 - w0);          // no stages for centre columns past the image
     CA_PIPE_PROLOGUE(false)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int slab = lane % NS, lrow = lane / NS;              // this lane's channel slab and row inside the warp
     const int lr = (lt >> 5) * RW + lrow, h = h0 + lr;         // row inside the tile, image row
     const bool active = h < g.H;
-    const int TR = RW + (TRANS ? 2 * g.p : 0);                 // CSR rows staged per warp and centre column
-    const int tile_floats = 4 * TR * g.ws;                     // one buffer: [4 centre columns][TR][ws]
-    // per warp: two tile buffers and the table of element offsets (row * K + e) inside a run block
+    // Values of A are staged for CH = min(ws, 32) window rows at a time, per centre column r in
+    // slot r (one shared slot when folded: a stage then pairs with a single column), as
+    // [tile row][CHS] with tile row = warp row (plain) or warp row + row inside the chunk
+    // (transposed: the CSR row of the streamed pixel).  Two buffers per warp: the next piece is
+    // copied while the current one is used.
+    const int CH = min(g.ws, kRunChunk), CHS = CH | 1;
+    const int TRW = RW + (TRANS ? CH - 1 : 0);
+    const int nslots = fold ? 1 : 4;
+    const int buf_floats = nslots * TRW * CHS;
     float* wbase = reinterpret_cast<float*>(smem_al + (size_t)kStages * a.stage_bytes) +
-                   (size_t)warp * (2 * tile_floats + TR * g.ws);
-    int* offs = reinterpret_cast<int*>(wbase + 2 * tile_floats);
+                   (size_t)warp * (2 * buf_floats + 2 * RW * CH);
     const int hw0 = h0 + (lt >> 5) * RW;                       // first image row of this warp
     const float* nzu = a.cs0 + (int64_t)u * g.Np * g.K;
-    const int nrows = hw0 >= g.H ? 0 : (TRANS ? TR : min(RW, g.H - hw0));
-    const int n = nrows * g.ws;
-    for (int idx = lane; idx < n; idx += 32) {
-        const int row = idx / g.ws, e = idx - row * g.ws;
-        int gr = hw0 + row - (TRANS ? g.p : 0);
-        gr %= g.H;
-        if (gr < 0) gr += g.H;
-        offs[idx] = gr * g.K + e;
+    const int rows_here = hw0 >= g.H ? 0 : min(RW, g.H - hw0);
+    const int nch = (g.ws + CH - 1) / CH;                      // pieces per stage
+    const int X = axis_len(g);
+    // 2-D windows that fit one piece: source and tile offsets of every staged element are the same
+    // for all stages and centre columns up to the column base; they come from two tables
+    const bool tabled = nch == 1 && !fold;
+    int* tsrc = reinterpret_cast<int*>(wbase + 2 * buf_floats);
+    int* tdst = tsrc + RW * CH;
+    if (tabled) {
+        for (int idx = lane; idx < RW * g.ws; idx += 32) {
+            const int wr = idx / g.ws, e = idx - wr * g.ws;
+            if (!TRANS) {
+                int posh = e + run_rot(hw0 + wr, g.H, g.p, g.ws);
+                posh -= (posh >= g.ws) ? g.ws : 0;
+                tsrc[idx] = (hw0 + wr) * g.K + posh;
+                tdst[idx] = wr * CHS + e;
+            } else {
+                const int tr = wr + e;
+                int hj = (hw0 + tr - g.p) % g.H;
+                hj += (hj < 0) ? g.H : 0;
+                tsrc[idx] = hj * g.K + axis_pos(g.p - e, hj, g.H, g.p, g.ws);
+                tdst[idx] = tr * CHS + e;
+            }
+        }
+        __syncwarp();
     }
-    __syncwarp();
 
-    // starts the copies of the runs that pair with stage s into tile buffer tb
-    auto fetch_runs = [&](int s, int tb) {
-        const int mask = stage_mask<4>(s, g.p);
+    // starts the copies for piece c of stage s into buffer tb
+    auto fetch_piece = [&](int s, int c, int tb) {
+        const int mask = stage_mask<4>(s, pw);
         const int wc = stage_column(g, w0, s);
-        float* tbuf = wbase + tb * tile_floats;
+        const int d0 = c * CH, len = min(CH, g.ws - d0);
+        float* tbuf = wbase + tb * buf_floats;
 #pragma unroll 1
         for (int r = 0; r < 4; ++r) {
             if (!((mask >> r) & 1) || w0 + r >= g.W) continue;
-            const int posw = TRANS ? axis_pos(r + g.p - s, wc, g.W, g.p, g.ws)
-                                   : axis_pos(s - g.p - r, w0 + r, g.W, g.p, g.ws);
-            const float* src = nzu + (int64_t)g.H * (TRANS ? wc : w0 + r) * g.K + posw * g.ws;
-            float* dst = tbuf + r * TR * g.ws;
+            float* dst = tbuf + (fold ? 0 : r) * TRW * CHS;
+            if (tabled) {
+                const int posw = TRANS ? axis_pos(r + pw - s, wc, g.W, pw, g.wsw)
+                                       : axis_pos(s - pw - r, w0 + r, g.W, pw, g.wsw);
+                const float* src = nzu + (int64_t)g.H * (TRANS ? wc : w0 + r) * g.K + posw * g.ws;
+                const int n = (TRANS ? RW : rows_here) * g.ws;
 #pragma unroll 4
-            for (int idx = lane; idx < n; idx += 32) cp_async4(dst + idx, src + offs[idx]);
+                for (int idx = lane; idx < n; idx += 32) cp_async4(dst + tdst[idx], src + tsrc[idx]);
+            } else if (!TRANS) {
+                const int posw = axis_pos(s - pw - r, w0 + r, g.W, pw, g.wsw);
+                const float* src = nzu + ((int64_t)g.H * (w0 + r) + hw0) * g.K + posw * g.ws;
+                const int n = rows_here * len;
+                for (int idx = lane; idx < n; idx += 32) {
+                    const int row = idx / len, e = idx - row * len;
+                    int posh = d0 + e + run_rot(axis_coord(g, hw0 + row, w0 + r), X, g.p, g.ws);
+                    posh -= (posh >= g.ws) ? g.ws : 0;
+                    cp_async4(dst + row * CHS + e, src + (int64_t)row * g.K + posh);
+                }
+            } else {
+                // entry (tile row tr, e) belongs to warp row tr - e: the CSR row of the streamed pixel
+                // (column wc, image row hw0 + d0 + tr - p), at the position of offset p - (d0 + e)
+                const int posw = axis_pos(r + pw - s, wc, g.W, pw, g.wsw);
+                const int n = RW * len;
+                for (int idx = lane; idx < n; idx += 32) {
+                    const int wr = idx / len, e = idx - wr * len;          // warp row, row inside the chunk
+                    const int tr = wr + e;
+                    int hj = hw0 + d0 + tr - g.p;
+                    int64_t rowidx;                                         // CSR row inside the unit
+                    int x;
+                    if (fold) {
+                        x = g.H * wc + hj;
+                        x %= X;
+                        x += (x < 0) ? X : 0;
+                        rowidx = x;
+                    } else {
+                        hj %= g.H;
+                        hj += (hj < 0) ? g.H : 0;
+                        x = hj;
+                        rowidx = hj + (int64_t)g.H * wc;
+                    }
+                    const int posh = axis_pos(g.p - d0 - e, x, X, g.p, g.ws);
+                    cp_async4(dst + tr * CHS + e, nzu + rowidx * g.K + posw * g.ws + posh);
+                }
+            }
         }
         cp_async_commit();
     };
@@ -735,68 +865,62 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[r][i] = zero2();
     }
-    const int hrot = (h < g.p) ? h - g.p + g.ws : (h >= g.H - g.p ? h - g.p - g.H + g.ws : 0);
-    fetch_runs(s_begin, 0);
+    fetch_piece(s_begin, 0, 0);
+    int piece = 0;                                             // pieces consumed so far (buffer = piece & 1)
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask<4>(s, g.p);
-        if (s + 1 < s_end) {
-            fetch_runs(s + 1, (it + 1) & 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncwarp();
-        const float* tile = wbase + (it & 1) * tile_floats;
+        const int mask = stage_mask<4>(s, pw);
         const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * RB;
-        // operands of window row di: the streamed vector and the four values of A; fetched one
-        // row ahead of the FMAs that use them
-        auto fetch_row = [&](int di, u64 (&vv)[8], float (&aa)[4]) {
-            lds_slab16<NS>(rowbase + di * RB, a.which, slab, vv);
-            int posh, trow;
-            if (!TRANS) {
-                posh = di + hrot;
-                posh -= (posh >= g.ws) ? g.ws : 0;
-                trow = lrow;
+        for (int c = 0; c < nch; ++c, ++piece) {
+            const int d0 = c * CH, len = min(CH, g.ws - d0);
+            if (c + 1 < nch) {
+                fetch_piece(s, c + 1, (piece + 1) & 1);
+                cp_async_wait<1>();
+            } else if (s + 1 < s_end) {
+                fetch_piece(s + 1, 0, (piece + 1) & 1);
+                cp_async_wait<1>();
             } else {
-                int hj = (active ? h : g.H - 1) + di - g.p;        // the row pixel of the entry (lanes past the image stay in range)
-                hj += (hj < 0) ? g.H : 0;
-                hj -= (hj >= g.H) ? g.H : 0;
-                posh = axis_pos(g.p - di, hj, g.H, g.p, g.ws);
-                trow = lrow + di;
+                cp_async_wait<0>();
             }
-            const float* ap = tile + trow * g.ws + posh;
+            __syncwarp();
+            const float* tile = wbase + (piece & 1) * buf_floats;
+            // operands of window row d0 + e: the streamed vector and the four values of A, fetched
+            // one row ahead of the FMAs that use them
+            auto fetch_row = [&](int e, u64 (&vv)[8], float (&aa)[4]) {
+                lds_slab16<NS>(rowbase + (d0 + e) * RB, a.which, slab, vv);
+                const float* ap = tile + (lrow + (TRANS ? e : 0)) * CHS + e;
 #pragma unroll
-            for (int r = 0; r < 4; ++r) aa[r] = ((mask >> r) & 1) ? ap[r * TR * g.ws] : 0.f;
-        };
-        u64 vn[8];
-        float an[4];
-        fetch_row(0, vn, an);
+                for (int r = 0; r < 4; ++r) aa[r] = ((mask >> r) & 1) ? ap[(fold ? 0 : r) * TRW * CHS] : 0.f;
+            };
+            u64 vn[8];
+            float an[4];
+            fetch_row(0, vn, an);
 #pragma unroll 2
-        for (int di = 0; di < g.ws; ++di) {
-            u64 v2[8];
-            float av[4];
+            for (int e = 0; e < len; ++e) {
+                u64 v2[8];
+                float av[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v2[i] = vn[i];
+                for (int i = 0; i < 8; ++i) v2[i] = vn[i];
 #pragma unroll
-            for (int r = 0; r < 4; ++r) av[r] = an[r];
-            if (di + 1 < g.ws) fetch_row(di + 1, vn, an);
+                for (int r = 0; r < 4; ++r) av[r] = an[r];
+                if (e + 1 < len) fetch_row(e + 1, vn, an);
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                if ((mask >> r) & 1) {
-                    asum[r] += av[r];
-                    const u64 a2 = pack2(av[r], av[r]);
+                for (int r = 0; r < 4; ++r) {
+                    if ((mask >> r) & 1) {
+                        asum[r] += av[r];
+                        const u64 a2 = pack2(av[r], av[r]);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[r][i] = fma2(a2, v2[i], acc[r][i]);
+                        for (int i = 0; i < 8; ++i) acc[r][i] = fma2(a2, v2[i], acc[r][i]);
+                    }
                 }
             }
+            __syncwarp();
         }
-        __syncwarp();
     })
 
     if (a.c0) {
         u64 ctr[4][8];
-        load_centre<CPE, 4, 16 * NS>(a.c0, g, u, h, w0, active, 1.f, ctr, 16 * slab);
+        load_centre<CPE, 4, NCRT>(a.c0, g, u, h, w0, active, 1.f, ctr, 16 * slab);
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             const u64 ns = pack2(-asum[r], -asum[r]);
@@ -810,7 +934,7 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
         for (int i = 0; i < 8; ++i) {
             float x, y;
             unpack2(acc[r][i], x, y);
-            store_centre<CPE, 16 * NS>(a.o0, g, u, h, w0, active, r, i, a.scale * x, a.scale * y, 16 * slab);
+            store_centre<CPE, NCRT>(a.o0, g, u, h, w0, active, r, i, a.scale * x, a.scale * y, 16 * slab);
         }
 }
 
@@ -868,7 +992,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
                                                           const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NSTAGES = g.ws + NQ - 1;
+    const int NSTAGES = g.wsw + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
@@ -899,7 +1023,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
     }
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask<NQ>(s, g.p);
+        const int mask = stage_mask<NQ>(s, radius_w(g));
         CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dq_stage<DIST, MK, NQ>(smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes, g.ws, mask,
                                                      sl2, q, dy, dq, nL2, nD2, bq, sumds)));
     })
@@ -1000,7 +1124,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
                                                             const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
-    const int NSTAGES = g.ws + NQ - 1;
+    const int NSTAGES = g.wsw + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(true)
@@ -1029,7 +1153,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
     }
 
     CA_PIPE_LOOP({
-        const int mask = stage_mask<NQ>(s, g.p);
+        const int mask = stage_mask<NQ>(s, radius_w(g));
         CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dkdv_stage<DIST, MK, NQ>(smem_u32(pipe.vec(buf)), pipe.sc0(buf), pipe.sc1(buf),
                                                       lr + a.roff, g.ws, mask, sl2, k, v, dk, dv, bk, sumds)));
     })
@@ -1102,9 +1226,10 @@ struct PackArgs {
     float* Dout;            // nullable: D in the reference layout (interior rows)
 };
 
-template <int CPE, int NS>
+template <int CPE, int NCRT>
 __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
-    constexpr int NCR = 16 * NS;
+    constexpr int NS = NCRT <= 16 ? 1 : NCRT / 16;
+    constexpr int NCR = NCRT;
     const Geo& g = a.g;
     const int rr = blockIdx.x * blockDim.x + threadIdx.x;
     const int w = blockIdx.y;
@@ -1114,8 +1239,17 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
     const int u = blockIdx.z / slots, slot = blockIdx.z % slots;
     if (rr >= a.Hp) return;
     const bool real_row = rr < g.H + 2 * a.pp;
-    const int hs = real_row ? (rr - a.pp + g.H) % g.H : 0;
-    const int pix = hs + g.H * w;
+    // source pixel of packed row rr: the halo rows wrap inside the column (2-D) or continue into the
+    // neighbouring columns of a folded 1-D signal
+    int pix = 0;
+    if (real_row) {
+        if (g.wsw == 1) {
+            pix = (g.H * w + rr - a.pp) % g.Npk;
+            if (pix < 0) pix += g.Npk;
+        } else {
+            pix = (rr - a.pp + g.H) % g.H + g.H * w;
+        }
+    }
     const int64_t orow = ((int64_t)u * g.Wk + w) * a.Hp + rr;
     if (slot < nt * a.npairs) {
         const int pair = slot / nt, t = slot % nt;
@@ -1130,7 +1264,7 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
 #pragma unroll
             for (int sl = 0; sl < NS; ++sl) {
                 const int cc = 16 * sl + 4 * c;
-                if (!real_row) {
+                if (!real_row || cc >= NCR) {             // padding rows; channels past a narrow unit
                     vals[sl] = make_float4(0.f, 0.f, 0.f, 0.f);
                 } else if (CPE == 1) {
                     const float* sp = src + goff<1, NCR>(u, cc, g.Npk, pix);
@@ -1183,24 +1317,47 @@ struct Padded {
     size_t plane_floats;    // both scalar planes
 };
 
+int slabs_of(const Geo& g) { return g.cr <= 16 ? 1 : g.cr / 16; }
+
 Padded padded_of(const Geo& g) {
     Padded P;
     P.pp = (g.p + 1) & ~1;
     P.Hp = (g.H + 2 * P.pp + 3) & ~3;
-    P.pair_floats = (size_t)g.units * g.Wk * P.Hp * kRowFloats * (g.cr / 16);
-    P.single_floats = (size_t)g.units * g.Wk * P.Hp * kSingleFloats * (g.cr / 16);
+    P.pair_floats = (size_t)g.units * g.Wk * P.Hp * kRowFloats * slabs_of(g);
+    P.single_floats = (size_t)g.units * g.Wk * P.Hp * kSingleFloats * slabs_of(g);
     P.plane_floats = (size_t)2 * g.units * g.Wk * P.Hp;
     return P;
 }
 
 bool tiled_shape_ok(const Geo& g) {
-    return g.cr == 16 && g.wsw == g.ws && g.ws >= 3 && g.H >= 16 && g.ws <= 63;
+    return g.cr == 16 && (g.wsw == g.ws || g.wsw == 1) && g.ws >= 3 && g.H >= 16 && g.ws <= (g.wsw == 1 ? 127 : 63);
 }
 
-// The stand-alone operator kernels also take 32 or 64 real channels per unit (2 or 4 lanes per pixel).
+// The stand-alone operator kernels also take 8 (zero-extended), 32 or 64 real channels per unit
+// (2 or 4 lanes per pixel for the wide ones).
 bool tiled_operator_ok(const Geo& g) {
-    return (g.cr == 16 || g.cr == 32 || g.cr == 64) && g.wsw == g.ws && g.ws >= 3 && g.H >= 16 && g.ws <= 63 &&
-           g.Wk == g.W;
+    return (g.cr == 8 || g.cr == 16 || g.cr == 32 || g.cr == 64) && (g.wsw == g.ws || g.wsw == 1) && g.ws >= 3 &&
+           g.H >= 16 && g.ws <= (g.wsw == 1 ? 127 : 63) && g.Wk == g.W;
+}
+
+// The geometry the tiled kernels run on.  2-D problems are taken as they are.  A 1-D signal of
+// length N (H = N, W = 1) is folded column-major into an Hf x (N / Hf) image: pixel n = h + Hf*w keeps
+// its address, its window is the rows h-p..h+p of its own column, and the halo rows of the packed
+// columns continue into the neighbouring columns (the pack kernel fills them by linear index), so
+// the 2-D kernels run unchanged with a window that is one column wide.
+bool fold_geo(const Geo& in, Geo* out) {
+    *out = in;
+    if (in.wsw == in.ws) return true;                      // 2-D
+    if (in.wsw != 1 || in.Wk != in.W) return false;
+    if (in.W != 1) return true;                            // already folded
+    for (int hf : {128, 96, 64, 48, 32, 16}) {
+        if (in.H % hf == 0 && in.H / hf >= 1) {
+            out->H = hf;
+            out->W = out->Wk = in.H / hf;
+            return true;
+        }
+    }
+    return false;
 }
 
 int env_int(const char* name, int dflt) {
@@ -1219,13 +1376,14 @@ int pick_dc(int ws) {
 
 int launch_pack(const PackArgs& a, cudaStream_t st) {
     dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * ((a.single ? 1 : 2) * a.npairs + (a.planes ? 1 : 0)));
-    const int ns = a.g.cr / 16;
-    if (a.planes && ns != 1) { set_error("scalar planes are packed for 16-channel units only"); return CA_ERR_UNSUPPORTED; }
-#define CA_PACK(CPEV)                                                      \
-    do {                                                                   \
-        if (ns == 1) pack_kernel<CPEV, 1><<<grid, 128, 0, st>>>(a);        \
-        else if (ns == 2) pack_kernel<CPEV, 2><<<grid, 128, 0, st>>>(a);   \
-        else pack_kernel<CPEV, 4><<<grid, 128, 0, st>>>(a);                \
+    const int cr = a.g.cr;
+    if (a.planes && cr != 16) { set_error("scalar planes are packed for 16-channel units only"); return CA_ERR_UNSUPPORTED; }
+#define CA_PACK(CPEV)                                                        \
+    do {                                                                     \
+        if (cr == 8) pack_kernel<CPEV, 8><<<grid, 128, 0, st>>>(a);          \
+        else if (cr == 16) pack_kernel<CPEV, 16><<<grid, 128, 0, st>>>(a);   \
+        else if (cr == 32) pack_kernel<CPEV, 32><<<grid, 128, 0, st>>>(a);   \
+        else pack_kernel<CPEV, 64><<<grid, 128, 0, st>>>(a);                 \
     } while (0)
     if (a.g.cpe == 1) CA_PACK(1);
     else CA_PACK(2);
@@ -1319,6 +1477,7 @@ int set_smem(K kernel, size_t bytes) {
         int rc__ = set_smem(KERNEL, (L).smem);                                        \
         if (rc__) return rc__;                                                        \
         KERNEL<<<(L).grid, (L).threads, (L).smem, st>>>((L).a, (L).mv, (L).msc);      \
+        count_tiled_launch();                                                         \
     } while (0)
 
 #define CA_DIST_CPE(KERNEL_T, dist, cpe, L, st)                                       \
@@ -1414,18 +1573,24 @@ int encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint6
 }
 
 // ---------------------------------------------------------------- entry points of this file
-size_t tiled_fwd_workspace(const Geo& g) {
+size_t tiled_fwd_workspace(const Geo& gin) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return 0;
     if (!tiled_shape_ok(g)) return 0;
     return (padded_of(g).pair_floats + (size_t)g.Np * g.units) * sizeof(float);
 }
 
-size_t tiled_bwd_stage_workspace(const Geo& g) {
+size_t tiled_bwd_stage_workspace(const Geo& gin) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return 0;
     if (!tiled_shape_ok(g)) return 0;
     const Padded P = padded_of(g);
     return (P.pair_floats + P.plane_floats) * sizeof(float);
 }
 
-size_t tiled_bwd_workspace(const Geo& g) {
+size_t tiled_bwd_workspace(const Geo& gin) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return 0;
     if (!tiled_shape_ok(g)) return 0;
     const Padded P = padded_of(g);
     return (2 * P.pair_floats + P.plane_floats) * sizeof(float);
@@ -1440,8 +1605,10 @@ int tiled_stage_timeouts(int* count) {
 int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const float* stats, float* nz,
                  void* workspace, cudaStream_t st, bool single = false);
 
-int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
+int tiled_attention_fwd(const Geo& gin, float scale, int dist, const float* q, const float* k, const float* v,
                         float* y, float* nz, float* stats, void* workspace, cudaStream_t st) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
     if (!tiled_shape_ok(g) || (nz && g.Wk != g.W)) return CA_ERR_UNSUPPORTED;
     if (!workspace) { set_error("workspace of ca_attention_fwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
     const Padded P = padded_of(g);
@@ -1496,12 +1663,16 @@ int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const floa
                  void* workspace, cudaStream_t st, bool single) {
     if (!tiled_operator_ok(g)) return CA_ERR_UNSUPPORTED;
     const Padded P = padded_of(g);
-    const int ns = g.cr / 16;
+    const int ns = slabs_of(g);
     Launch L{};
     int rc = prepare(g, P, 4, 0, "CIRCATT_FWD_WARPS", static_cast<const float*>(workspace), nullptr, &L, true, 4, ns,
                      single);
     if (rc) return rc;
-    L.smem += (size_t)L.threads / 32 * 4 * (32 / ns) * g.ws * sizeof(float);
+    {
+        const int ch = std::min(g.ws, kRunChunk), nslots = g.wsw == 1 ? 1 : 4;
+        L.smem += (size_t)L.threads / 32 * (32 / ns) * (nslots * (ch + 1) + 4 + ch) * sizeof(float);
+    }
+    if (L.smem > 200 * 1024) return CA_ERR_UNSUPPORTED;
 #define CA_EMIT(NSV)                                                                  \
     do {                                                                              \
         if (g.cpe == 1) {                                                             \
@@ -1513,17 +1684,20 @@ int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const floa
         }                                                                             \
     } while (0)
     L.a.scale = scale; L.a.c0 = q; L.a.cs0 = stats; L.a.o0 = nz;
-    if (ns == 1) CA_EMIT(1);
-    else if (ns == 2) CA_EMIT(2);
-    else CA_EMIT(4);
+    if (g.cr == 8) CA_EMIT(8);
+    else if (g.cr == 16) CA_EMIT(16);
+    else if (g.cr == 32) CA_EMIT(32);
+    else CA_EMIT(64);
 #undef CA_EMIT
     CA_CHECK_LAUNCH("tiled A kernel");
     return CA_OK;
 }
 
-int tiled_attention_bwd_dq(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
+int tiled_attention_bwd_dq(const Geo& gin, float scale, int dist, const float* q, const float* k, const float* v,
                            const float* dy, const float* stats, const float* D, float* dq, void* workspace,
                            cudaStream_t st) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
     if (!tiled_shape_ok(g)) return CA_ERR_UNSUPPORTED;
     if (!workspace) { set_error("workspace of ca_attention_bwd_stage_workspace() bytes is NULL"); return CA_ERR_NULL; }
     const Padded P = padded_of(g);
@@ -1536,9 +1710,11 @@ int tiled_attention_bwd_dq(const Geo& g, float scale, int dist, const float* q, 
     return run_dq(g, P, scale, dist, q, dy, stats, D, kv, dq, st);
 }
 
-int tiled_attention_bwd_dkdv(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
+int tiled_attention_bwd_dkdv(const Geo& gin, float scale, int dist, const float* q, const float* k, const float* v,
                              const float* dy, const float* stats, const float* D, float* dk, float* dv,
                              void* workspace, cudaStream_t st) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
     if (!tiled_shape_ok(g)) return CA_ERR_UNSUPPORTED;
     if (!workspace) { set_error("workspace of ca_attention_bwd_stage_workspace() bytes is NULL"); return CA_ERR_NULL; }
     const Padded P = padded_of(g);
@@ -1580,9 +1756,11 @@ static ForkJoin* fork_join_for_current_device() {
 }
 
 // Whole backward in three launches: pack (both pairs, D, planes), dq, dk/dv.
-int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
+int tiled_attention_bwd(const Geo& gin, float scale, int dist, const float* q, const float* k, const float* v,
                         const float* y, const float* dy, const float* stats, float* D, float* dq, float* dk,
                         float* dv, void* workspace, cudaStream_t st) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
     if (!tiled_shape_ok(g) || g.Wk != g.W) return CA_ERR_UNSUPPORTED;
     if (!workspace) { set_error("workspace is NULL"); return CA_ERR_NULL; }
     const Padded P = padded_of(g);
@@ -1615,7 +1793,9 @@ int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, con
 }
 
 // ---------------------------------------------------------------- stand-alone operators
-size_t tiled_operator_workspace(const Geo& g) {
+size_t tiled_operator_workspace(const Geo& gin) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return 0;
     if (!tiled_operator_ok(g)) return 0;
     return padded_of(g).single_floats * sizeof(float);
 }
@@ -1629,8 +1809,10 @@ static int pack_single(const Geo& g, const Padded& P, const float* src, float* d
 }
 
 // Scaled similarity scores in CSR order: x indexes the row pixel, y the column pixel.
-int tiled_similarity(const Geo& g, float scale, int dist, const float* x, const float* y, float* nz,
+int tiled_similarity(const Geo& gin, float scale, int dist, const float* x, const float* y, float* nz,
                      void* workspace, cudaStream_t st) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
     if (!workspace || !tiled_operator_workspace(g)) return CA_ERR_UNSUPPORTED;
     int rc = pack_single(g, padded_of(g), y, static_cast<float*>(workspace), st);
     if (rc) return rc;
@@ -1640,11 +1822,13 @@ int tiled_similarity(const Geo& g, float scale, int dist, const float* x, const 
 static int run_apply(const Geo& g, const Padded& P, const float* nz, const float* packed,
                      const float* centre, float* out, float alpha, int transposed, cudaStream_t st) {
     Launch L{};
-    const int ns = g.cr / 16;
+    const int ns = slabs_of(g);
     int rc = prepare(g, P, 4, 0, "CIRCATT_APPLY_WARPS", packed, nullptr, &L, false, ns == 1 ? 2 : 4, ns, true);
     if (rc) return rc;
-    const int TR = 32 / ns + (transposed ? 2 * g.p : 0);
-    L.smem += (size_t)L.threads / 32 * 9 * TR * g.ws * sizeof(float);     // two tile buffers + offsets per warp
+    const int ch = std::min(g.ws, kRunChunk), chs = ch | 1;
+    const int trw = 32 / ns + (transposed ? ch - 1 : 0);
+    // per warp: two buffers and the two offset tables
+    L.smem += (size_t)L.threads / 32 * (2 * (g.wsw == 1 ? 1 : 4) * trw * chs + 2 * (32 / ns) * ch) * sizeof(float);
     if (L.smem > 200 * 1024) return CA_ERR_UNSUPPORTED;
     L.a.scale = alpha; L.a.which = 0; L.a.c0 = centre; L.a.cs0 = nz; L.a.o0 = out;
 #define CA_APPLY(NSV)                                                                     \
@@ -1657,17 +1841,20 @@ static int run_apply(const Geo& g, const Padded& P, const float* nz, const float
             else CA_LAUNCH_TILED((apply_tiled_kernel<2, false, NSV>), L, st);             \
         }                                                                                 \
     } while (0)
-    if (ns == 1) CA_APPLY(1);
-    else if (ns == 2) CA_APPLY(2);
-    else CA_APPLY(4);
+    if (g.cr == 8) CA_APPLY(8);
+    else if (g.cr == 16) CA_APPLY(16);
+    else if (g.cr == 32) CA_APPLY(32);
+    else CA_APPLY(64);
 #undef CA_APPLY
     CA_CHECK_LAUNCH("tiled apply kernel");
     return CA_OK;
 }
 
 // out = alpha * (A (x) v) or alpha * (A^T (x) v) from the values of A in CSR order.
-int tiled_apply(const Geo& g, const float* nz, const float* v, float* out, float alpha, int transposed,
+int tiled_apply(const Geo& gin, const float* nz, const float* v, float* out, float alpha, int transposed,
                 void* workspace, cudaStream_t st) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
     if (!workspace || !tiled_operator_workspace(g)) return CA_ERR_UNSUPPORTED;
     const Padded P = padded_of(g);
     float* packed = static_cast<float*>(workspace);
@@ -1678,8 +1865,10 @@ int tiled_apply(const Geo& g, const float* nz, const float* v, float* out, float
 
 // Pullback of the similarity: dx[j] = scale * sum_i dS[j,i] y[i], dy[i] = scale * sum_j dS[j,i] x[j]
 // (Distance: minus the sum of the dS involved times the pixel's own vector).
-int tiled_similarity_bwd(const Geo& g, float scale, int dist, const float* x, const float* y, const float* dS,
+int tiled_similarity_bwd(const Geo& gin, float scale, int dist, const float* x, const float* y, const float* dS,
                          float* dx, float* dy, void* workspace, cudaStream_t st) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
     if (!workspace || !tiled_operator_workspace(g)) return CA_ERR_UNSUPPORTED;
     const Padded P = padded_of(g);
     float* packed = static_cast<float*>(workspace);

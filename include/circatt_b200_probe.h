@@ -14,6 +14,10 @@ extern "C" {
 /* Number of kernels this library has launched in the calling process so far. */
 int64_t ca_probe_launch_count(void);
 
+/* Of those, the launches of the TMA-tiled kernels (the tests use the difference around a call
+ * to assert that the call ran on the tiled path and not on the generic kernels). */
+int64_t ca_probe_tiled_launch_count(void);
+
 /* Launches one kernel of `blocks` x 256 threads; each thread runs `iters`
  * rounds of 16 independent packed FP32 FMAs (fma.rn.f32x2) on registers and
  * stores one value to `sink` (blocks*256 floats).  The kernel executes

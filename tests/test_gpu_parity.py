@@ -262,6 +262,13 @@ TILED_OPERATOR_CASES = [
     ((24, 20), 5, 64, 2, False),        # 64 real channels: four lanes per pixel
     ((40, 21), 7, 32, 1, True),         # 32 complex channels (BASELINE config 4's channel count)
     ((16, 16), 3, 64, 3, False),        # smallest window, two warps of rows
+    ((40, 24), 7, 8, 2, False),         # 8 channels per unit: zero-extended to one slab
+    ((64, 40), 35, 16, 1, False),       # window wider than the 32-row staging chunk
+    ((256,), 9, 16, 2, False),          # 1-D signal, folded into 128-row columns
+    ((384,), 33, 8, 3, False),          # 1-D, 8 channels, three columns, chunked window
+    ((4096,), 127, 8, 2, False),        # BASELINE config 3's window and channel count
+    ((96,), 5, 16, 1, True),            # 1-D that folds into a single column (wraps onto itself)
+    ((64,), 7, 64, 2, False),           # 1-D, four lanes per pixel
 ]
 
 
@@ -276,11 +283,15 @@ def test_tiled_similarity_and_pullback(ca, spatial, ws, c, units, cplx, simname)
     m = ca.ops.meta_of(x, ws)
     assert ca._lib.lib.ca_operator_workspace(m.desc()) > 0           # the shape is covered by the tiled kernels
     scale = 0.37
+    lib = ca._lib.lib
+    n0 = lib.ca_probe_tiled_launch_count()
     S = ca.ops.similarity(KIND[simname], x, y, ws, scale)
+    assert lib.ca_probe_tiled_launch_count() == n0 + 1               # ... and ran on them
     So = scale * orc.similarity(KIND[simname], up(xn), up(yn), ws)
     assert rel_err(ca.jl.to_numpy(S), So.reshape(S.shape, order="F")) < TOL
     dSn = np.asfortranarray(rng.standard_normal(tuple(S.shape)).astype(np.float32))
     dx, dy = ca.ops.similarity_bwd(KIND[simname], x, y, ws, ca.jl.from_numpy(dSn), scale)
+    assert lib.ca_probe_tiled_launch_count() == n0 + 3               # one plain and one transposed apply
     dxo, dyo = orc.similarity_pullback(KIND[simname], up(xn), up(yn), ws,
                                        scale * dSn.astype(np.float64).reshape(So.shape, order="F"))
     assert rel_err(ca.jl.to_numpy(dx), dxo) < TOL
@@ -292,10 +303,12 @@ def test_tiled_similarity_and_pullback(ca, spatial, ws, c, units, cplx, simname)
 def test_tiled_apply(ca, spatial, ws, c, units, cplx, transpose):
     """R6 (src/batchedmul.jl:82-150 as used by src/attention.jl:53-80) on the tiled kernels."""
     rng = np.random.default_rng(22)
-    K, Np = ws ** 2, int(np.prod(spatial))
+    K, Np = ws ** len(spatial), int(np.prod(spatial))
     nzn = np.asfortranarray(rng.standard_normal((Np * K, units)).astype(np.float32))
     vn = randn(rng, spatial + (c, units), cplx)
+    n0 = ca._lib.lib.ca_probe_tiled_launch_count()
     out = ca.ops.apply(ca.jl.from_numpy(nzn), ca.jl.from_numpy(vn), ws, transpose)
+    assert ca._lib.lib.ca_probe_tiled_launch_count() == n0 + 1       # the tiled kernel ran, not the generic one
     oo = orc.apply(nzn.astype(np.float64).reshape((K, Np, units), order="F"), up(vn), ws, transpose)
     assert rel_err(ca.jl.to_numpy(out), oo) < TOL
 
