@@ -141,6 +141,78 @@ def reference_main(args):
     print(json.dumps(line))
 
 
+
+# --------------------------------------------------------------------------- other configurations (--extra)
+EXTRA_CONFIGS = {
+    # name: (Julia shape, ws, heads, similarity, normaliser, complex, A materialised)
+    "c1": ((32, 32, 16, 1), 7, 1, 0, 0, False, True),
+    "c2": ((128, 96, 64, 2), 15, 4, 0, 0, False, False),
+    "c3": ((16384, 64, 16), 127, 8, 1, 1, False, False),          # 1-D, Distance, entmax-1.5
+    "c4": ((320, 320, 32, 8), 7, 1, 0, 0, True, True),            # ComplexF32, A materialised
+    "c5_one_batch": ((1024, 1024, 128, 1), 21, 8, 0, 0, False, False),
+}
+
+
+def extra_main(args):
+    """Not the headline: forward / backward times of the other BASELINE configurations and of the
+    stand-alone operators at the bench shape, one JSON line.  L2 is flushed before every timed call."""
+    import torch
+    from __graft_entry__ import load_package
+    torch.cuda.set_device(0)
+    ca = load_package()
+    ops, jl = ca.ops, ca.jl
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, n=5):
+        fn(); fn()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for a, b in evs:
+            for _ in range(4):
+                flush.fill_(1)             # also lets the host run ahead of the device
+            a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        return sorted(a.elapsed_time(b) * 1e-3 for a, b in evs)[n // 2]
+
+    out = {"configs": {}, "operators_c2_us": {}}
+    for name, (shape, ws, nh, kind, norm, cplx, want_nz) in EXTRA_CONFIGS.items():
+        dt = torch.complex64 if cplx else torch.float32
+        q, k, v, dy = (ca.splitheads(jl.randn(*shape, generator=gen, dtype=dt), nh) for _ in range(4))
+        C = shape[-2] * (2 if cplx else 1)
+        Np, K = int(np.prod(shape[:-2])), ws ** (len(shape) - 2)
+        px = Np * shape[-1]
+        res = {}
+        tf = timed(lambda: res.__setitem__("r", ops.attention_fwd(kind, norm, q, k, v, ws, want_nz)))
+        y, nz, stats = res["r"]
+        tb = timed(lambda: ops.attention_bwd(kind, norm, q, k, v, y, dy, stats, ws, nz=nz))
+        fl_f, fl_b = (5 if kind else 4) * K * C, (11 if kind else 10) * K * C
+        out["configs"][name] = {
+            "fwd_us": tf * 1e6, "bwd_us": tb * 1e6, "fwd_px_per_s": px / tf, "fwd_bwd_px_per_s": px / (tf + tb),
+            "fwd_tflops": px * fl_f / tf / 1e12, "bwd_tflops": px * fl_b / tb / 1e12}
+        del q, k, v, dy, y, nz, stats, res
+        torch.cuda.empty_cache()
+    H, W, C, B, ws, nh = (WORKLOAD[k_] for k_ in ("H", "W", "C", "B", "ws", "nheads"))
+    q, k, v = (ca.splitheads(jl.randn(H, W, C, B, generator=gen), nh) for _ in range(3))
+    nz = ops.similarity(0, q, k, ws)
+    P = ops.row_normalize(nz, (H, W), ws, 0)
+    for name, fn in {
+        "similarity": lambda: ops.similarity(0, q, k, ws),
+        "row_softmax": lambda: ops.row_normalize(nz, (H, W), ws, 0),
+        "row_entmax15": lambda: ops.row_normalize(nz, (H, W), ws, 1),
+        "row_softmax_bwd": lambda: ops.row_normalize_bwd(P, nz, (H, W), ws, 0),
+        "apply": lambda: ops.apply(P, v, ws),
+        "apply_transposed": lambda: ops.apply(P, v, ws, True),
+        "similarity_bwd": lambda: ops.similarity_bwd(0, q, k, ws, nz),
+        "axpby": lambda: ops.axpby(1.0, P, 2.0, nz),
+        "sum_rows": lambda: ops.sum_rows(P, (H, W), ws),
+        "sum_cols": lambda: ops.sum_cols(P, (H, W), ws),
+        "structure": lambda: ops.structure((H, W), ws, (nh, B), "cuda"),
+    }.items():
+        out["operators_c2_us"][name] = timed(fn) * 1e6
+    out["operators_c2_nz_mbytes"] = nz.numel() * 4 / 1e6
+    print(json.dumps(out))
+
+
 # --------------------------------------------------------------------------- B200 arm
 def main():
     ap = argparse.ArgumentParser()
@@ -149,7 +221,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--extra", action="store_true",
+                    help="time the other configurations and the stand-alone operators instead of the headline step")
     args = ap.parse_args()
+    if args.extra:
+        return extra_main(args)
     if args.impl == "reference":
         return reference_main(args)
 

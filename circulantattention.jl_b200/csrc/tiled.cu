@@ -769,16 +769,16 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
     const int TRW = RW + (TRANS ? CH - 1 : 0);
     const int nslots = fold ? 1 : 4;
     const int buf_floats = nslots * TRW * CHS;
-    float* wbase = reinterpret_cast<float*>(smem_al + (size_t)kStages * a.stage_bytes) +
-                   (size_t)warp * (2 * buf_floats + 2 * RW * CH);
-    const int hw0 = h0 + (lt >> 5) * RW;                       // first image row of this warp
-    const float* nzu = a.cs0 + (int64_t)u * g.Np * g.K;
-    const int rows_here = hw0 >= g.H ? 0 : min(RW, g.H - hw0);
     const int nch = (g.ws + CH - 1) / CH;                      // pieces per stage
-    const int X = axis_len(g);
     // 2-D windows that fit one piece: source and tile offsets of every staged element are the same
     // for all stages and centre columns up to the column base; they come from two tables
     const bool tabled = nch == 1 && !fold;
+    float* wbase = reinterpret_cast<float*>(smem_al + (size_t)kStages * a.stage_bytes) +
+                   (size_t)warp * (2 * buf_floats + (tabled ? 2 * RW * CH : 0));
+    const int hw0 = h0 + (lt >> 5) * RW;                       // first image row of this warp
+    const float* nzu = a.cs0 + (int64_t)u * g.Np * g.K;
+    const int rows_here = hw0 >= g.H ? 0 : min(RW, g.H - hw0);
+    const int X = axis_len(g);
     int* tsrc = reinterpret_cast<int*>(wbase + 2 * buf_floats);
     int* tdst = tsrc + RW * CH;
     if (tabled) {
@@ -806,6 +806,9 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
         const int wc = stage_column(g, w0, s);
         const int d0 = c * CH, len = min(CH, g.ws - d0);
         float* tbuf = wbase + tb * buf_floats;
+        if (hw0 >= g.H) { cp_async_commit(); return; }                 // warp past the image: nothing to stage
+        const int row0 = lane / len, e0 = lane - row0 * len;           // first element of this lane
+        const int drow = 32 / len, de = 32 - drow * len;               // step of 32 elements
 #pragma unroll 1
         for (int r = 0; r < 4; ++r) {
             if (!((mask >> r) & 1) || w0 + r >= g.W) continue;
@@ -821,36 +824,42 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
                 const int posw = axis_pos(s - pw - r, w0 + r, g.W, pw, g.wsw);
                 const float* src = nzu + ((int64_t)g.H * (w0 + r) + hw0) * g.K + posw * g.ws;
                 const int n = rows_here * len;
+                int row = row0, e = e0;                                    // element idx = row*len + e
                 for (int idx = lane; idx < n; idx += 32) {
-                    const int row = idx / len, e = idx - row * len;
                     int posh = d0 + e + run_rot(axis_coord(g, hw0 + row, w0 + r), X, g.p, g.ws);
                     posh -= (posh >= g.ws) ? g.ws : 0;
                     cp_async4(dst + row * CHS + e, src + (int64_t)row * g.K + posh);
+                    row += drow;
+                    e += de;
+                    if (e >= len) { e -= len; ++row; }
                 }
             } else {
                 // entry (tile row tr, e) belongs to warp row tr - e: the CSR row of the streamed pixel
                 // (column wc, image row hw0 + d0 + tr - p), at the position of offset p - (d0 + e)
                 const int posw = axis_pos(r + pw - s, wc, g.W, pw, g.wsw);
                 const int n = RW * len;
+                int wr = row0, e = e0;                                     // warp row, row inside the chunk
                 for (int idx = lane; idx < n; idx += 32) {
-                    const int wr = idx / len, e = idx - wr * len;          // warp row, row inside the chunk
                     const int tr = wr + e;
                     int hj = hw0 + d0 + tr - g.p;
                     int64_t rowidx;                                         // CSR row inside the unit
                     int x;
                     if (fold) {
-                        x = g.H * wc + hj;
-                        x %= X;
+                        x = (g.H * wc + hj) % X;
                         x += (x < 0) ? X : 0;
                         rowidx = x;
                     } else {
-                        hj %= g.H;
-                        hj += (hj < 0) ? g.H : 0;
+                        hj += (hj < 0) ? g.H : 0;                          // here ws > 32, so H > 32 > the tile's
+                        hj -= (hj >= g.H) ? g.H : 0;                       // overhang: two subtractions suffice
+                        hj -= (hj >= g.H) ? g.H : 0;
                         x = hj;
                         rowidx = hj + (int64_t)g.H * wc;
                     }
                     const int posh = axis_pos(g.p - d0 - e, x, X, g.p, g.ws);
                     cp_async4(dst + tr * CHS + e, nzu + rowidx * g.K + posw * g.ws + posh);
+                    wr += drow;
+                    e += de;
+                    if (e >= len) { e -= len; ++wr; }
                 }
             }
         }
@@ -1823,12 +1832,14 @@ static int run_apply(const Geo& g, const Padded& P, const float* nz, const float
                      const float* centre, float* out, float alpha, int transposed, cudaStream_t st) {
     Launch L{};
     const int ns = slabs_of(g);
-    int rc = prepare(g, P, 4, 0, "CIRCATT_APPLY_WARPS", packed, nullptr, &L, false, ns == 1 ? 2 : 4, ns, true);
+    // 2-D, one slab: two warps of rows per CTA (smaller stages, more CTAs per SM); otherwise four
+    int rc = prepare(g, P, 4, 0, "CIRCATT_APPLY_WARPS", packed, nullptr, &L, false, (ns == 1 && g.wsw != 1) ? 2 : 4, ns, true);
     if (rc) return rc;
     const int ch = std::min(g.ws, kRunChunk), chs = ch | 1;
     const int trw = 32 / ns + (transposed ? ch - 1 : 0);
-    // per warp: two buffers and the two offset tables
-    L.smem += (size_t)L.threads / 32 * (2 * (g.wsw == 1 ? 1 : 4) * trw * chs + 2 * (32 / ns) * ch) * sizeof(float);
+    // per warp: two buffers and, for single-piece 2-D windows, the two offset tables
+    const bool tabled = g.ws <= kRunChunk && g.wsw != 1;
+    L.smem += (size_t)L.threads / 32 * (2 * (g.wsw == 1 ? 1 : 4) * trw * chs + (tabled ? 2 * (32 / ns) * ch : 0)) * sizeof(float);
     if (L.smem > 200 * 1024) return CA_ERR_UNSUPPORTED;
     L.a.scale = alpha; L.a.which = 0; L.a.c0 = centre; L.a.cs0 = nz; L.a.o0 = out;
 #define CA_APPLY(NSV)                                                                     \
