@@ -109,6 +109,7 @@ def cpu_step(cpu, orc, arrs, workload):
 def run_cpu(workload, steps, warmup):
     from oracle import circatt_oracle as orc
     from oracle import cpu_baseline as cpu
+    cpu.use_all_cores()              # launchers such as torchrun export OMP_NUM_THREADS=1
     arrs = make_inputs(workload, 0)
     for _ in range(warmup):
         cpu_step(cpu, orc, arrs, workload)

@@ -33,6 +33,15 @@ int ca_cpu_threads(void) {
 #endif
 }
 
+/* Overrides OMP_NUM_THREADS (process launchers often pin it to 1). */
+void ca_cpu_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 static inline int wrapi(int x, int X) {
     if (x < 0) x += X;
     if (x >= X) x -= X;

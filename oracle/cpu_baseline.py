@@ -37,6 +37,13 @@ def threads() -> int:
     return int(lib().ca_cpu_threads())
 
 
+def use_all_cores() -> int:
+    """Run on every core this process may use, whatever OMP_NUM_THREADS says; returns the count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().ca_cpu_set_threads(n)
+    return threads()
+
+
 def _prep(x, dtype):
     x = np.asfortranarray(x, dtype=dtype)
     return x, x.ctypes.data_as(C.c_void_p)
