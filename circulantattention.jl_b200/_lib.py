@@ -12,7 +12,7 @@ import os
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("CIRCATT_B200_LIB") or os.path.join(PKG_DIR, "libcircatt_b200.so")
 
-CA_F32, CA_C64 = 0, 1
+CA_F32, CA_C64, CA_BF16 = 0, 1, 2
 CA_DOT, CA_DISTANCE = 0, 1
 CA_SOFTMAX, CA_ENTMAX15 = 0, 1
 

@@ -329,6 +329,7 @@ class _AttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, kind, ws, normalizer, want_A):
         y, nz, stats = ops.attention_fwd(kind, normalizer, q, k, v, ws, want_A)
+        ctx.set_materialize_grads(False)      # an unused A must arrive as None, not as zeros, in backward
         ctx.save_for_backward(q, k, v, y, stats, nz if want_A else None)
         ctx.cfg = (kind, ws, normalizer, want_A)
         return (y, nz) if want_A else (y, None)

@@ -59,7 +59,7 @@ int make_geo(const ca_desc* d, Geo* g, bool allow_band) {
     if (d->H < d->ws) { set_error("spatial extent %d is smaller than the window %d", d->H, d->ws); return CA_ERR_BAD_DESC; }
     if (d->ndim == 1 && d->W != 1) { set_error("1-D signals must have W == 1 (got %d)", d->W); return CA_ERR_BAD_DESC; }
     if (d->channels < 1 || d->units < 1) { set_error("channels=%d units=%d must be positive", d->channels, d->units); return CA_ERR_BAD_DESC; }
-    if (d->dtype != CA_F32 && d->dtype != CA_C64) { set_error("unknown dtype %d", d->dtype); return CA_ERR_BAD_DESC; }
+    if (d->dtype != CA_F32 && d->dtype != CA_C64 && d->dtype != CA_BF16) { set_error("unknown dtype %d", d->dtype); return CA_ERR_BAD_DESC; }
     if (d->similarity != CA_DOT && d->similarity != CA_DISTANCE) { set_error("unknown similarity %d", d->similarity); return CA_ERR_BAD_DESC; }
     if (d->normalizer != CA_SOFTMAX && d->normalizer != CA_ENTMAX15) { set_error("unknown normalizer %d", d->normalizer); return CA_ERR_BAD_DESC; }
     const int p = (d->ws - 1) / 2;
@@ -88,8 +88,17 @@ int make_geo(const ca_desc* d, Geo* g, bool allow_band) {
     g->c = d->channels;
     g->cpe = d->dtype == CA_C64 ? 2 : 1;
     g->cr = g->c * g->cpe;
+    g->bf16 = d->dtype == CA_BF16;
     if (d->units > 65535) { set_error("units=%d exceeds the grid limit 65535", d->units); return CA_ERR_TOO_LARGE; }
     return CA_OK;
+}
+
+// bfloat16 storage exists only in the fused tiled attention kernels.
+static int no_bf16(const Geo& g, const char* what) {
+    if (!g.bf16) return CA_OK;
+    set_error("%s: bfloat16 storage is implemented by the fused attention kernels only "
+              "(softmax, 16 channels per unit, a workspace given)", what);
+    return CA_ERR_UNSUPPORTED;
 }
 
 static int pick_cmax(int cr) {
@@ -218,6 +227,7 @@ int ca_similarity(const ca_desc* d, const void* x, const void* y, float* nz, voi
     int rc = make_geo(d, &g, false);
     if (rc) return rc;
     if (!x || !y || !nz) { set_error("x/y/nz is NULL"); return CA_ERR_NULL; }
+    if ((rc = no_bf16(g, "ca_similarity"))) return rc;
     if ((rc = check_nnz(g))) return rc;
     rc = tiled_similarity(g, d->scale, d->similarity == CA_DISTANCE, (const float*)x, (const float*)y, nz, workspace,
                           as_stream(stream));
@@ -232,6 +242,7 @@ int ca_similarity_bwd(const ca_desc* d, const void* x, const void* y, const floa
     int rc = make_geo(d, &g, false);
     if (rc) return rc;
     if (!x || !y || !dS) { set_error("x/y/dS is NULL"); return CA_ERR_NULL; }
+    if ((rc = no_bf16(g, "ca_similarity_bwd"))) return rc;
     const bool dist = d->similarity == CA_DISTANCE;
     cudaStream_t st = as_stream(stream);
     rc = tiled_similarity_bwd(g, d->scale, dist, (const float*)x, (const float*)y, dS, (float*)dx, (float*)dy,
@@ -271,6 +282,7 @@ int ca_apply(const ca_desc* d, const float* nz, const void* v, void* out,
     int rc = make_geo(d, &g, false);
     if (rc) return rc;
     if (!nz || !v || !out) { set_error("nz/v/out is NULL"); return CA_ERR_NULL; }
+    if ((rc = no_bf16(g, "ca_apply"))) return rc;
     if (!a_bcast && !v_bcast) {
         rc = tiled_apply(g, nz, (const float*)v, (float*)out, 1.f, transpose != 0, workspace, as_stream(stream));
         if (rc != CA_ERR_UNSUPPORTED) return rc;
@@ -288,7 +300,7 @@ static size_t score_bytes(const Geo& g) {
 // Used where no fused tiled kernel exists: 32 or 64 real channels per unit, and entmax.  The
 // scratch is A-sized, so the chain is taken only while A fits Int32 indexing and 4 GiB.
 static bool composed_path(const ca_desc* d, const Geo& g, bool backward = false) {
-    if (g.Wk != g.W || !tiled_operator_workspace(g)) return false;
+    if (g.bf16 || g.Wk != g.W || !tiled_operator_workspace(g)) return false;
     // 1-D windows are long (the scores of a row do not stay in cache between the operators): the
     // backward of narrow units is faster on the generic kernels, which recompute instead
     if (backward && g.wsw == 1 && g.cr <= 16) return false;
@@ -322,6 +334,7 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
     const int dist = d->similarity == CA_DISTANCE;
 
     const bool ent = d->normalizer == CA_ENTMAX15;
+    if (ent && (rc = no_bf16(g, "ca_attention_fwd with entmax"))) return rc;
     if (ent || (composed_path(d, g) && (nz || workspace))) {
         // scores -> row normaliser (threshold or log-sum-exp per row) -> apply; the scores live in
         // nz or in the workspace
@@ -347,6 +360,7 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
 
+    if ((rc = no_bf16(g, "ca_attention_fwd on this shape"))) return rc;
     const int cmax = pick_cmax(g.cr);
     if (!cmax) { set_error("fused attention supports at most 64 real channels per unit (got %d); use similarity + normalize + apply", g.cr); return CA_ERR_UNSUPPORTED; }
     FwdArgs a{g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v, (float*)y, nz, stats};
@@ -386,6 +400,7 @@ int ca_attention_bwd_pre(const ca_desc* d, const void* q, const void* k, const v
     int rc = make_geo(d, &g, true);
     if (rc) return rc;
     if (!dy || !D) { set_error("dy/D is NULL"); return CA_ERR_NULL; }
+    if ((rc = no_bf16(g, "ca_attention_bwd_pre"))) return rc;
     if (dA && !nz && d->normalizer == CA_SOFTMAX) { set_error("a cotangent on A needs the saved A (nz)"); return CA_ERR_NULL; }
     if (dA && g.Wk != g.W) { set_error("band mode never materialises A"); return CA_ERR_UNSUPPORTED; }
     cudaStream_t st = as_stream(stream);
@@ -422,6 +437,7 @@ int ca_attention_bwd_dq(const ca_desc* d, const void* q, const void* k, const vo
                                     (const float*)dy, stats, D, (float*)dq, workspace, st);
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
+    if ((rc = no_bf16(g, "ca_attention_bwd_dq on this shape"))) return rc;
     const int cmax = pick_cmax(g.cr);
     if (!cmax) { set_error("fused attention supports at most 64 real channels per unit (got %d)", g.cr); return CA_ERR_UNSUPPORTED; }
     BwdArgs a{g, d->scale, dist, ent, (const float*)q, (const float*)k, (const float*)v, nullptr,
@@ -447,6 +463,7 @@ int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const 
                                       (const float*)dy, stats, D, (float*)dk, (float*)dv, workspace, st);
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
+    if ((rc = no_bf16(g, "ca_attention_bwd_dkdv on this shape"))) return rc;
     const int cmax = pick_cmax(g.cr);
     if (!cmax) { set_error("fused attention supports at most 64 real channels per unit (got %d)", g.cr); return CA_ERR_UNSUPPORTED; }
     BwdArgs a{g, d->scale, dist, ent, (const float*)q, (const float*)k, (const float*)v, nullptr,
@@ -498,6 +515,7 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
                                  (float*)dk, (float*)dv, (char*)workspace + d_bytes(g), as_stream(stream));
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
+    if ((rc = no_bf16(g, "ca_attention_bwd on this shape"))) return rc;
     if ((rc = ca_attention_bwd_pre(d, q, k, v, y, dy, stats, nz, dA, D, stream))) return rc;
     if ((rc = ca_attention_bwd_dq(d, q, k, v, dy, stats, D, dA, dq, nullptr, stream))) return rc;
     return ca_attention_bwd_dkdv(d, q, k, v, dy, stats, D, dA, dk, dv, nullptr, stream);

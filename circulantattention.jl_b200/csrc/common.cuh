@@ -38,6 +38,7 @@ struct Geo {
     int c;        // channels per unit in elements
     int cpe;      // floats per element: 1 (f32) or 2 (c64)
     int cr;       // real channels per unit: c * cpe
+    int bf16;     // dense tensors are stored as bfloat16 (cpe == 1); arithmetic stays Float32
 };
 
 __host__ __device__ inline int wrap_axis(int x, int X) {

@@ -42,6 +42,7 @@
 // copy pipeline) whose partial results are merged through shared memory.
 #include "tiled.cuh"
 #include "tma.cuh"
+#include <cuda_bf16.h>
 #include <stdlib.h>
 #include <algorithm>
 #include <type_traits>
@@ -284,6 +285,19 @@ struct StagePipe {
         return;                                                                                      \
     }
 
+// One real element of a dense tensor stored as Float32 or bfloat16 (element offset `off`).
+__device__ __forceinline__ float ld_real(const float* base, int64_t off, int bf16) {
+    if (bf16) {
+        const unsigned short h = __ldg(reinterpret_cast<const unsigned short*>(base) + off);
+        return __uint_as_float((unsigned)h << 16);
+    }
+    return __ldg(base + off);
+}
+__device__ __forceinline__ void st_real(float* base, int64_t off, float v, int bf16) {
+    if (bf16) reinterpret_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(v);
+    else base[off] = v;
+}
+
 // Loads the 16-channel vectors of the NQ centre pixels of this thread, times `mul`.
 template <int CPE, int NQ, int NCR = 16>
 __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int u, int h, int w0, bool active,
@@ -297,8 +311,8 @@ __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int 
             float x = 0.f, y = 0.f;
             if (ok && (NCR >= 16 || 2 * i < NCR)) {         // units narrower than a slab are zero-extended
                 if (CPE == 1) {
-                    x = __ldg(src + goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix));
-                    y = __ldg(src + goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix));
+                    x = ld_real(src, goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix), g.bf16);
+                    y = ld_real(src, goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix), g.bf16);
                 } else {
                     const float2 t = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, ch0 + 2 * i, g.Np, pix)));
                     x = t.x;
@@ -317,8 +331,8 @@ __device__ __forceinline__ void store_centre(float* dst, const Geo& g, int u, in
     if (NCR < 16 && 2 * i >= NCR) return;
     const int pix = h + g.H * (w0 + r);
     if (CPE == 1) {
-        dst[goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix)] = x;
-        dst[goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix)] = y;
+        st_real(dst, goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix), x, g.bf16);
+        st_real(dst, goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix), y, g.bf16);
     } else {
         *reinterpret_cast<float2*>(dst + goff<2, NCR>(u, ch0 + 2 * i, g.Np, pix)) = make_float2(x, y);
     }
@@ -1276,9 +1290,10 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
                 if (!real_row || cc >= NCR) {             // padding rows; channels past a narrow unit
                     vals[sl] = make_float4(0.f, 0.f, 0.f, 0.f);
                 } else if (CPE == 1) {
-                    const float* sp = src + goff<1, NCR>(u, cc, g.Npk, pix);
-                    vals[sl] = make_float4(__ldg(sp), __ldg(sp + g.Npk), __ldg(sp + 2 * (int64_t)g.Npk),
-                                           __ldg(sp + 3 * (int64_t)g.Npk));
+                    const int64_t o = goff<1, NCR>(u, cc, g.Npk, pix);
+                    vals[sl] = make_float4(ld_real(src, o, g.bf16), ld_real(src, o + g.Npk, g.bf16),
+                                           ld_real(src, o + 2 * (int64_t)g.Npk, g.bf16),
+                                           ld_real(src, o + 3 * (int64_t)g.Npk, g.bf16));
                 } else {
                     const float2 lo = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, cc, g.Npk, pix)));
                     const float2 hi = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, cc + 2, g.Npk, pix)));
@@ -1305,8 +1320,8 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
 #pragma unroll
             for (int cc = 0; cc < 16; ++cc) {
                 const int64_t o = goff<CPE>(u, cc, g.Npk, pix);
-                dyv[cc] = __ldg(a.dy + o);
-                yv[cc] = __ldg(a.y + o);
+                dyv[cc] = ld_real(a.dy, o, g.bf16);
+                yv[cc] = ld_real(a.y, o, g.bf16);
             }
 #pragma unroll
             for (int cc = 0; cc < 16; ++cc) D = fmaf(dyv[cc], yv[cc], D);

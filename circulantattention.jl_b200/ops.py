@@ -9,7 +9,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib, jl
-from ._lib import CA_C64, CA_F32, ca_desc, check, lib, ptr
+from ._lib import CA_BF16, CA_C64, CA_F32, ca_desc, check, lib, ptr
 
 
 @dataclass(frozen=True)
@@ -20,6 +20,7 @@ class Meta:
     units: int
     ws: int
     cplx: bool
+    bf16: bool = False      # bfloat16 storage (fused attention only)
 
     @property
     def ndim(self):
@@ -44,13 +45,14 @@ class Meta:
     def desc(self, similarity=0, normalizer=0, scale=1.0, Wk=0, wk_off=0, units=None, W=None):
         return ca_desc(self.H, self.W if W is None else W, self.ndim, self.channels,
                        self.units if units is None else units, self.ws,
-                       CA_C64 if self.cplx else CA_F32, similarity, normalizer, Wk, wk_off, float(scale))
+                       CA_C64 if self.cplx else (CA_BF16 if self.bf16 else CA_F32), similarity, normalizer, Wk, wk_off,
+                       float(scale))
 
 
 def meta_of(x: torch.Tensor, ws: int) -> Meta:
     if x.ndim not in (3, 4):
         raise AssertionError(f"expected a (spatial..., channels, batch) array with 1 or 2 spatial dims, got {tuple(x.shape)}")
-    return Meta(tuple(x.shape[:-2]), x.shape[-2], x.shape[-1], int(ws), x.is_complex())
+    return Meta(tuple(x.shape[:-2]), x.shape[-2], x.shape[-1], int(ws), x.is_complex(), x.dtype == torch.bfloat16)
 
 
 def _stream():
@@ -64,9 +66,9 @@ def require_cuda(*ts):
 
 
 def _dense_ok(t, cplx=None):
-    want = (torch.float32, torch.complex64)
+    want = (torch.float32, torch.complex64, torch.bfloat16)
     if t.dtype not in want:
-        raise TypeError(f"only Float32 and ComplexF32 are supported, got {t.dtype}")
+        raise TypeError(f"only Float32, ComplexF32 and (fused attention) BFloat16 are supported, got {t.dtype}")
     return jl.colmajor(t)
 
 

@@ -48,7 +48,10 @@ typedef enum ca_status {
     CA_ERR_TOO_LARGE = -5      /* a size exceeds a documented limit */
 } ca_status;
 
-enum { CA_F32 = 0, CA_C64 = 1 };            /* element type of dense tensors */
+enum { CA_F32 = 0, CA_C64 = 1, CA_BF16 = 2 }; /* element type of dense tensors; CA_BF16 (storage only: all
+                                              * arithmetic and A's values, statistics and scratch stay Float32)
+                                              * is accepted by the fused attention entry points on the shapes
+                                              * their tiled kernels cover, and has no reference counterpart */
 enum { CA_DOT = 0, CA_DISTANCE = 1 };       /* src/similarity.jl:15,29 */
 enum { CA_SOFTMAX = 0, CA_ENTMAX15 = 1 };   /* row normaliser; entmax has no reference counterpart */
 
@@ -60,7 +63,7 @@ typedef struct ca_desc {
     int32_t channels;   /* channels per unit (C / nheads), counted in elements of `dtype` */
     int32_t units;      /* independent head*batch units */
     int32_t ws;         /* odd window length; every spatial extent must be >= ws */
-    int32_t dtype;      /* CA_F32 or CA_C64 */
+    int32_t dtype;      /* CA_F32, CA_C64 or CA_BF16 */
     int32_t similarity; /* CA_DOT or CA_DISTANCE */
     int32_t normalizer; /* CA_SOFTMAX or CA_ENTMAX15 */
     int32_t Wk;         /* band mode: columns of the key-side tensors (0 or W = circular wrap) */

@@ -125,6 +125,45 @@ def test_cotangent_on_returned_A(ca, shape, ws, nheads):
     assert rel_err(ca.jl.to_numpy(v.grad), dvo) < TOL
 
 
+@pytest.mark.parametrize("simname", ["dot", "distance"])
+@pytest.mark.parametrize("shape,ws,nheads", [((37, 29, 32, 2), 9, 2), ((64, 48, 64, 1), 15, 4), ((256, 16, 2), 9, 1)])
+def test_bfloat16_storage(ca, shape, ws, nheads, simname):
+    """BFloat16 tensors in and out, Float32 arithmetic (no reference counterpart).  The oracle runs in
+    float64 on the bfloat16-rounded inputs, so the differences are Float32 accumulation, the final rounding
+    of the outputs to bfloat16 (half an ulp = 2^-9 of each value) and, in the backward, the bfloat16-rounded
+    y that was saved by the forward: bar 1e-2 of the largest value."""
+    import torch
+    BF16_TOL = 1e-2
+    rng = np.random.default_rng(11)
+    qn, kn, vn, rn = (randn(rng, shape) for _ in range(4))
+    to_bf = lambda a: ca.jl.from_numpy(a).to(torch.bfloat16)
+    q, k, v, r = (to_bf(t) for t in (qn, kn, vn, rn))
+    back = lambda t: ca.jl.to_numpy(t.float()).astype(np.float64)
+    q64, k64, v64, r64 = (back(t) for t in (q, k, v, r))
+    q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+    n0 = ca._lib.lib.ca_probe_tiled_launch_count()
+    y, A = ca.circulant_mh_attention(sim_of(ca, simname), q, k, v, ws, nheads)
+    (y.float() * r.float()).sum().backward()
+    assert ca._lib.lib.ca_probe_tiled_launch_count() > n0
+    assert y.dtype == torch.bfloat16 and q.grad.dtype == torch.bfloat16 and A.nzVal.dtype == torch.float32
+    yo, nzo = orc.mh_attention(KIND[simname], q64, k64, v64, ws, nheads)
+    dqo, dko, dvo = orc.mh_attention_pullback(KIND[simname], q64, k64, v64, ws, nheads, r64)
+    assert rel_err(back(y), yo) < BF16_TOL
+    assert rel_err(ca.jl.to_numpy(A.nzVal), nzo) < TOL                 # A stays Float32
+    assert rel_err(back(q.grad), dqo) < BF16_TOL
+    assert rel_err(back(k.grad), dko) < BF16_TOL
+    assert rel_err(back(v.grad), dvo) < BF16_TOL
+
+
+def test_bfloat16_is_refused_outside_the_fused_kernels(ca):
+    import torch
+    x = ca.jl.randn(16, 16, 4, 1).to(torch.bfloat16)
+    with pytest.raises(ca._lib.CircAttError, match="bfloat16"):
+        ca.ops.similarity(0, x, x, 5)
+    with pytest.raises(ca._lib.CircAttError, match="bfloat16"):
+        ca.ops.attention_fwd(0, 0, x, x, x, 5, False)                 # 4 channels per unit: no tiled kernel
+
+
 def test_large_scores_running_max(ca):
     """Inputs scaled x30: scores in the hundreds; exercises the online-softmax rescale."""
     rng = np.random.default_rng(3)
