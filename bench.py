@@ -177,6 +177,8 @@ def extra_main(args):
 
     out = {"configs": {}, "operators_c2_us": {}}
     for name, (shape, ws, nh, kind, norm, cplx, want_nz) in EXTRA_CONFIGS.items():
+        if args.extra == "operators":
+            break
         dt = torch.complex64 if cplx else torch.float32
         q, k, v, dy = (ca.splitheads(jl.randn(*shape, generator=gen, dtype=dt), nh) for _ in range(4))
         C = shape[-2] * (2 if cplx else 1)
@@ -192,6 +194,9 @@ def extra_main(args):
             "fwd_tflops": px * fl_f / tf / 1e12, "bwd_tflops": px * fl_b / tb / 1e12}
         del q, k, v, dy, y, nz, stats, res
         torch.cuda.empty_cache()
+    if args.extra == "configs":
+        print(json.dumps(out))
+        return
     H, W, C, B, ws, nh = (WORKLOAD[k_] for k_ in ("H", "W", "C", "B", "ws", "nheads"))
     q, k, v = (ca.splitheads(jl.randn(H, W, C, B, generator=gen), nh) for _ in range(3))
     nz = ops.similarity(0, q, k, ws)
@@ -222,8 +227,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--extra", action="store_true",
-                    help="time the other configurations and the stand-alone operators instead of the headline step")
+    ap.add_argument("--extra", nargs="?", const="all", default=None, choices=["all", "configs", "operators"],
+                    help="time the other configurations and/or the stand-alone operators instead of the headline step")
     args = ap.parse_args()
     if args.extra:
         return extra_main(args)
