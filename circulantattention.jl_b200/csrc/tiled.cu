@@ -286,22 +286,37 @@ struct StagePipe {
     }
 
 // One real element of a dense tensor stored as Float32 or bfloat16 (element offset `off`).
-__device__ __forceinline__ float ld_real(const float* base, int64_t off, int bf16) {
-    if (bf16) {
+// BF is a compile-time flag so that a batch of loads stays a batch of independent loads; callers
+// branch once on Geo::bf16 around the whole batch.
+template <bool BF>
+__device__ __forceinline__ float ld_real(const float* base, int64_t off) {
+    if (BF) {
         const unsigned short h = __ldg(reinterpret_cast<const unsigned short*>(base) + off);
         return __uint_as_float((unsigned)h << 16);
     }
     return __ldg(base + off);
 }
-__device__ __forceinline__ void st_real(float* base, int64_t off, float v, int bf16) {
-    if (bf16) reinterpret_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(v);
+template <bool BF>
+__device__ __forceinline__ void st_real(float* base, int64_t off, float v) {
+    if (BF) reinterpret_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(v);
     else base[off] = v;
 }
 
+// Runs the statements once with `constexpr bool BF` set from Geo::bf16 (one uniform branch around
+// a whole epilogue instead of one per element).  Needs CPE and g in scope.
+#define CA_BF_DISPATCH(...)                            \
+    if (CPE == 1 && g.bf16) {                          \
+        constexpr bool BF = true;                      \
+        __VA_ARGS__                                    \
+    } else {                                           \
+        constexpr bool BF = false;                     \
+        __VA_ARGS__                                    \
+    }
+
 // Loads the 16-channel vectors of the NQ centre pixels of this thread, times `mul`.
-template <int CPE, int NQ, int NCR = 16>
-__device__ __forceinline__ void load_centre(const float* src, const Geo& g, int u, int h, int w0, bool active,
-                                            float mul, u64 (&dst)[NQ][8], int ch0 = 0) {
+template <int CPE, int NQ, int NCR, bool BF>
+__device__ __forceinline__ void load_centre_impl(const float* src, const Geo& g, int u, int h, int w0, bool active,
+                                                 float mul, u64 (&dst)[NQ][8], int ch0) {
 #pragma unroll
     for (int r = 0; r < NQ; ++r) {
         const bool ok = active && (w0 + r < g.W);
@@ -311,8 +326,8 @@ __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int 
             float x = 0.f, y = 0.f;
             if (ok && (NCR >= 16 || 2 * i < NCR)) {         // units narrower than a slab are zero-extended
                 if (CPE == 1) {
-                    x = ld_real(src, goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix), g.bf16);
-                    y = ld_real(src, goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix), g.bf16);
+                    x = ld_real<BF>(src, goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix));
+                    y = ld_real<BF>(src, goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix));
                 } else {
                     const float2 t = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, ch0 + 2 * i, g.Np, pix)));
                     x = t.x;
@@ -324,15 +339,22 @@ __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int 
     }
 }
 
-template <int CPE, int NCR = 16>
+template <int CPE, int NQ, int NCR = 16>
+__device__ __forceinline__ void load_centre(const float* src, const Geo& g, int u, int h, int w0, bool active,
+                                            float mul, u64 (&dst)[NQ][8], int ch0 = 0) {
+    if (CPE == 1 && g.bf16) load_centre_impl<CPE, NQ, NCR, true>(src, g, u, h, w0, active, mul, dst, ch0);
+    else load_centre_impl<CPE, NQ, NCR, false>(src, g, u, h, w0, active, mul, dst, ch0);
+}
+
+template <int CPE, int NCR = 16, bool BF = false>
 __device__ __forceinline__ void store_centre(float* dst, const Geo& g, int u, int h, int w0, bool active, int r,
                                              int i, float x, float y, int ch0 = 0) {
     if (!(active && (w0 + r < g.W))) return;
     if (NCR < 16 && 2 * i >= NCR) return;
     const int pix = h + g.H * (w0 + r);
     if (CPE == 1) {
-        st_real(dst, goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix), x, g.bf16);
-        st_real(dst, goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix), y, g.bf16);
+        st_real<BF>(dst, goff<1, NCR>(u, ch0 + 2 * i, g.Np, pix), x);
+        st_real<BF>(dst, goff<1, NCR>(u, ch0 + 2 * i + 1, g.Np, pix), y);
     } else {
         *reinterpret_cast<float2*>(dst + goff<2, NCR>(u, ch0 + 2 * i, g.Np, pix)) = make_float2(x, y);
     }
@@ -566,18 +588,21 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
             }
         }
     }
+    CA_BF_DISPATCH(
+        _Pragma("unroll")
+        for (int r = 0; r < NQ; ++r) {
+            const float inv = 1.f / l[r];
+            _Pragma("unroll")
+            for (int i = 0; i < 8; ++i) {
+                float x, y;
+                unpack2(acc[r][i], x, y);
+                store_centre<CPE, 16, BF>(a.o0, g, u, h, w0, active, r, i, x * inv, y * inv);
+            }
+        })
 #pragma unroll
-    for (int r = 0; r < NQ; ++r) {
-        const float inv = 1.f / l[r];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float x, y;
-            unpack2(acc[r][i], x, y);
-            store_centre<CPE>(a.o0, g, u, h, w0, active, r, i, x * inv, y * inv);
-        }
+    for (int r = 0; r < NQ; ++r)
         if (a.ostats && active && w0 + r < g.W)
             a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = (log2f(l[r]) - nm[r]) * kLn2;
-    }
 }
 
 // =====================================================================
@@ -1077,17 +1102,19 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
         }
     }
     // dq = scale * (sum ds*k - [distance] sum(ds) * q);  q registers hold q*scale*log2(e)
-#pragma unroll
-    for (int r = 0; r < NQ; ++r)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float x, y, qx, qy;
-            unpack2(dq[r][i], x, y);
-            unpack2(q[r][i], qx, qy);
-            x = a.scale * x - (DIST ? sumds[r] * qx * kLn2 : 0.f);
-            y = a.scale * y - (DIST ? sumds[r] * qy * kLn2 : 0.f);
-            store_centre<CPE>(a.o0, g, u, h, w0, active, r, i, x, y);
-        }
+    CA_BF_DISPATCH(
+        _Pragma("unroll")
+        for (int r = 0; r < NQ; ++r) {
+            _Pragma("unroll")
+            for (int i = 0; i < 8; ++i) {
+                float x, y, qx, qy;
+                unpack2(dq[r][i], x, y);
+                unpack2(q[r][i], qx, qy);
+                x = a.scale * x - (DIST ? sumds[r] * qx * kLn2 : 0.f);
+                y = a.scale * y - (DIST ? sumds[r] * qy * kLn2 : 0.f);
+                store_centre<CPE, 16, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
+            }
+        })
 }
 
 // =====================================================================
@@ -1212,19 +1239,21 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
         }
     }
     // dk = scale * (sum ds*q - [distance] sum(ds) * k);  k registers hold k*scale*log2(e)
-#pragma unroll
-    for (int r = 0; r < NQ; ++r)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float x, y, kx, ky, vx, vy;
-            unpack2(dk[r][i], x, y);
-            unpack2(k[r][i], kx, ky);
-            unpack2(dv[r][i], vx, vy);
-            x = a.scale * x - (DIST ? sumds[r] * kx * kLn2 : 0.f);
-            y = a.scale * y - (DIST ? sumds[r] * ky * kLn2 : 0.f);
-            store_centre<CPE>(a.o0, g, u, h, w0, active, r, i, x, y);
-            store_centre<CPE>(a.o1, g, u, h, w0, active, r, i, vx, vy);
-        }
+    CA_BF_DISPATCH(
+        _Pragma("unroll")
+        for (int r = 0; r < NQ; ++r) {
+            _Pragma("unroll")
+            for (int i = 0; i < 8; ++i) {
+                float x, y, kx, ky, vx, vy;
+                unpack2(dk[r][i], x, y);
+                unpack2(k[r][i], kx, ky);
+                unpack2(dv[r][i], vx, vy);
+                x = a.scale * x - (DIST ? sumds[r] * kx * kLn2 : 0.f);
+                y = a.scale * y - (DIST ? sumds[r] * ky * kLn2 : 0.f);
+                store_centre<CPE, 16, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
+                store_centre<CPE, 16, BF>(a.o1, g, u, h, w0, active, r, i, vx, vy);
+            }
+        })
 }
 
 // =====================================================================
@@ -1249,8 +1278,8 @@ struct PackArgs {
     float* Dout;            // nullable: D in the reference layout (interior rows)
 };
 
-template <int CPE, int NCRT>
-__global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
+template <int CPE, int NCRT, bool BF>
+__device__ __forceinline__ void pack_body(const PackArgs& a) {
     constexpr int NS = NCRT <= 16 ? 1 : NCRT / 16;
     constexpr int NCR = NCRT;
     const Geo& g = a.g;
@@ -1291,9 +1320,9 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
                     vals[sl] = make_float4(0.f, 0.f, 0.f, 0.f);
                 } else if (CPE == 1) {
                     const int64_t o = goff<1, NCR>(u, cc, g.Npk, pix);
-                    vals[sl] = make_float4(ld_real(src, o, g.bf16), ld_real(src, o + g.Npk, g.bf16),
-                                           ld_real(src, o + 2 * (int64_t)g.Npk, g.bf16),
-                                           ld_real(src, o + 3 * (int64_t)g.Npk, g.bf16));
+                    vals[sl] = make_float4(ld_real<BF>(src, o), ld_real<BF>(src, o + g.Npk),
+                                           ld_real<BF>(src, o + 2 * (int64_t)g.Npk),
+                                           ld_real<BF>(src, o + 3 * (int64_t)g.Npk));
                 } else {
                     const float2 lo = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, cc, g.Npk, pix)));
                     const float2 hi = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCR>(u, cc + 2, g.Npk, pix)));
@@ -1320,8 +1349,8 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
 #pragma unroll
             for (int cc = 0; cc < 16; ++cc) {
                 const int64_t o = goff<CPE>(u, cc, g.Npk, pix);
-                dyv[cc] = ld_real(a.dy, o, g.bf16);
-                yv[cc] = ld_real(a.y, o, g.bf16);
+                dyv[cc] = ld_real<BF>(a.dy, o);
+                yv[cc] = ld_real<BF>(a.y, o);
             }
 #pragma unroll
             for (int cc = 0; cc < 16; ++cc) D = fmaf(dyv[cc], yv[cc], D);
@@ -1331,6 +1360,12 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
     const int64_t plane = (int64_t)g.Wk * a.Hp;
     a.planes[(2 * (int64_t)u) * plane + (int64_t)w * a.Hp + rr] = L;
     a.planes[(2 * (int64_t)u + 1) * plane + (int64_t)w * a.Hp + rr] = D;
+}
+
+template <int CPE, int NCRT>
+__global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
+    if (CPE == 1 && a.g.bf16) pack_body<CPE, NCRT, true>(a);
+    else pack_body<CPE, NCRT, false>(a);
 }
 
 // ---------------------------------------------------------------- host side
