@@ -340,8 +340,8 @@ class _AttentionFn(torch.autograd.Function):
         kind, ws, normalizer, want_A = ctx.cfg
         if dy is None:
             dy = jl.zeros(y.shape, y.dtype, y.device)
-        dq, dk, dv = ops.attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws,
-                                       nz=nz if dnz is not None else None, dA=dnz)
+        # the saved A (when the forward materialised it) spares the operator-chain backward a recomputation
+        dq, dk, dv = ops.attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=nz, dA=dnz)
         return dq, dk, dv, None, None, None, None
 
 

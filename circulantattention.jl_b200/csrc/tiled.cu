@@ -117,6 +117,7 @@ struct TileArgs {
     int nsplit;             // 1 or 2 groups of warps sharing the stages of a tile
     int which;              // half of the packed pair a single-tensor kernel streams (0 or 1)
     int row_bytes;          // bytes of one packed pixel row: 144 per 16-channel slab
+    int nstages;            // copy stages in flight per part: 2 or 3 (kStages)
     const float* c0;        // centre tensors (reference layout)
     const float* c1;
     const float* cs0;       // centre scalars (dq kernel: stats, D)
@@ -252,7 +253,7 @@ struct StagePipe {
     unsigned char* smem_al = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);            \
     StagePipe<NSCV> pipe;                                                                            \
     pipe.full = full_bar + part * kStages;                                                           \
-    pipe.base = smem_al + (size_t)part * kStages * a.stage_bytes;                                    \
+    pipe.base = smem_al + (size_t)part * a.nstages * a.stage_bytes;                                  \
     pipe.mv = &mv; pipe.msc = &msc;                                                                  \
     pipe.ROWS = ROWS; pipe.stage_bytes = a.stage_bytes; pipe.row_bytes = a.row_bytes;                \
     pipe.u = u; pipe.h0 = h0; pipe.w0 = w0;                                                          \
@@ -263,24 +264,24 @@ struct StagePipe {
     }                                                                                                \
     __syncthreads();                                                                                 \
     if (lt == 0)                                                                                     \
-        for (int i = 0; i < kStages && s_begin + i < s_end; ++i) pipe.issue(g, s_begin + i, i);
+        for (int i = 0; i < a.nstages && s_begin + i < s_end; ++i) pipe.issue(g, s_begin + i, i);
 
 // Consumer loop over the stages of this part: bounded wait, BODY, recycle the buffer.
 #define CA_PIPE_LOOP(...)                                                                            \
     for (int s = s_begin; s < s_end; ++s) {                                                          \
         const int it = s - s_begin;                                                                  \
-        const int buf = it % kStages;                                                                \
-        if (!mbar_wait(&pipe.full[buf], (uint32_t)((it / kStages) & 1))) s_err = 1;                  \
+        const int buf = it % a.nstages;                                                              \
+        if (!mbar_wait(&pipe.full[buf], (uint32_t)((it / a.nstages) & 1))) s_err = 1;                \
         __VA_ARGS__                                                                                  \
         part_sync(part, PT);                                                                         \
         if (s_err) break;                                                                            \
-        if (lt == 0 && s + kStages < s_end) pipe.issue(g, s + kStages, buf);                         \
+        if (lt == 0 && s + a.nstages < s_end) pipe.issue(g, s + a.nstages, buf);                     \
     }                                                                                                \
     __syncthreads();                                                                                 \
     if (s_err) {                                                                                     \
         /* give copies still in flight a bounded chance to land before the CTA exits */              \
         if (lt == 0)                                                                                 \
-            for (int i = 0; i < kStages; ++i) mbar_wait(&pipe.full[i], 0, 1u << 12);                 \
+            for (int i = 0; i < a.nstages; ++i) mbar_wait(&pipe.full[i], 0, 1u << 12);               \
         if (threadIdx.x == 0) atomicAdd(&g_stage_timeouts, 1);                                       \
         return;                                                                                      \
     }
@@ -638,7 +639,7 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
     const int CH = min(g.ws, kRunChunk);
     const int CHS = CH | 1;                                    // odd row stride: conflict-free column access
     const int nslots = g.wsw == 1 ? 1 : 4;                     // folded 1-D: a stage pairs with one centre column
-    float* tile = reinterpret_cast<float*>(smem_al + (size_t)a.nsplit * kStages * a.stage_bytes) +
+    float* tile = reinterpret_cast<float*>(smem_al + (size_t)a.nsplit * a.nstages * a.stage_bytes) +
                   (size_t)warp * (nslots * RW * CHS + 4 * RW + RW * CH);     // tile, rotations, offset table
     int* rots = reinterpret_cast<int*>(tile + nslots * RW * CHS);
     // 2-D windows that fit one piece: the destination offset of every tile element is the same
@@ -682,7 +683,9 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
         const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * RB;
         for (int d0 = 0; d0 < g.ws; d0 += CH) {
             const int len = min(CH, g.ws - d0);                // window rows d0 .. d0 + len - 1
-            // FULL: all four centre columns pair with this stage (compile-time), else per-column tests
+            // FULL: the dot products of all four centre columns run interleaved (the columns that do
+            // not pair with this stage are computed too and dropped: cheaper than four serial chains);
+            // otherwise only the paired columns are computed (folded 1-D: one column per stage)
             auto sweep = [&](auto full_tag) {
                 constexpr bool FULL = decltype(full_tag)::value;
                 u64 kn[8];                                 // the next window row's vector, fetched one row ahead
@@ -721,7 +724,7 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
                     }
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
-                        if (!FULL && !((mask >> r) & 1)) continue;
+                        if (!((mask >> r) & 1)) continue;
                         float sc = hsum2(t[r]);
 #pragma unroll
                         for (int m = 1; m < NS; m <<= 1) sc += __shfl_xor_sync(0xffffffffu, sc, m);
@@ -729,7 +732,7 @@ __global__ void __launch_bounds__(128, 3) emit_a_tiled_kernel(TileArgs a, const 
                     }
                 }
             };
-            if (mask == 15) sweep(std::true_type{});
+            if (mask == 15 || g.wsw != 1) sweep(std::true_type{});
             else sweep(std::false_type{});
             __syncwarp();
             // write this piece of the runs of the stage: row j, positions posw*ws + (d + rot_j) mod ws
@@ -812,7 +815,7 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
     // 2-D windows that fit one piece: source and tile offsets of every staged element are the same
     // for all stages and centre columns up to the column base; they come from two tables
     const bool tabled = nch == 1 && !fold;
-    float* wbase = reinterpret_cast<float*>(smem_al + (size_t)kStages * a.stage_bytes) +
+    float* wbase = reinterpret_cast<float*>(smem_al + (size_t)a.nstages * a.stage_bytes) +
                    (size_t)warp * (2 * buf_floats + (tabled ? 2 * RW * CH : 0));
     const int hw0 = h0 + (lt >> 5) * RW;                       // first image row of this warp
     const float* nzu = a.cs0 + (int64_t)u * g.Np * g.K;
@@ -1476,7 +1479,7 @@ int sm_count() {
 // warps of rows, or two warps of rows times two stage groups on small grids.
 int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* env_warps, const float* pair,
             const float* planes, Launch* L, bool allow_split = true, int max_warps = 4, int ns = 1,
-            bool single = false) {
+            bool single = false, int stages = kStages) {
     const int rw = 32 / ns;                             // pixel rows per warp (ns lanes share a pixel)
     const int rf = (single ? kSingleFloats : kRowFloats) * ns, rb = rf * 4;
     int warps = (g.H + rw - 1) / rw;
@@ -1502,7 +1505,8 @@ int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* e
     a.stage_bytes = (vbytes + (planes ? 2 * sstride : 0) + 1023) & ~1023;
     L->grid = dim3((unsigned)cols, (g.H + a.TH - 1) / a.TH, g.units);
     L->threads = 32 * warps * nsplit;
-    size_t smem = (size_t)nsplit * kStages * a.stage_bytes;
+    a.nstages = stages;
+    size_t smem = (size_t)nsplit * stages * a.stage_bytes;
     const size_t xch = (size_t)xch_floats * 32 * warps * sizeof(float);
     if (nsplit == 2 && xch > smem) smem = xch;
     L->smem = smem + 1024;
@@ -1724,12 +1728,24 @@ int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const floa
     const Padded P = padded_of(g);
     const int ns = slabs_of(g);
     Launch L{};
-    int rc = prepare(g, P, 4, 0, "CIRCATT_FWD_WARPS", static_cast<const float*>(workspace), nullptr, &L, true, 4, ns,
-                     single);
-    if (rc) return rc;
+    // three copy stages, or two when that lets one more CTA reside on an SM
+    const int ch = std::min(g.ws, kRunChunk), nslots = g.wsw == 1 ? 1 : 4;
+    int rc = CA_OK;
+    auto setup = [&](int stages) {
+        L = Launch{};
+        rc = prepare(g, P, 4, 0, "CIRCATT_FWD_WARPS", static_cast<const float*>(workspace), nullptr, &L, true, 4, ns,
+                     single, stages);
+        // per warp: staging tile, run rotations, offset table
+        if (!rc) L.smem += (size_t)L.threads / 32 * (32 / ns) * (nslots * (ch + 1) + 4 + ch) * sizeof(float);
+        return rc;
+    };
+    if (setup(kStages)) return rc;
     {
-        const int ch = std::min(g.ws, kRunChunk), nslots = g.wsw == 1 ? 1 : 4;
-        L.smem += (size_t)L.threads / 32 * (32 / ns) * (nslots * (ch + 1) + 4 + ch) * sizeof(float);
+        const size_t per_sm = 227 * 1024, with3 = L.smem + 1024;          // + the driver's per-CTA reservation
+        const size_t with2 = with3 - (size_t)L.a.nsplit * L.a.stage_bytes;
+        const int want = env_int("CIRCATT_EMIT_STAGES", 0);
+        if (want == 2 || (want == 0 && per_sm / with2 > per_sm / with3))
+            if (setup(2)) return rc;
     }
     if (L.smem > 200 * 1024) return CA_ERR_UNSUPPORTED;
 #define CA_EMIT(NSV)                                                                  \
