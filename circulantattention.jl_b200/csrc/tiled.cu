@@ -1744,7 +1744,8 @@ int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const floa
         const size_t per_sm = 227 * 1024, with3 = L.smem + 1024;          // + the driver's per-CTA reservation
         const size_t with2 = with3 - (size_t)L.a.nsplit * L.a.stage_bytes;
         const int want = env_int("CIRCATT_EMIT_STAGES", 0);
-        if (want == 2 || (want == 0 && per_sm / with2 > per_sm / with3))
+        // the kernel's registers allow three CTAs per SM at most
+        if (want == 2 || (want == 0 && std::min<size_t>(3, per_sm / with2) > std::min<size_t>(3, per_sm / with3)))
             if (setup(2)) return rc;
     }
     if (L.smem > 200 * 1024) return CA_ERR_UNSUPPORTED;
