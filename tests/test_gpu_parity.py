@@ -64,6 +64,9 @@ CASES = [
     ((37, 29, 64, 2), 9, 2, False),      # 32 channels per head: chain of tiled operators with scratch scores
     ((24, 20, 32, 2), 5, 1, True),       # 32 complex = 64 real channels (BASELINE config 4's channel count)
     ((33, 16, 64, 1), 7, 1, False),      # 64 real channels
+    ((256, 16, 2), 9, 1, False),         # 1-D, 16 channels: fused kernels on the folded signal (two columns)
+    ((384, 32, 1), 33, 2, False),        # 1-D folded into three columns, window wider than a staging piece
+    ((512, 16, 1), 127, 1, False),       # 1-D, the widest window the folded kernels take
 ]
 
 
@@ -162,6 +165,19 @@ def test_bfloat16_is_refused_outside_the_fused_kernels(ca):
         ca.ops.similarity(0, x, x, 5)
     with pytest.raises(ca._lib.CircAttError, match="bfloat16"):
         ca.ops.attention_fwd(0, 0, x, x, x, 5, False)                 # 4 channels per unit: no tiled kernel
+
+
+def test_folded_1d_runs_on_the_fused_tiled_kernels(ca):
+    """A 1-D signal with 16 channels per head takes the TMA-tiled forward and backward (5 launches: pack, fwd,
+    pack, dq, dk/dv), not the generic kernels."""
+    rng = np.random.default_rng(12)
+    q, k, v = (ca.jl.from_numpy(randn(rng, (256, 32, 2))).requires_grad_(True) for _ in range(3))
+    lib = ca._lib.lib
+    n0 = lib.ca_probe_tiled_launch_count()
+    y, _ = ca.circulant_mh_attention(ca.DotSimilarity(), q, k, v, 9, 2, return_A=False)
+    assert lib.ca_probe_tiled_launch_count() == n0 + 1
+    y.sum().backward()
+    assert lib.ca_probe_tiled_launch_count() == n0 + 3
 
 
 def test_large_scores_running_max(ca):
