@@ -11,7 +11,7 @@ from .api import (  # noqa: F401
     AbstractSimilarity, BatchedTranspose, Circulant, CuSparseArrayCSR, DistanceSimilarity, DotSimilarity,
     ENTMAX15, SOFTMAX, Otimes, batched_adjoint, batched_mul, batched_transpose, cat, circulant,
     circulant_adjacency, circulant_adjacency_, circulant_attention, circulant_attention_,
-    circulant_mh_adjacency, circulant_mh_attention, circulant_mh_transposed_attention,
+    circulant_mh_adjacency, circulant_mh_attention, circulant_mh_transposed_attention, mix_otimes,
     circulant_similarity, circulant_similarity_, circulant_transposed_attention,
     circulant_transposed_attention_, dot, entmax15, kernel_length, otimes, scale, softmax, softmax_,
     spatial_dims, spatial_size, splitheads, sum,

@@ -517,6 +517,40 @@ def circulant_mh_transposed_attention(A: Circulant, x):
     return jl.reshape(circulant_transposed_attention(A, xr), tuple(x.shape))
 
 
+def mix_otimes(terms, x):
+    """y = (sum_i c_i * A_i) ⨷ x without ever materialising the sum.
+
+    The pattern of the reference's gradient test and of GroupCDL-style models (test/grad.jl:17-21,
+    README.md:126-136): `C = α*A + (1-α)*B; y = C ⨷ x`.  There `C` is a third A-sized array that is
+    written and read again; by linearity y = sum_i c_i * (A_i ⨷ x), so each A_i is read exactly once and
+    only pixel-sized arrays are combined.  `terms` is a sequence of (c_i, A_i): c_i a number or an array
+    of size (1, 1, h', b') as accepted by `scale` (src/array.jl:179-186); the A_i are Circulants of equal
+    window and spatial size, 4-dimensional (multi-head, ⨷) or 3-dimensional (⊗).  Differentiable in the
+    c_i, the A_i and x through the rrules of ⊗ / ⨷ (src/rrules.jl:58-72)."""
+    terms = list(terms)
+    if not terms:
+        raise TypeError("mix_otimes needs at least one (c, A) term")
+    out = None
+    for c, A in terms:
+        if not isinstance(A, Circulant):
+            raise TypeError("terms are (c, A) with A a Circulant")
+        terms[0][1]._same(A)
+        mh = A.ndim == 4
+        xr = splitheads(x, A.size(3)) if mh else x
+        y = otimes(A, xr)                                   # (spatial..., c, heads*B): head fastest in the last dim
+        if isinstance(c, torch.Tensor) and c.ndim > 0:
+            if c.ndim != A.ndim or c.shape[0] != 1 or c.shape[1] != 1:
+                raise TypeError(f"coefficient of size {tuple(c.shape)} does not scale the batch dims of A {tuple(A.shape)}")
+            cb = c[0, 0].expand(*A.shape[2:])               # (heads, B) or (B,)
+            cu = (cb.t() if cb.ndim == 2 else cb).reshape(-1)    # one value per unit, head fastest
+            y = y * cu.reshape((1,) * (y.ndim - 1) + (-1,))
+        else:
+            y = y * float(c)
+        y = jl.reshape(y, tuple(x.shape)) if mh else y
+        out = y if out is None else out + y
+    return out
+
+
 class BatchedTranspose:
     """NNlib.batched_transpose(A::Circulant) marker (src/batchedmul.jl:13-19)."""
 

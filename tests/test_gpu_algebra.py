@@ -117,3 +117,32 @@ def test_grad_smoke_network(ca):
         (z * z).sum().backward()
         for t in (xx, k, q, v, alpha):
             assert t.grad is not None and torch.isfinite(t.grad).all() and t.grad.abs().sum() > 0
+
+
+def test_mix_otimes_equals_materialised_sum(ca):
+    """test/grad.jl:17-21 pattern: (α*A + (1-α)*B) ⨷ x and its gradients, computed without the sum."""
+    import torch
+    rng = np.random.default_rng(31)
+    shape, ws, nheads = (24, 20, 32, 2), 5, 2
+    q1, k1, q2, k2, xn, rn = (randn(rng, shape) for _ in range(6))
+    def build():
+        ts = [ca.jl.from_numpy(t).requires_grad_(True) for t in (q1, k1, q2, k2, xn)]
+        A = ca.circulant_mh_adjacency(ca.DotSimilarity(), ts[0], ts[1], ws, nheads)
+        B = ca.circulant_mh_adjacency(ca.DistanceSimilarity(), ts[2], ts[3], ws, nheads)
+        alpha = ca.jl.from_numpy(rng_alpha.copy()).requires_grad_(True)
+        return ts, A, B, alpha
+    rng_alpha = np.asfortranarray(np.random.default_rng(32).uniform(0.2, 0.8, (1, 1, nheads, 2)).astype(np.float32))
+    r = ca.jl.from_numpy(rn)
+    # materialised: C = α*A + (1-α)*B ; y = C ⨷ x
+    ts, A, B, alpha = build()
+    y_ref = ca.Otimes(ca.scale(alpha, A) + ca.scale(1 - alpha, B), ts[4])
+    (y_ref * r).sum().backward()
+    g_ref = [ca.jl.to_numpy(t.grad) for t in ts] + [ca.jl.to_numpy(alpha.grad)]
+    # fused by linearity
+    ts, A, B, alpha = build()
+    y = ca.mix_otimes([(alpha, A), (1 - alpha, B)], ts[4])
+    (y * r).sum().backward()
+    g = [ca.jl.to_numpy(t.grad) for t in ts] + [ca.jl.to_numpy(alpha.grad)]
+    assert rel_err(ca.jl.to_numpy(y), ca.jl.to_numpy(y_ref).astype(np.float64)) < TOL
+    for a, b in zip(g, g_ref):
+        assert rel_err(a, b.astype(np.float64)) < TOL
