@@ -67,6 +67,8 @@ CASES = [
     ((256, 16, 2), 9, 1, False),         # 1-D, 16 channels: fused kernels on the folded signal (two columns)
     ((384, 32, 1), 33, 2, False),        # 1-D folded into three columns, window wider than a staging piece
     ((512, 16, 1), 127, 1, False),       # 1-D, the widest window the folded kernels take
+    ((16, 16, 2), 15, 1, False),         # shortest 1-D signal, every row wraps
+    ((16, 15, 16, 1), 15, 1, False),     # shortest 2-D image, extent == window along w
 ]
 
 
@@ -324,6 +326,9 @@ TILED_OPERATOR_CASES = [
     ((4096,), 127, 8, 2, False),        # BASELINE config 3's window and channel count
     ((96,), 5, 16, 1, True),            # 1-D that folds into a single column (wraps onto itself)
     ((64,), 7, 64, 2, False),           # 1-D, four lanes per pixel
+    ((16,), 15, 16, 2, False),          # shortest 1-D signal, window = extent - 1: every row wraps
+    ((48,), 31, 16, 1, False),          # one 48-row column
+    ((16, 15), 15, 16, 1, False),       # shortest 2-D image, extent == window along w
 ]
 
 
