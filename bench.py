@@ -219,6 +219,60 @@ def extra_main(args):
     print(json.dumps(out))
 
 
+
+# --------------------------------------------------------------------------- band split (--extra band)
+def band_main(args):
+    """Not the headline: one image of BASELINE config 5 (1024 x 1024 x 128, ws 21, 8 heads, flash mode) split
+    into bands of columns over the ranks, forward + backward including the halo exchanges (NCCL point to
+    point, the circular wrap between the last and the first rank).  One JSON line from rank 0."""
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ca = load_package()
+    jl, par = ca.jl, ca.parallel
+    H, W, C, B, ws, nh = 1024, 1024, 128, 1, 21, 8
+    plan = par.BandPlan(W, world, ws)
+    start, width = plan.band(rank)
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    q, k, v, dy = (ca.splitheads(jl.randn(H, width, C, B, generator=gen, device=dev), nh) for _ in range(4))
+
+    def step():
+        y, stats, k_ext, v_ext = par.band_attention_fwd(0, q, k, v, ws)
+        return par.band_attention_bwd(0, q, k, v, y, dy, stats, k_ext, v_ext, ws)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    steps, warmup = max(1, min(args.steps, 10)), max(3, min(args.warmup, 5))
+    for _ in range(warmup):
+        step()
+    barrier()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        a.record(); step(); b.record()          # 67 MB per tensor and rank at 8 ranks: larger than what stays in L2
+    barrier()
+    total = torch.tensor([sum(a.elapsed_time(b) for a, b in evs) * 1e-3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        t = float(total.item()) / steps
+        print(json.dumps({
+            "workload": "one 1024x1024x128 image, ws=21, 8 heads, Dot, flash mode, band split over columns with "
+                        "halo exchange, fwd+bwd", "n_gpus": world, "scaling": "strong", "steps": steps,
+            "ms_per_step": t * 1e3, "px_per_s": H * W * B / t, "band_columns": width, "halo_columns": plan.p}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------------- B200 arm
 def main():
     ap = argparse.ArgumentParser()
@@ -227,9 +281,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--extra", nargs="?", const="all", default=None, choices=["all", "configs", "operators"],
+    ap.add_argument("--extra", nargs="?", const="all", default=None, choices=["all", "configs", "operators", "band"],
                     help="time the other configurations and/or the stand-alone operators instead of the headline step")
     args = ap.parse_args()
+    if args.extra == "band":
+        return band_main(args)
     if args.extra:
         return extra_main(args)
     if args.impl == "reference":
