@@ -305,7 +305,7 @@ static bool composed_path(const ca_desc* d, const Geo& g, bool backward = false)
     // backward of narrow units is faster on the generic kernels, which recompute instead
     if (backward && g.wsw == 1 && g.cr <= 16) return false;
     if ((int64_t)g.Np * g.K > INT32_MAX || score_bytes(g) > ((size_t)4 << 30)) return false;
-    return d->normalizer == CA_ENTMAX15 || g.cr != 16;
+    return d->normalizer == CA_ENTMAX15 || g.cr > 16;
 }
 
 size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {

@@ -303,15 +303,24 @@ __device__ __forceinline__ void st_real(float* base, int64_t off, float v) {
     else base[off] = v;
 }
 
-// Runs the statements once with `constexpr bool BF` set from Geo::bf16 (one uniform branch around
-// a whole epilogue instead of one per element).  Needs CPE and g in scope.
-#define CA_BF_DISPATCH(...)                            \
+// Runs the statements once with `constexpr bool BF` (bfloat16 storage) and `constexpr int NCRV`
+// (8 or 16 real channels per unit) set from the geometry: one uniform branch around a whole
+// epilogue instead of one per element.  Needs CPE and g in scope.
+#define CA_OUT_DISPATCH_NCR(NCRVAL, ...)               \
     if (CPE == 1 && g.bf16) {                          \
         constexpr bool BF = true;                      \
+        constexpr int NCRV = NCRVAL;                   \
         __VA_ARGS__                                    \
     } else {                                           \
         constexpr bool BF = false;                     \
+        constexpr int NCRV = NCRVAL;                   \
         __VA_ARGS__                                    \
+    }
+#define CA_BF_DISPATCH(...)                            \
+    if (g.cr == 8) {                                   \
+        CA_OUT_DISPATCH_NCR(8, __VA_ARGS__)            \
+    } else {                                           \
+        CA_OUT_DISPATCH_NCR(16, __VA_ARGS__)           \
     }
 
 // Loads the 16-channel vectors of the NQ centre pixels of this thread, times `mul`.
@@ -343,6 +352,12 @@ __device__ __forceinline__ void load_centre_impl(const float* src, const Geo& g,
 template <int CPE, int NQ, int NCR = 16>
 __device__ __forceinline__ void load_centre(const float* src, const Geo& g, int u, int h, int w0, bool active,
                                             float mul, u64 (&dst)[NQ][8], int ch0 = 0) {
+    if (NCR == 16 && g.cr == 8) {
+        // a kernel compiled for one 16-channel slab running on 8-channel units: zero-extended
+        if (CPE == 1 && g.bf16) load_centre_impl<CPE, NQ, 8, true>(src, g, u, h, w0, active, mul, dst, ch0);
+        else load_centre_impl<CPE, NQ, 8, false>(src, g, u, h, w0, active, mul, dst, ch0);
+        return;
+    }
     if (CPE == 1 && g.bf16) load_centre_impl<CPE, NQ, NCR, true>(src, g, u, h, w0, active, mul, dst, ch0);
     else load_centre_impl<CPE, NQ, NCR, false>(src, g, u, h, w0, active, mul, dst, ch0);
 }
@@ -597,7 +612,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
             for (int i = 0; i < 8; ++i) {
                 float x, y;
                 unpack2(acc[r][i], x, y);
-                store_centre<CPE, 16, BF>(a.o0, g, u, h, w0, active, r, i, x * inv, y * inv);
+                store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x * inv, y * inv);
             }
         })
 #pragma unroll
@@ -1115,7 +1130,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
                 unpack2(q[r][i], qx, qy);
                 x = a.scale * x - (DIST ? sumds[r] * qx * kLn2 : 0.f);
                 y = a.scale * y - (DIST ? sumds[r] * qy * kLn2 : 0.f);
-                store_centre<CPE, 16, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
+                store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
             }
         })
 }
@@ -1253,8 +1268,8 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
                 unpack2(dv[r][i], vx, vy);
                 x = a.scale * x - (DIST ? sumds[r] * kx * kLn2 : 0.f);
                 y = a.scale * y - (DIST ? sumds[r] * ky * kLn2 : 0.f);
-                store_centre<CPE, 16, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
-                store_centre<CPE, 16, BF>(a.o1, g, u, h, w0, active, r, i, vx, vy);
+                store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
+                store_centre<CPE, NCRV, BF>(a.o1, g, u, h, w0, active, r, i, vx, vy);
             }
         })
 }
@@ -1348,15 +1363,16 @@ __device__ __forceinline__ void pack_body(const PackArgs& a) {
         if (a.Din) {
             D = __ldg(a.Din + so);
         } else {
-            float dyv[16], yv[16];
+            constexpr int NC = NCR < 16 ? NCR : 16;             // planes exist for one-slab units only
+            float dyv[NC], yv[NC];
 #pragma unroll
-            for (int cc = 0; cc < 16; ++cc) {
-                const int64_t o = goff<CPE>(u, cc, g.Npk, pix);
+            for (int cc = 0; cc < NC; ++cc) {
+                const int64_t o = goff<CPE, NCR>(u, cc, g.Npk, pix);
                 dyv[cc] = ld_real<BF>(a.dy, o);
                 yv[cc] = ld_real<BF>(a.y, o);
             }
 #pragma unroll
-            for (int cc = 0; cc < 16; ++cc) D = fmaf(dyv[cc], yv[cc], D);
+            for (int cc = 0; cc < NC; ++cc) D = fmaf(dyv[cc], yv[cc], D);
             if (a.Dout && rr >= a.pp && rr < a.pp + g.H) a.Dout[so] = D;
         }
     }
@@ -1392,7 +1408,9 @@ Padded padded_of(const Geo& g) {
 }
 
 bool tiled_shape_ok(const Geo& g) {
-    return g.cr == 16 && (g.wsw == g.ws || g.wsw == 1) && g.ws >= 3 && g.H >= 16 && g.ws <= (g.wsw == 1 ? 127 : 63);
+    // 16 real channels per unit, or 8 zero-extended to 16 (half of the FMAs are then spent on zeros)
+    return (g.cr == 16 || g.cr == 8) && (g.wsw == g.ws || g.wsw == 1) && g.ws >= 3 && g.H >= 16 &&
+           g.ws <= (g.wsw == 1 ? 127 : 63);
 }
 
 // The stand-alone operator kernels also take 8 (zero-extended), 32 or 64 real channels per unit
@@ -1439,7 +1457,7 @@ int pick_dc(int ws) {
 int launch_pack(const PackArgs& a, cudaStream_t st) {
     dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * ((a.single ? 1 : 2) * a.npairs + (a.planes ? 1 : 0)));
     const int cr = a.g.cr;
-    if (a.planes && cr != 16) { set_error("scalar planes are packed for 16-channel units only"); return CA_ERR_UNSUPPORTED; }
+    if (a.planes && cr > 16) { set_error("scalar planes are packed for one-slab units only"); return CA_ERR_UNSUPPORTED; }
 #define CA_PACK(CPEV)                                                        \
     do {                                                                     \
         if (cr == 8) pack_kernel<CPEV, 8><<<grid, 128, 0, st>>>(a);          \

@@ -69,6 +69,9 @@ CASES = [
     ((512, 16, 1), 127, 1, False),       # 1-D, the widest window the folded kernels take
     ((16, 16, 2), 15, 1, False),         # shortest 1-D signal, every row wraps
     ((16, 15, 16, 1), 15, 1, False),     # shortest 2-D image, extent == window along w
+    ((37, 29, 16, 2), 9, 2, False),      # 8 channels per head: fused kernels on zero-extended units
+    ((40, 21, 8, 2), 7, 2, True),        # 4 complex = 8 real channels per head
+    ((256, 16, 2), 9, 2, False),         # 1-D, 8 channels per head
 ]
 
 
@@ -131,7 +134,8 @@ def test_cotangent_on_returned_A(ca, shape, ws, nheads):
 
 
 @pytest.mark.parametrize("simname", ["dot", "distance"])
-@pytest.mark.parametrize("shape,ws,nheads", [((37, 29, 32, 2), 9, 2), ((64, 48, 64, 1), 15, 4), ((256, 16, 2), 9, 1)])
+@pytest.mark.parametrize("shape,ws,nheads", [((37, 29, 32, 2), 9, 2), ((64, 48, 64, 1), 15, 4), ((256, 16, 2), 9, 1),
+                                             ((40, 24, 16, 2), 7, 2)])
 def test_bfloat16_storage(ca, shape, ws, nheads, simname):
     """BFloat16 tensors in and out, Float32 arithmetic (no reference counterpart).  The oracle runs in
     float64 on the bfloat16-rounded inputs, so the differences are Float32 accumulation, the final rounding
@@ -169,14 +173,15 @@ def test_bfloat16_is_refused_outside_the_fused_kernels(ca):
         ca.ops.attention_fwd(0, 0, x, x, x, 5, False)                 # 4 channels per unit: no tiled kernel
 
 
-def test_folded_1d_runs_on_the_fused_tiled_kernels(ca):
-    """A 1-D signal with 16 channels per head takes the TMA-tiled forward and backward (5 launches: pack, fwd,
+@pytest.mark.parametrize("shape,nheads", [((256, 32, 2), 2), ((256, 32, 2), 4), ((40, 24, 32, 1), 4)])
+def test_folded_1d_and_narrow_units_run_on_the_fused_tiled_kernels(ca, shape, nheads):
+    """1-D signals and units of 16 or 8 channels per head take the TMA-tiled forward and backward (pack, fwd,
     pack, dq, dk/dv), not the generic kernels."""
     rng = np.random.default_rng(12)
-    q, k, v = (ca.jl.from_numpy(randn(rng, (256, 32, 2))).requires_grad_(True) for _ in range(3))
+    q, k, v = (ca.jl.from_numpy(randn(rng, shape)).requires_grad_(True) for _ in range(3))
     lib = ca._lib.lib
     n0 = lib.ca_probe_tiled_launch_count()
-    y, _ = ca.circulant_mh_attention(ca.DotSimilarity(), q, k, v, 9, 2, return_A=False)
+    y, _ = ca.circulant_mh_attention(ca.DotSimilarity(), q, k, v, 9, nheads, return_A=False)
     assert lib.ca_probe_tiled_launch_count() == n0 + 1
     y.sum().backward()
     assert lib.ca_probe_tiled_launch_count() == n0 + 3
