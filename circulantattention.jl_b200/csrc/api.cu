@@ -1,4 +1,5 @@
 // C ABI of the circulant-attention library: argument checks and dispatch.
+#include <cstdlib>
 #include "common.cuh"
 #include "rowops.cuh"
 #include "window_generic.cuh"
@@ -375,8 +376,10 @@ static size_t d_bytes(const Geo& g) { return (((size_t)g.Npk * g.units * sizeof(
 size_t ca_attention_bwd_workspace(const ca_desc* d) {
     Geo g;
     if (make_geo(d, &g, false)) return 0;
-    if (composed_path(d, g, true)) return d_bytes(g) + 2 * score_bytes(g) + tiled_operator_workspace(g);
-    return d_bytes(g) + (d->normalizer == CA_SOFTMAX ? tiled_bwd_workspace(g) : 0);
+    // D, then the larger of the two scratch layouts the shape can take (fused tiled kernels; operator chain)
+    const size_t fused = tiled_bwd_workspace(g);
+    const size_t chain = composed_path(d, g, true) ? 2 * score_bytes(g) + tiled_operator_workspace(g) : 0;
+    return d_bytes(g) + (fused > chain ? fused : chain);
 }
 
 size_t ca_attention_bwd_stage_workspace(const ca_desc* d) {
@@ -483,6 +486,15 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
     if (rc) return rc;
     if (!workspace) { set_error("workspace of ca_attention_bwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
     float* D = (float*)workspace;
+    if (d->normalizer == CA_ENTMAX15 && !dA && (g.wsw != 1 || getenv("CIRCATT_ENTMAX_FUSED_1D"))) {
+        // fused kernels with the entmax weights recomputed from tau (no A-sized traffic).  2-D only:
+        // on folded 1-D signals the three sweeps are shared-memory bound and the generic kernels win.
+        if (!q || !k || !v || !dy || !stats || !dq || !dk || !dv) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
+        rc = tiled_attention_bwd_entmax(g, d->scale, d->similarity == CA_DISTANCE, (const float*)q, (const float*)k,
+                                        (const float*)v, (const float*)dy, stats, D, (float*)dq, (float*)dk,
+                                        (float*)dv, (char*)workspace + d_bytes(g), as_stream(stream));
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+    }
     if (composed_path(d, g, true)) {
         // the pullback chain of src/rrules.jl:42-72 on the tiled operators:
         //   P (saved, or recomputed from q, k) ; dv = P^T dy ; dP = Re(dy . conj(v)) on the window (+ dA) ;

@@ -1008,10 +1008,13 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
 // Backward, query-owned: dq.  The s chain starts at -L (log2 domain) and the
 // dP chain at -D, so P = 2^chain and dS = P * chain'.
 // =====================================================================
-template <bool DIST, int MASK, int NQ>
+// MODE 0: softmax, P = 2^chain.  MODE 1: 1.5-entmax, g = max(chain, 0) with the chain = s/2 - tau, dS = g*(dP - D).
+// MODE 2: the entmax pre-pass: only num += g*dP and den += g (in aux and sumds), D = num/den.
+template <bool DIST, int MASK, int NQ, int MODE>
 __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[NQ][8],
                                          const u64 (&dy)[NQ][8], u64 (&dq)[NQ][8], const u64 (&nL2)[NQ],
-                                         const u64 (&nD2)[NQ], const float (&bq)[NQ], float (&sumds)[NQ]) {
+                                         const u64 (&nD2)[NQ], const float (&bq)[NQ], float (&sumds)[NQ],
+                                         float (&aux)[NQ]) {
 #pragma unroll 1
     for (int di = 0; di < ws; ++di) {
         const uint32_t a0 = rowbase + di * kRowBytes;
@@ -1044,23 +1047,29 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
                 if (DIST) t = add2(t, pack2(bq[r] + bk, 0.f));
 #pragma unroll
                 for (int i = 0; i < 8; ++i) t = fma2(q[r][i], k2[i], t);
-                const float ds = fast_exp2(hsum2(t)) * dp[r];
-                if (DIST) sumds[r] += ds;
-                const u64 d2 = pack2(ds, ds);
+                if (MODE == 2) {
+                    const float gg = fmaxf(hsum2(t), 0.f);
+                    aux[r] = fmaf(gg, dp[r], aux[r]);
+                    sumds[r] += gg;
+                } else {
+                    const float ds = (MODE == 0 ? fast_exp2(hsum2(t)) : fmaxf(hsum2(t), 0.f)) * dp[r];
+                    if (DIST) sumds[r] += ds;
+                    const u64 d2 = pack2(ds, ds);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) dq[r][i] = fma2(d2, k2[i], dq[r][i]);
+                    for (int i = 0; i < 8; ++i) dq[r][i] = fma2(d2, k2[i], dq[r][i]);
+                }
             }
     }
 }
 
-template <bool DIST, int CPE, int NQ>
+template <bool DIST, int CPE, int NQ, int MODE>
 __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                           const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
     const int NSTAGES = g.wsw + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
-    const float sl2 = a.scale * kLog2e;
+    const float sl2 = MODE ? 0.5f * a.scale : a.scale * kLog2e;     // entmax: the chain is s/2 - tau
     CA_PIPE_PROLOGUE(false)
     const int lr = lt, h = h0 + lr;
     const bool active = h < g.H;
@@ -1069,14 +1078,15 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
     load_centre<CPE, NQ>(a.c0, g, u, h, w0, active, sl2, q);
     load_centre<CPE, NQ>(a.c1, g, u, h, w0, active, 1.f, dy);
     u64 nL2[NQ], nD2[NQ];
-    float bq[NQ], sumds[NQ];
+    float bq[NQ], sumds[NQ], aux[NQ];
 #pragma unroll
     for (int r = 0; r < NQ; ++r) {
         const bool ok = active && (w0 + r < g.W);
         const int64_t o = (int64_t)u * g.Np + h + g.H * (w0 + r);
-        nL2[r] = pack2(ok ? -__ldg(a.cs0 + o) * kLog2e : 0.f, 0.f);
-        nD2[r] = pack2(ok ? -__ldg(a.cs1 + o) : 0.f, 0.f);
+        nL2[r] = pack2(ok ? -__ldg(a.cs0 + o) * (MODE ? 1.f : kLog2e) : 0.f, 0.f);
+        nD2[r] = pack2((ok && MODE != 2) ? -__ldg(a.cs1 + o) : 0.f, 0.f);
         sumds[r] = 0.f;
+        aux[r] = 0.f;
         bq[r] = 0.f;
         if (DIST) {
             u64 n = zero2();
@@ -1090,10 +1100,18 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
 
     CA_PIPE_LOOP({
         const int mask = stage_mask<NQ>(s, radius_w(g));
-        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dq_stage<DIST, MK, NQ>(smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes, g.ws, mask,
-                                                     sl2, q, dy, dq, nL2, nD2, bq, sumds)));
+        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dq_stage<DIST, MK, NQ, MODE>(smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes, g.ws, mask,
+                                                     sl2, q, dy, dq, nL2, nD2, bq, sumds, aux)));
     })
 
+    if (MODE == 2) {
+        // pre-pass of the entmax pullback: D = sum g*dP / sum g per query row (launched without a stage split)
+#pragma unroll
+        for (int r = 0; r < NQ; ++r)
+            if (active && w0 + r < g.W)
+                a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = sumds[r] > 0.f ? aux[r] / sumds[r] : 0.f;
+        return;
+    }
     if (a.nsplit == 2) {
         float* xch = reinterpret_cast<float*>(smem_al);
         if (part == 1) {
@@ -1119,7 +1137,8 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
                 dq[r][i] = add2(dq[r][i], pack2(xch[(r * 17 + 2 * i) * PT + lt], xch[(r * 17 + 2 * i + 1) * PT + lt]));
         }
     }
-    // dq = scale * (sum ds*k - [distance] sum(ds) * q);  q registers hold q*scale*log2(e)
+    // dq = scale * (sum ds*k - [distance] sum(ds) * q);  q registers hold q*scale*log2(e) (entmax: q*scale/2)
+    const float qfac = MODE ? 2.f : kLn2;
     CA_BF_DISPATCH(
         _Pragma("unroll")
         for (int r = 0; r < NQ; ++r) {
@@ -1128,8 +1147,8 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
                 float x, y, qx, qy;
                 unpack2(dq[r][i], x, y);
                 unpack2(q[r][i], qx, qy);
-                x = a.scale * x - (DIST ? sumds[r] * qx * kLn2 : 0.f);
-                y = a.scale * y - (DIST ? sumds[r] * qy * kLn2 : 0.f);
+                x = a.scale * x - (DIST ? sumds[r] * qx * qfac : 0.f);
+                y = a.scale * y - (DIST ? sumds[r] * qy * qfac : 0.f);
                 store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
             }
         })
@@ -1139,7 +1158,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
 // Backward, key-owned: dk and dv of three key pixels per thread.  The stage
 // rows carry (q | dy) of the query pixels plus their L and D.
 // =====================================================================
-template <bool DIST, int MASK, int NQ>
+template <bool DIST, int MASK, int NQ, bool ENT>
 __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const float* Db, int row0, int ws, int rm,
                                            float sl2, const u64 (&k)[NQ][8], const u64 (&v)[NQ][8], u64 (&dk)[NQ][8],
                                            u64 (&dv)[NQ][8], const float (&bk)[NQ], float (&sumds)[NQ]) {
@@ -1174,8 +1193,15 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
                 u64 t = pack2(DIST ? nLj + bk[r] + bqj : nLj, 0.f);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) t = fma2(k[r][i], q2[i], t);
-                const float P = fast_exp2(hsum2(t));
-                const float ds = P * dp[r];
+                float P, ds;
+                if (!ENT) {
+                    P = fast_exp2(hsum2(t));
+                    ds = P * dp[r];
+                } else {                                     // g = max(s/2 - tau, 0): P = g^2, dS = g*(dP - D)
+                    const float gg = fmaxf(hsum2(t), 0.f);
+                    P = gg * gg;
+                    ds = gg * dp[r];
+                }
                 if (DIST) sumds[r] += ds;
                 const u64 d2 = pack2(ds, ds), p2 = pack2(P, P);
 #pragma unroll
@@ -1187,14 +1213,14 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
     }
 }
 
-template <bool DIST, int CPE, int NQ>
+template <bool DIST, int CPE, int NQ, bool ENT>
 __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                             const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
     const int NSTAGES = g.wsw + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
-    const float sl2 = a.scale * kLog2e;
+    const float sl2 = ENT ? 0.5f * a.scale : a.scale * kLog2e;      // entmax: the chain is s/2 - tau
     CA_PIPE_PROLOGUE(true)
     const int lr = lt, h = h0 + lr;
     const bool active = h < g.H;
@@ -1222,7 +1248,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
 
     CA_PIPE_LOOP({
         const int mask = stage_mask<NQ>(s, radius_w(g));
-        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dkdv_stage<DIST, MK, NQ>(smem_u32(pipe.vec(buf)), pipe.sc0(buf), pipe.sc1(buf),
+        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dkdv_stage<DIST, MK, NQ, ENT>(smem_u32(pipe.vec(buf)), pipe.sc0(buf), pipe.sc1(buf),
                                                       lr + a.roff, g.ws, mask, sl2, k, v, dk, dv, bk, sumds)));
     })
 
@@ -1266,8 +1292,8 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
                 unpack2(dk[r][i], x, y);
                 unpack2(k[r][i], kx, ky);
                 unpack2(dv[r][i], vx, vy);
-                x = a.scale * x - (DIST ? sumds[r] * kx * kLn2 : 0.f);
-                y = a.scale * y - (DIST ? sumds[r] * ky * kLn2 : 0.f);
+                x = a.scale * x - (DIST ? sumds[r] * kx * (ENT ? 2.f : kLn2) : 0.f);
+                y = a.scale * y - (DIST ? sumds[r] * ky * (ENT ? 2.f : kLn2) : 0.f);
                 store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
                 store_centre<CPE, NCRV, BF>(a.o1, g, u, h, w0, active, r, i, vx, vy);
             }
@@ -1290,6 +1316,7 @@ struct PackArgs {
     float* dst[2];
     float* planes;          // nullable
     const float* stats;     // with planes
+    float stat_mul;         // plane 0 = stats * stat_mul: log2(e) for the softmax log-sum-exp, 1 for the entmax tau
     const float* Din;       // with planes: D given ...
     const float* y;         // ... or computed as dy . y
     const float* dy;
@@ -1359,7 +1386,7 @@ __device__ __forceinline__ void pack_body(const PackArgs& a) {
     float L = 0.f, D = 0.f;
     if (real_row) {
         const int64_t so = (int64_t)u * g.Npk + pix;
-        L = __ldg(a.stats + so) * kLog2e;
+        L = __ldg(a.stats + so) * a.stat_mul;
         if (a.Din) {
             D = __ldg(a.Din + so);
         } else {
@@ -1572,14 +1599,14 @@ int set_smem(K kernel, size_t bytes) {
         }                                                                             \
     } while (0)
 
-#define CA_DIST_CPE_NQ(KERNEL_T, dist, cpe, NQV, L, st)                               \
+#define CA_DIST_CPE_NQ(KERNEL_T, dist, cpe, NQV, XV, L, st)                           \
     do {                                                                              \
         if ((cpe) == 1) {                                                             \
-            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 1, NQV>), L, st);               \
-            else CA_LAUNCH_TILED((KERNEL_T<false, 1, NQV>), L, st);                   \
+            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 1, NQV, XV>), L, st);           \
+            else CA_LAUNCH_TILED((KERNEL_T<false, 1, NQV, XV>), L, st);               \
         } else {                                                                      \
-            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 2, NQV>), L, st);               \
-            else CA_LAUNCH_TILED((KERNEL_T<false, 2, NQV>), L, st);                   \
+            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 2, NQV, XV>), L, st);           \
+            else CA_LAUNCH_TILED((KERNEL_T<false, 2, NQV, XV>), L, st);               \
         }                                                                             \
     } while (0)
 
@@ -1592,29 +1619,34 @@ int pick_nq(const Geo& g, int wide, int narrow, const char* env) {
     return env_int(env, nq);
 }
 
+// mode 0: softmax; 1: entmax; 2: entmax pre-pass (writes D, needs no D and no dq).  The entmax
+// variants exist for four centre pixels per thread and run without a stage split.
 int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q, const float* dy, const float* stats,
-           const float* D, const float* kv, float* dq, cudaStream_t st) {
+           const float* D, const float* kv, float* dq, cudaStream_t st, int mode = 0, float* Dout = nullptr) {
     Launch L{};
-    const int nq = pick_nq(g, 4, 2, "CIRCATT_DQ_NQ");
-    int rc = prepare(g, P, nq, 17 * nq, "CIRCATT_DQ_WARPS", kv, nullptr, &L);
+    const int nq = mode ? 4 : pick_nq(g, 4, 2, "CIRCATT_DQ_NQ");
+    int rc = prepare(g, P, nq, 17 * nq, "CIRCATT_DQ_WARPS", kv, nullptr, &L, mode == 0);
     if (rc) return rc;
-    L.a.scale = scale; L.a.c0 = q; L.a.c1 = dy; L.a.cs0 = stats; L.a.cs1 = D; L.a.o0 = dq;
-    if (nq == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 2, L, st);
-    else CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, L, st);
+    L.a.scale = scale; L.a.c0 = q; L.a.c1 = dy; L.a.cs0 = stats; L.a.cs1 = D; L.a.o0 = dq; L.a.ostats = Dout;
+    if (mode == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 2, L, st);
+    else if (mode == 1) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 1, L, st);
+    else if (nq == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 2, 0, L, st);
+    else CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 0, L, st);
     CA_CHECK_LAUNCH("tiled dq kernel");
     return CA_OK;
 }
 
 int run_dkdv(const Geo& g, const Padded& P, float scale, int dist, const float* k, const float* v, const float* qdy,
-             const float* planes, float* dk, float* dv, cudaStream_t st) {
+             const float* planes, float* dk, float* dv, cudaStream_t st, bool entmax = false) {
     Launch L{};
-    const int nq = pick_nq(g, 3, 3, "CIRCATT_DKDV_NQ");
+    const int nq = entmax ? 3 : pick_nq(g, 3, 3, "CIRCATT_DKDV_NQ");
     int rc = prepare(g, P, nq, 33 * nq, "CIRCATT_DKDV_WARPS", qdy, planes, &L);
     if (rc) return rc;
     L.a.scale = scale; L.a.c0 = k; L.a.c1 = v; L.a.o0 = dk; L.a.o1 = dv;
-    if (nq == 1) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 1, L, st);
-    else if (nq == 2) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 2, L, st);
-    else CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, L, st);
+    if (entmax) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, true, L, st);
+    else if (nq == 1) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 1, false, L, st);
+    else if (nq == 2) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 2, false, L, st);
+    else CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, false, L, st);
     CA_CHECK_LAUNCH("tiled dk/dv kernel");
     return CA_OK;
 }
@@ -1817,7 +1849,7 @@ int tiled_attention_bwd_dkdv(const Geo& gin, float scale, int dist, const float*
     PackArgs pa{};
     pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1;
     pa.src[0] = q; pa.src[1] = dy; pa.dst[0] = qdy;
-    pa.planes = planes; pa.stats = stats; pa.Din = D;
+    pa.planes = planes; pa.stats = stats; pa.stat_mul = kLog2e; pa.Din = D;
     int rc = launch_pack(pa, st);
     if (rc) return rc;
     return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st);
@@ -1865,7 +1897,7 @@ int tiled_attention_bwd(const Geo& gin, float scale, int dist, const float* q, c
     pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 2;
     pa.src[0] = k; pa.src[1] = v; pa.src[2] = q; pa.src[3] = dy;
     pa.dst[0] = kv; pa.dst[1] = qdy;
-    pa.planes = planes; pa.stats = stats; pa.y = y; pa.dy = dy; pa.Dout = D;
+    pa.planes = planes; pa.stats = stats; pa.stat_mul = kLog2e; pa.y = y; pa.dy = dy; pa.Dout = D;
     int rc = launch_pack(pa, st);
     if (rc) return rc;
     const bool small = (long)g.Np * g.units < 2048L * sm_count();      // fewer than ~4 CTAs per SM per sweep
@@ -1884,6 +1916,35 @@ int tiled_attention_bwd(const Geo& gin, float scale, int dist, const float* q, c
     }
     if ((rc = run_dq(g, P, scale, dist, q, dy, stats, D, kv, dq, st))) return rc;
     return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st);
+}
+
+// Entmax-1.5 backward on the fused kernels.  Unlike the softmax, D = sum g*dP / sum g is not dy.y, so
+// a pre-pass over the packed (k|v) computes it first: pack (k|v) -> pre-pass -> pack (q|dy) + planes
+// (tau, D) -> dq and dk/dv.  `stats` holds tau.
+int tiled_attention_bwd_entmax(const Geo& gin, float scale, int dist, const float* q, const float* k, const float* v,
+                               const float* dy, const float* stats, float* D, float* dq, float* dk, float* dv,
+                               void* workspace, cudaStream_t st) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
+    if (!tiled_shape_ok(g) || g.Wk != g.W || g.bf16) return CA_ERR_UNSUPPORTED;
+    if (!workspace) { set_error("workspace is NULL"); return CA_ERR_NULL; }
+    const Padded P = padded_of(g);
+    float* kv = static_cast<float*>(workspace);
+    float* qdy = kv + P.pair_floats;
+    float* planes = qdy + P.pair_floats;
+    PackArgs pa{};
+    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1;
+    pa.src[0] = k; pa.src[1] = v; pa.dst[0] = kv;
+    int rc = launch_pack(pa, st);
+    if (rc) return rc;
+    if ((rc = run_dq(g, P, scale, dist, q, dy, stats, nullptr, kv, nullptr, st, 2, D))) return rc;
+    PackArgs pb{};
+    pb.g = g; pb.pp = P.pp; pb.Hp = P.Hp; pb.npairs = 1;
+    pb.src[0] = q; pb.src[1] = dy; pb.dst[0] = qdy;
+    pb.planes = planes; pb.stats = stats; pb.stat_mul = 1.f; pb.Din = D;
+    if ((rc = launch_pack(pb, st))) return rc;
+    if ((rc = run_dq(g, P, scale, dist, q, dy, stats, D, kv, dq, st, 1))) return rc;
+    return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st, true);
 }
 
 // ---------------------------------------------------------------- stand-alone operators

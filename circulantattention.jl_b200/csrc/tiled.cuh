@@ -23,6 +23,10 @@ int tiled_attention_bwd_dq(const Geo& g, float scale, int dist, const float* q, 
 int tiled_attention_bwd_dkdv(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                              const float* dy, const float* stats, const float* D, float* dk, float* dv,
                              void* workspace, cudaStream_t st);
+// The 1.5-entmax backward (stats = tau); workspace of tiled_bwd_workspace bytes.
+int tiled_attention_bwd_entmax(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
+                               const float* dy, const float* stats, float* D, float* dq, float* dk, float* dv,
+                               void* workspace, cudaStream_t st);
 // Copies the count of stage-copy timeouts to the host (synchronises the device).
 int tiled_stage_timeouts(int* count);
 

@@ -218,7 +218,9 @@ def test_deterministic_gradients(ca):
 # ------------------------------------------------------------------ entmax (no reference counterpart)
 @pytest.mark.parametrize("want_A", [True, False])
 @pytest.mark.parametrize("shape,ws,nheads,simname", [((64, 16, 2), 15, 2, "distance"), ((12, 11, 8, 1), 5, 2, "dot"),
-                                                     ((40, 24, 32, 1), 7, 2, "distance")])
+                                                     ((40, 24, 32, 1), 7, 2, "distance"), ((40, 24, 32, 1), 7, 2, "dot"),
+                                                     ((2048, 32, 2), 127, 4, "distance"),      # config 3's window and head size
+                                                     ((37, 29, 16, 1), 9, 1, "dot")])
 def test_entmax_attention(ca, shape, ws, nheads, simname, want_A):
     rng = np.random.default_rng(5)
     qn, kn, vn, rn = (randn(rng, shape, scale=1.5) for _ in range(4))
