@@ -332,7 +332,7 @@ def main():
     ptr_, check_ = ca.ops.ptr, ca._lib.check
     fwd_args = (d_, ptr_(q), ptr_(k), ptr_(v), ptr_(y_), None, ptr_(stats_), ptr_(wsf_))
     bwd_args = (d_, ptr_(q), ptr_(k), ptr_(v), ptr_(y_), ptr_(r), ptr_(stats_), None, None,
-                ptr_(grads_[0]), ptr_(grads_[1]), ptr_(grads_[2]), ptr_(wsb_))
+                ptr_(grads_[0]), ptr_(grads_[1]), ptr_(grads_[2]), ptr_(wsb_), ptr_(wsf_))
 
     def step():
         st_ = torch.cuda.current_stream().cuda_stream

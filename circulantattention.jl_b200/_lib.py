@@ -58,11 +58,12 @@ PROTOTYPES = {
     "ca_static_scratch_bytes": (C.c_size_t, []),
     "ca_attention_fwd_static": (C.c_int, [_D, _p, _p, _p, _p, _p, _p, _p]),
     "ca_attention_bwd_workspace": (C.c_size_t, [_D]),
-    "ca_attention_bwd": (C.c_int, [_D] + [_p] * 13),
+    "ca_attention_bwd": (C.c_int, [_D] + [_p] * 14),
     "ca_attention_bwd_pre": (C.c_int, [_D] + [_p] * 10),
     "ca_attention_bwd_stage_workspace": (C.c_size_t, [_D]),
     "ca_attention_bwd_dq": (C.c_int, [_D] + [_p] * 10),
     "ca_attention_bwd_dkdv": (C.c_int, [_D] + [_p] * 11),
+    "ca_status_word": (C.c_int, [_p]),
     "ca_stage_timeouts": (C.c_int, [C.POINTER(C.c_int32)]),
     "ca_axpby": (C.c_int, [_i64, _f32, _p, _f32, _p, _p, _p]),
     "ca_scale_batch": (C.c_int, [_i64, _i32, _i32, _p, _i32, _i32, _p, _i32, _i32, _p, _p]),
@@ -73,6 +74,7 @@ PROTOTYPES = {
     "ca_probe_launch_count": (C.c_int64, []),
     "ca_probe_tiled_launch_count": (C.c_int64, []),
     "ca_probe_ffma": (C.c_int, [_i32, _i32, _p, _p]),
+    "ca_probe_stage_timeout": (C.c_int, [_i32, _p, _p]),
 }
 
 for _name, (_res, _args) in PROTOTYPES.items():

@@ -328,9 +328,12 @@ class _AttentionFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, kind, ws, normalizer, want_A):
-        y, nz, stats = ops.attention_fwd(kind, normalizer, q, k, v, ws, want_A)
+        # the forward's workspace (the packed copy of k and v) is kept for the pullback, like the
+        # intermediates the reference's pullback closures capture (src/rrules.jl:44-55)
+        y, nz, stats, fws = ops.attention_fwd(kind, normalizer, q, k, v, ws, want_A, keep_workspace=True)
         ctx.set_materialize_grads(False)      # an unused A must arrive as None, not as zeros, in backward
         ctx.save_for_backward(q, k, v, y, stats, nz if want_A else None)
+        ctx.fws = fws if normalizer == 0 else None
         ctx.cfg = (kind, ws, normalizer, want_A)
         return (y, nz) if want_A else (y, None)
 
@@ -341,7 +344,9 @@ class _AttentionFn(torch.autograd.Function):
         if dy is None:
             dy = jl.zeros(y.shape, y.dtype, y.device)
         # the saved A (when the forward materialised it) spares the operator-chain backward a recomputation
-        dq, dk, dv = ops.attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=nz, dA=dnz)
+        dq, dk, dv = ops.attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=nz, dA=dnz,
+                                       fwd_workspace=ctx.fws)
+        ctx.fws = None
         return dq, dk, dv, None, None, None, None
 
 

@@ -1,5 +1,4 @@
 // C ABI of the circulant-attention library: argument checks and dispatch.
-#include <cstdlib>
 #include "common.cuh"
 #include "rowops.cuh"
 #include "window_generic.cuh"
@@ -11,6 +10,8 @@
 namespace ca {
 
 static thread_local char g_err[512] = "";
+static thread_local int* g_status_word = nullptr;
+int* status_word() { return g_status_word; }
 static std::atomic<int64_t> g_launches{0};
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
@@ -164,6 +165,15 @@ static int launch_row_normalize(int64_t rows, int K, int entmax, const float* s,
     return CA_OK;
 }
 
+static int launch_row_normalize_bwd(int64_t rows, int K, int entmax, const float* p, const float* dp, float* ds,
+                                    cudaStream_t st) {
+    const int64_t blocks = (rows * 32 + 255) / 256;
+    if (blocks > INT32_MAX) { set_error("too many rows"); return CA_ERR_TOO_LARGE; }
+    row_normalize_bwd_kernel<<<(unsigned)blocks, 256, 0, st>>>(rows, K, entmax, p, dp, ds);
+    CA_CHECK_LAUNCH("row normalize pullback kernel");
+    return CA_OK;
+}
+
 static int check_nnz(const Geo& g) {
     // the reference stores nnz as Int32 (src/circulant.jl:64,86)
     const int64_t nnz = (int64_t)g.Np * g.K;
@@ -198,6 +208,16 @@ int ca_probe_ffma(int32_t blocks, int32_t iters, float* sink, void* stream) {
 }
 
 const char* ca_last_error(void) { return g_err; }
+
+int ca_status_word(int32_t* device_word) {
+    g_status_word = device_word;
+    return CA_OK;
+}
+
+int ca_probe_stage_timeout(int32_t max_tries, int32_t* out, void* stream) {
+    if (max_tries < 1 || max_tries > (1 << 20)) { set_error("max_tries must be in 1..2^20"); return CA_ERR_BAD_DESC; }
+    return tiled_probe_stage_timeout((uint32_t)max_tries, out, as_stream(stream));
+}
 
 int ca_structure(int32_t H, int32_t W, int32_t ndim, int32_t ws, int64_t nbatch,
                  int32_t* rowptr, int32_t* colval, void* stream) {
@@ -270,11 +290,8 @@ int ca_row_normalize_bwd(const ca_desc* d, const float* p, const float* dp, floa
     int rc = make_geo(d, &g, false);
     if (rc) return rc;
     if (!p || !dp || !ds) { set_error("p/dp/ds is NULL"); return CA_ERR_NULL; }
-    const int64_t rows = (int64_t)g.Np * g.units;
-    row_normalize_bwd_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, as_stream(stream)>>>(
-        rows, g.K, d->normalizer == CA_ENTMAX15, p, dp, ds);
-    CA_CHECK_LAUNCH("row normalize pullback kernel");
-    return CA_OK;
+    return launch_row_normalize_bwd((int64_t)g.Np * g.units, g.K, d->normalizer == CA_ENTMAX15, p, dp, ds,
+                                    as_stream(stream));
 }
 
 int ca_apply(const ca_desc* d, const float* nz, const void* v, void* out,
@@ -480,13 +497,13 @@ int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const 
 int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void* v,
                      const void* y, const void* dy, const float* stats,
                      const float* nz, const float* dA,
-                     void* dq, void* dk, void* dv, void* workspace, void* stream) {
+                     void* dq, void* dk, void* dv, void* workspace, const void* fwd_workspace, void* stream) {
     Geo g;
     int rc = make_geo(d, &g, false);
     if (rc) return rc;
     if (!workspace) { set_error("workspace of ca_attention_bwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
     float* D = (float*)workspace;
-    if (d->normalizer == CA_ENTMAX15 && !dA && (g.wsw != 1 || getenv("CIRCATT_ENTMAX_FUSED_1D"))) {
+    if (d->normalizer == CA_ENTMAX15 && !dA && g.wsw != 1) {
         // fused kernels with the entmax weights recomputed from tau (no A-sized traffic).  2-D only:
         // on folded 1-D signals the three sweeps are shared-memory bound and the generic kernels win.
         if (!q || !k || !v || !dy || !stats || !dq || !dk || !dv) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
@@ -506,25 +523,32 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
         float* dpbuf = (float*)((char*)pbuf + score_bytes(g));
         void* opws = (char*)dpbuf + score_bytes(g);
         const int64_t rows = (int64_t)g.Np * g.units, nnz = rows * g.K;
-        const float* P = nz;
-        if (!P) {
-            if ((rc = tiled_similarity(g, d->scale, dist, (const float*)q, (const float*)k, pbuf, opws, st))) return rc;
-            if ((rc = launch_row_normalize(rows, g.K, ent, pbuf, pbuf, nullptr, st))) return rc;
-            P = pbuf;
-        }
-        if ((rc = tiled_apply(g, P, (const float*)dy, (float*)dv, 1.f, 1, opws, st))) return rc;
-        if ((rc = tiled_similarity(g, 1.f, 0, (const float*)dy, (const float*)v, dpbuf, opws, st))) return rc;
-        if (dA && (rc = ca_axpby(nnz, 1.f, dpbuf, 1.f, dA, dpbuf, stream))) return rc;
-        row_normalize_bwd_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(rows, g.K, ent, P, dpbuf, dpbuf);
-        CA_CHECK_LAUNCH("row normalize pullback kernel");
-        return tiled_similarity_bwd(g, d->scale, dist, (const float*)q, (const float*)k, dpbuf, (float*)dq,
-                                    (float*)dk, opws, st);
+        auto chain = [&]() -> int {
+            int r;
+            const float* P = nz;
+            if (!P) {
+                if ((r = tiled_similarity(g, d->scale, dist, (const float*)q, (const float*)k, pbuf, opws, st))) return r;
+                if ((r = launch_row_normalize(rows, g.K, ent, pbuf, pbuf, nullptr, st))) return r;
+                P = pbuf;
+            }
+            if ((r = tiled_apply(g, P, (const float*)dy, (float*)dv, 1.f, 1, opws, st))) return r;
+            if ((r = tiled_similarity(g, 1.f, 0, (const float*)dy, (const float*)v, dpbuf, opws, st))) return r;
+            if (dA && (r = ca_axpby(nnz, 1.f, dpbuf, 1.f, dA, dpbuf, stream))) return r;
+            if ((r = launch_row_normalize_bwd(rows, g.K, ent, P, dpbuf, dpbuf, st))) return r;
+            return tiled_similarity_bwd(g, d->scale, dist, (const float*)q, (const float*)k, dpbuf, (float*)dq,
+                                        (float*)dk, opws, st);
+        };
+        rc = chain();
+        // a step of the chain that does not fit this window (shared memory of the transposed apply
+        // at wide units and large windows) leaves the whole pullback to the generic kernels below,
+        // which overwrite dq, dk and dv
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
     if (d->normalizer == CA_SOFTMAX && !dA) {
         if (!q || !k || !v || !y || !dy || !stats || !dq || !dk || !dv) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
         rc = tiled_attention_bwd(g, d->scale, d->similarity == CA_DISTANCE, (const float*)q, (const float*)k,
                                  (const float*)v, (const float*)y, (const float*)dy, stats, D, (float*)dq,
-                                 (float*)dk, (float*)dv, (char*)workspace + d_bytes(g), as_stream(stream));
+                                 (float*)dk, (float*)dv, (char*)workspace + d_bytes(g), fwd_workspace, as_stream(stream));
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
     if ((rc = no_bf16(g, "ca_attention_bwd on this shape"))) return rc;
@@ -591,6 +615,7 @@ int ca_sum_rows(const ca_desc* d, const float* nz, float* out, void* stream) {
     if (rc) return rc;
     if (!nz || !out) { set_error("nz/out is NULL"); return CA_ERR_NULL; }
     const int64_t rows = (int64_t)g.Np * g.units;
+    if ((rows * 32 + 255) / 256 > INT32_MAX) { set_error("too many rows"); return CA_ERR_TOO_LARGE; }
     sum_rows_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, as_stream(stream)>>>(rows, g.K, nz, out);
     CA_CHECK_LAUNCH("row sum kernel");
     return CA_OK;

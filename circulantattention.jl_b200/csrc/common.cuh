@@ -13,6 +13,9 @@ namespace ca {
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 
+// Device word registered by the calling host thread with ca_status_word (NULL: none).
+int* status_word();
+
 void count_launch();
 void count_tiled_launch();     // launches of the TMA-tiled kernels only (tests use it to see which path ran)
 

@@ -28,11 +28,8 @@
 // conflict free without any address swizzle and every chunk of every row of a
 // window column is the thread's row base plus a compile-time constant.
 //
-// Arithmetic: FP32 on the FMA pipe.  Channel pairs are carried as two-element
-// values; whether a pair operation is one packed fma.rn.f32x2 or two scalar FMAs
-// is a build switch (CA_PACKED_FMA) decided by measurement (scalar is the
-// default: the register file cannot feed packed FMAs with two fresh 64-bit
-// operands at full rate).  Softmax in the log2 domain with ex2.approx.  The running maximum (forward) or the saved row
+// Arithmetic: FP32 on the FMA pipe, channel pairs as two scalar FMAs.  Softmax in
+// the log2 domain with ex2.approx.  The running maximum (forward) or the saved row
 // statistic (backward) is folded into the initial value of the dot-product
 // chain, and the forward only touches the maximum when the sign bits of a chunk
 // of relative scores say that one of them is positive.
@@ -47,51 +44,16 @@
 #include <algorithm>
 #include <type_traits>
 #include <mutex>
+#include <atomic>
 
 namespace ca {
 namespace {
 
-// Two-channel arithmetic.  CA_PACKED_FMA = 1 issues packed fma.rn.f32x2 on 64-bit register
-// pairs; CA_PACKED_FMA = 0 (default) issues two scalar FMAs.  The choice is measured, not
-// assumed: a packed FMA needs its multiplicands re-used between consecutive instructions to
-// run at full rate, and the dot-product / outer-product patterns below have two fresh 64-bit
-// operands per instruction, which the register file delivers at one FFMA2 per ~3.5 cycles,
-// against ~1.33 cycles per scalar FFMA (csrc/probe/ffma_operands.cu).
-#ifndef CA_PACKED_FMA
-#define CA_PACKED_FMA 0
-#endif
-
-#if CA_PACKED_FMA
-typedef unsigned long long u64;
-__device__ __forceinline__ u64 pack2(float a, float b) {
-    u64 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpack2(u64 v, float& a, float& b) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
-    u64 d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
-    u64 d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ u64 add2(u64 a, u64 b) {
-    u64 d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ u64 zero2() { return 0ull; }
-__device__ __forceinline__ void lds128(uint32_t addr, u64& lo, u64& hi) {
-    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(addr));
-}
-#else
-struct u64 { float x, y; };                       // a channel pair in two ordinary registers
+// Two-channel arithmetic: a channel pair lives in two ordinary registers and a pair operation is
+// two scalar FMAs.  (Packed fma.rn.f32x2 was measured slower here: a dot product or an outer
+// product has two fresh 64-bit operands per instruction, which the register file does not deliver
+// at the packed rate.)
+struct u64 { float x, y; };
 __device__ __forceinline__ u64 pack2(float a, float b) { return u64{a, b}; }
 __device__ __forceinline__ void unpack2(u64 v, float& a, float& b) { a = v.x; b = v.y; }
 __device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) { return u64{fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)}; }
@@ -101,7 +63,6 @@ __device__ __forceinline__ u64 zero2() { return u64{0.f, 0.f}; }
 __device__ __forceinline__ void lds128(uint32_t addr, u64& lo, u64& hi) {
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(lo.x), "=f"(lo.y), "=f"(hi.x), "=f"(hi.y) : "r"(addr));
 }
-#endif
 __device__ __forceinline__ float hsum2(u64 v) {
     float a, b;
     unpack2(v, a, b);
@@ -125,13 +86,12 @@ struct TileArgs {
     float* o0;              // outputs
     float* o1;
     float* ostats;
+    int* status;            // nullable device word of the caller: bit 0 is set when a stage wait ran out
+    uint32_t wait_tries;    // polls before a stage wait gives up
 };
 
 constexpr int kStages = 3;
-
-#ifndef CA_FWD_MIN_BLOCKS
-#define CA_FWD_MIN_BLOCKS 2
-#endif
+constexpr uint32_t kWaitTries = 1u << 20;
 
 // Number of CTAs that gave up waiting for a stage copy (stays 0 in a healthy run).
 __device__ int g_stage_timeouts = 0;
@@ -271,19 +231,25 @@ struct StagePipe {
     for (int s = s_begin; s < s_end; ++s) {                                                          \
         const int it = s - s_begin;                                                                  \
         const int buf = it % a.nstages;                                                              \
-        if (!mbar_wait(&pipe.full[buf], (uint32_t)((it / a.nstages) & 1))) s_err = 1;                \
+        if (!mbar_wait(&pipe.full[buf], (uint32_t)((it / a.nstages) & 1), a.wait_tries)) s_err = 1;  \
         __VA_ARGS__                                                                                  \
         part_sync(part, PT);                                                                         \
         if (s_err) break;                                                                            \
         if (lt == 0 && s + a.nstages < s_end) pipe.issue(g, s + a.nstages, buf);                     \
     }                                                                                                \
     __syncthreads();                                                                                 \
+    /* A wait that ran out: the CTA stops computing, reports (device counter, caller's status word)  \
+       and poisons what it still stores with NaN, so that the failure cannot pass for a result. */   \
+    float ca_poison = 0.f;                                                                           \
     if (s_err) {                                                                                     \
         /* give copies still in flight a bounded chance to land before the CTA exits */              \
         if (lt == 0)                                                                                 \
             for (int i = 0; i < a.nstages; ++i) mbar_wait(&pipe.full[i], 0, 1u << 12);               \
-        if (threadIdx.x == 0) atomicAdd(&g_stage_timeouts, 1);                                       \
-        return;                                                                                      \
+        if (threadIdx.x == 0) {                                                                      \
+            atomicAdd(&g_stage_timeouts, 1);                                                         \
+            if (a.status) atomicOr(a.status, 1);                                                     \
+        }                                                                                            \
+        ca_poison = __int_as_float(0x7fc00000);                                                      \
     }
 
 // One real element of a dense tensor stored as Float32 or bfloat16 (element offset `off`).
@@ -524,7 +490,7 @@ __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float s
     else { constexpr int MK = 0; CALL; }
 
 template <int DC, bool DIST, int CPE, bool EXACT, int NQ>
-__global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
+__global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) fwd_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                            const __grid_constant__ CUtensorMap msc) {
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
@@ -607,7 +573,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
     CA_BF_DISPATCH(
         _Pragma("unroll")
         for (int r = 0; r < NQ; ++r) {
-            const float inv = 1.f / l[r];
+            const float inv = 1.f / l[r] + ca_poison;
             _Pragma("unroll")
             for (int i = 0; i < 8; ++i) {
                 float x, y;
@@ -618,7 +584,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : CA_FWD_MIN_BLOCKS)) fwd_ti
 #pragma unroll
     for (int r = 0; r < NQ; ++r)
         if (a.ostats && active && w0 + r < g.W)
-            a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = (log2f(l[r]) - nm[r]) * kLn2;
+            a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = (log2f(l[r]) - nm[r]) * kLn2 + ca_poison;
 }
 
 // =====================================================================
@@ -1000,7 +966,7 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
         for (int i = 0; i < 8; ++i) {
             float x, y;
             unpack2(acc[r][i], x, y);
-            store_centre<CPE, NCRT>(a.o0, g, u, h, w0, active, r, i, a.scale * x, a.scale * y, 16 * slab);
+            store_centre<CPE, NCRT>(a.o0, g, u, h, w0, active, r, i, a.scale * x + ca_poison, a.scale * y + ca_poison, 16 * slab);
         }
 }
 
@@ -1109,7 +1075,7 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
 #pragma unroll
         for (int r = 0; r < NQ; ++r)
             if (active && w0 + r < g.W)
-                a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = sumds[r] > 0.f ? aux[r] / sumds[r] : 0.f;
+                a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = (sumds[r] > 0.f ? aux[r] / sumds[r] : 0.f) + ca_poison;
         return;
     }
     if (a.nsplit == 2) {
@@ -1147,8 +1113,8 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
                 float x, y, qx, qy;
                 unpack2(dq[r][i], x, y);
                 unpack2(q[r][i], qx, qy);
-                x = a.scale * x - (DIST ? sumds[r] * qx * qfac : 0.f);
-                y = a.scale * y - (DIST ? sumds[r] * qy * qfac : 0.f);
+                x = a.scale * x - (DIST ? sumds[r] * qx * qfac : 0.f) + ca_poison;
+                y = a.scale * y - (DIST ? sumds[r] * qy * qfac : 0.f) + ca_poison;
                 store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
             }
         })
@@ -1292,10 +1258,10 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
                 unpack2(dk[r][i], x, y);
                 unpack2(k[r][i], kx, ky);
                 unpack2(dv[r][i], vx, vy);
-                x = a.scale * x - (DIST ? sumds[r] * kx * (ENT ? 2.f : kLn2) : 0.f);
-                y = a.scale * y - (DIST ? sumds[r] * ky * (ENT ? 2.f : kLn2) : 0.f);
+                x = a.scale * x - (DIST ? sumds[r] * kx * (ENT ? 2.f : kLn2) : 0.f) + ca_poison;
+                y = a.scale * y - (DIST ? sumds[r] * ky * (ENT ? 2.f : kLn2) : 0.f) + ca_poison;
                 store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
-                store_centre<CPE, NCRV, BF>(a.o1, g, u, h, w0, active, r, i, vx, vy);
+                store_centre<CPE, NCRV, BF>(a.o1, g, u, h, w0, active, r, i, vx + ca_poison, vy + ca_poison);
             }
         })
 }
@@ -1467,10 +1433,16 @@ bool fold_geo(const Geo& in, Geo* out) {
     return false;
 }
 
-int env_int(const char* name, int dflt) {
+// Launch-shape overrides for tuning sessions.  Compiled out of the shipped library (the build
+// never defines CA_TUNING): no launch reads the environment.
+#ifdef CA_TUNING
+int tune_int(const char* name, int dflt) {
     const char* v = getenv(name);
     return v && *v ? atoi(v) : dflt;
 }
+#else
+inline int tune_int(const char*, int dflt) { return dflt; }
+#endif
 
 int pick_dc(int ws) {
     int best = 5, waste = 1 << 30;
@@ -1484,6 +1456,8 @@ int pick_dc(int ws) {
 int launch_pack(const PackArgs& a, cudaStream_t st) {
     dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * ((a.single ? 1 : 2) * a.npairs + (a.planes ? 1 : 0)));
     const int cr = a.g.cr;
+    // beyond the grid limits (very long folded 1-D signals, very many units) the generic kernels run
+    if (grid.y > 65535u || grid.z > 65535u) return CA_ERR_UNSUPPORTED;
     if (a.planes && cr > 16) { set_error("scalar planes are packed for one-slab units only"); return CA_ERR_UNSUPPORTED; }
 #define CA_PACK(CPEV)                                                        \
     do {                                                                     \
@@ -1507,13 +1481,15 @@ struct Launch {
     size_t smem;
 };
 
+// SM count of the current device (cached per device ordinal).
 int sm_count() {
-    static int n = 0;
+    static std::atomic<int> cache[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = cache[dev].load(std::memory_order_relaxed);
     if (!n) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cache[dev].store(n, std::memory_order_relaxed);
     }
     return n;
 }
@@ -1532,13 +1508,15 @@ int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* e
     const long cols = (g.W + nq - 1) / nq;
     const long ctas4 = cols * ((g.H + rw * warps - 1) / (rw * warps)) * g.units;
     int nsplit = (ctas4 * warps < 6L * sm_count()) ? 2 : 1;
-    nsplit = env_int("CIRCATT_SPLIT", nsplit);
+    nsplit = tune_int("CIRCATT_SPLIT", nsplit);
     if (!allow_split) nsplit = 1;
     if (nsplit == 2 && warps > 2) warps = 2;
-    warps = env_int(env_warps, warps);
+    warps = tune_int(env_warps, warps);
     if (warps * nsplit > 4) warps = 4 / nsplit;
     TileArgs& a = L->a;
     a.g = g;
+    a.status = status_word();
+    a.wait_tries = kWaitTries;
     a.TH = rw * warps;
     a.roff = P.pp - g.p;
     a.nsplit = nsplit;
@@ -1616,7 +1594,7 @@ int set_smem(K kernel, size_t bytes) {
 int pick_nq(const Geo& g, int wide, int narrow, const char* env) {
     const long tasks = ((long)(g.W + wide - 1) / wide) * ((g.H + 31) / 32) * g.units;     // warps at the wide tile
     const int nq = tasks < 12L * sm_count() ? narrow : wide;
-    return env_int(env, nq);
+    return tune_int(env, nq);
 }
 
 // mode 0: softmax; 1: entmax; 2: entmax pre-pass (writes D, needs no D and no dq).  The entmax
@@ -1639,13 +1617,11 @@ int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q,
 int run_dkdv(const Geo& g, const Padded& P, float scale, int dist, const float* k, const float* v, const float* qdy,
              const float* planes, float* dk, float* dv, cudaStream_t st, bool entmax = false) {
     Launch L{};
-    const int nq = entmax ? 3 : pick_nq(g, 3, 3, "CIRCATT_DKDV_NQ");
+    const int nq = 3;
     int rc = prepare(g, P, nq, 33 * nq, "CIRCATT_DKDV_WARPS", qdy, planes, &L);
     if (rc) return rc;
     L.a.scale = scale; L.a.c0 = k; L.a.c1 = v; L.a.o0 = dk; L.a.o1 = dv;
     if (entmax) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, true, L, st);
-    else if (nq == 1) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 1, false, L, st);
-    else if (nq == 2) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 2, false, L, st);
     else CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, false, L, st);
     CA_CHECK_LAUNCH("tiled dk/dv kernel");
     return CA_OK;
@@ -1793,7 +1769,7 @@ int tiled_emit_a(const Geo& g, float scale, int dist, const float* q, const floa
     {
         const size_t per_sm = 227 * 1024, with3 = L.smem + 1024;          // + the driver's per-CTA reservation
         const size_t with2 = with3 - (size_t)L.a.nsplit * L.a.stage_bytes;
-        const int want = env_int("CIRCATT_EMIT_STAGES", 0);
+        const int want = tune_int("CIRCATT_EMIT_STAGES", 0);
         // the kernel's registers allow three CTAs per SM at most
         if (want == 2 || (want == 0 && std::min<size_t>(3, per_sm / with2) > std::min<size_t>(3, per_sm / with3)))
             if (setup(2)) return rc;
@@ -1884,7 +1860,7 @@ static ForkJoin* fork_join_for_current_device() {
 // Whole backward in three launches: pack (both pairs, D, planes), dq, dk/dv.
 int tiled_attention_bwd(const Geo& gin, float scale, int dist, const float* q, const float* k, const float* v,
                         const float* y, const float* dy, const float* stats, float* D, float* dq, float* dk,
-                        float* dv, void* workspace, cudaStream_t st) {
+                        float* dv, void* workspace, const void* fwd_workspace, cudaStream_t st) {
     Geo g;
     if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
     if (!tiled_shape_ok(g) || g.Wk != g.W) return CA_ERR_UNSUPPORTED;
@@ -1894,14 +1870,24 @@ int tiled_attention_bwd(const Geo& gin, float scale, int dist, const float* q, c
     float* qdy = kv + P.pair_floats;
     float* planes = qdy + P.pair_floats;
     PackArgs pa{};
-    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 2;
-    pa.src[0] = k; pa.src[1] = v; pa.src[2] = q; pa.src[3] = dy;
-    pa.dst[0] = kv; pa.dst[1] = qdy;
+    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp;
+    if (fwd_workspace) {
+        // the forward of the same problem left its packed (k|v) at the start of its workspace: only
+        // (q|dy) and the planes are packed here
+        kv = const_cast<float*>(static_cast<const float*>(fwd_workspace));
+        pa.npairs = 1;
+        pa.src[0] = q; pa.src[1] = dy;
+        pa.dst[0] = qdy;
+    } else {
+        pa.npairs = 2;
+        pa.src[0] = k; pa.src[1] = v; pa.src[2] = q; pa.src[3] = dy;
+        pa.dst[0] = kv; pa.dst[1] = qdy;
+    }
     pa.planes = planes; pa.stats = stats; pa.stat_mul = kLog2e; pa.y = y; pa.dy = dy; pa.Dout = D;
     int rc = launch_pack(pa, st);
     if (rc) return rc;
     const bool small = (long)g.Np * g.units < 2048L * sm_count();      // fewer than ~4 CTAs per SM per sweep
-    if (small && env_int("CIRCATT_CONCURRENT", 1)) {
+    if (small && tune_int("CIRCATT_CONCURRENT", 1)) {
         std::lock_guard<std::mutex> lock(g_fork_mutex);
         ForkJoin* f = fork_join_for_current_device();
         if (f && cudaEventRecord(f->fork, st) == cudaSuccess && cudaStreamWaitEvent(f->side, f->fork, 0) == cudaSuccess) {
@@ -1986,7 +1972,10 @@ static int run_apply(const Geo& g, const Padded& P, const float* nz, const float
     // per warp: two buffers and, for single-piece 2-D windows, the two offset tables
     const bool tabled = g.ws <= kRunChunk && g.wsw != 1;
     L.smem += (size_t)L.threads / 32 * (2 * (g.wsw == 1 ? 1 : 4) * trw * chs + (tabled ? 2 * (32 / ns) * ch : 0)) * sizeof(float);
-    if (L.smem > 200 * 1024) return CA_ERR_UNSUPPORTED;
+    if (L.smem > 200 * 1024) {
+        set_error("tiled apply: window %d with %d channels per unit needs %zu bytes of shared memory", g.ws, g.cr, L.smem);
+        return CA_ERR_UNSUPPORTED;
+    }
     L.a.scale = alpha; L.a.which = 0; L.a.c0 = centre; L.a.cs0 = nz; L.a.o0 = out;
 #define CA_APPLY(NSV)                                                                     \
     do {                                                                                  \
@@ -2038,6 +2027,45 @@ int tiled_similarity_bwd(const Geo& gin, float scale, int dist, const float* x, 
         if ((rc = pack_single(g, P, x, packed, st))) return rc;
         if ((rc = run_apply(g, P, dS, packed, dist ? y : nullptr, dy, scale, 1, st))) return rc;
     }
+    return CA_OK;
+}
+
+
+// ---------------------------------------------------------------- bounded-wait self test
+// One CTA arms a stage barrier with more bytes than the single bulk copy it issues delivers, so the
+// barrier never completes; the wait must run out after `tries` polls, the CTA must report through the
+// same counter and status word as the tiled kernels and return.  Nothing faults and nothing spins
+// without a limit; the copy itself lands (the thread polls its destination, again with a limit).
+__device__ __align__(16) float g_probe_src[8] = {1.f, 2.f, 3.f, 4.f, 5.f, 6.f, 7.f, 8.f};
+
+__global__ void __launch_bounds__(32) stage_timeout_probe_kernel(uint32_t tries, int* status, int* out) {
+    __shared__ __align__(16) float dst[8];
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        dst[7] = 0.f;
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) {
+        mbar_arrive_expect_tx(&bar, 64);                      // 64 bytes expected ...
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 32, [%2];"
+                     ::"r"(smem_u32(dst)), "l"(g_probe_src), "r"(smem_u32(&bar)) : "memory");   // ... 32 delivered
+        ok = mbar_wait(&bar, 0, tries);
+        // the copy in flight gets a bounded chance to land before the CTA (and its shared memory) goes away
+        for (uint32_t i = 0; i < (1u << 16) && *reinterpret_cast<volatile float*>(&dst[7]) != 8.f; ++i) {}
+        if (!ok) {
+            atomicAdd(&g_stage_timeouts, 1);
+            if (status) atomicOr(status, 1);
+        }
+        if (out) *out = ok ? 0 : 1;
+    }
+}
+
+int tiled_probe_stage_timeout(uint32_t tries, int* out, cudaStream_t st) {
+    stage_timeout_probe_kernel<<<1, 32, 0, st>>>(tries, status_word(), out);
+    CA_CHECK_LAUNCH("stage timeout probe kernel");
     return CA_OK;
 }
 

@@ -16,7 +16,7 @@ int tiled_attention_fwd(const Geo& g, float scale, int dist, const float* q, con
                         float* y, float* nz, float* stats, void* workspace, cudaStream_t st);
 int tiled_attention_bwd(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                         const float* y, const float* dy, const float* stats, float* D, float* dq, float* dk,
-                        float* dv, void* workspace, cudaStream_t st);
+                        float* dv, void* workspace, const void* fwd_workspace, cudaStream_t st);
 int tiled_attention_bwd_dq(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                            const float* dy, const float* stats, const float* D, float* dq, void* workspace,
                            cudaStream_t st);
@@ -29,6 +29,8 @@ int tiled_attention_bwd_entmax(const Geo& g, float scale, int dist, const float*
                                void* workspace, cudaStream_t st);
 // Copies the count of stage-copy timeouts to the host (synchronises the device).
 int tiled_stage_timeouts(int* count);
+// Launches the one-CTA self test of the bounded stage wait (`out`: nullable device int, 1 = the wait ran out).
+int tiled_probe_stage_timeout(uint32_t tries, int* out, cudaStream_t st);
 
 // Stand-alone operators on the tiled kernels.  `workspace` holds one packed
 // tensor pair (tiled_operator_workspace bytes, 0 when the shape is not covered).

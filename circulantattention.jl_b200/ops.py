@@ -162,8 +162,59 @@ def apply(nz, v, ws, transpose=False, out=None):
     return out
 
 
-def attention_fwd(kind, normalizer, q, k, v, ws, want_nz, scale=None, band=None):
-    """Fused forward on (spatial..., c, units) tensors.  Returns (y, nz | None, stats).
+# Transient scratch per (device, stream, purpose): grown on demand and reused by later calls on the
+# same stream, which is safe because work on one stream is ordered.  Buffers that must outlive the
+# call (the forward workspace kept for the backward) are never taken from here.
+_SCRATCH = {}
+
+
+def _scratch(purpose, nbytes, device):
+    if not nbytes:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream, purpose)
+    buf = _SCRATCH.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _SCRATCH[key] = buf
+    return buf
+
+
+def release_scratch():
+    """Drops the cached transient workspaces (they are re-created on demand)."""
+    _SCRATCH.clear()
+
+
+# ------------------------------------------------------------------ device-side failure reporting
+_STATUS = {}
+
+
+def _status_word(device):
+    """Registers (once per device and host thread use) the int32 the kernels flag a timed-out wait in."""
+    w = _STATUS.get(device.index)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[device.index] = w
+    check(lib.ca_status_word(ptr(w)))
+    return w
+
+
+def check_status(device=None):
+    """Synchronising check: raises if a kernel of this library gave up a bounded device-side wait since the
+    last check on `device` (its tile then holds NaN).  Call it where the program synchronises anyway."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = _STATUS.get(device.index)
+    if w is None:
+        return
+    flag = int(w.item())
+    if flag:
+        w.zero_()
+        raise _lib.CircAttError("a circatt_b200 kernel gave up a bounded wait for a shared-memory stage copy; "
+                                "the outputs of that call hold NaN")
+
+
+def attention_fwd(kind, normalizer, q, k, v, ws, want_nz, scale=None, band=None, keep_workspace=False):
+    """Fused forward on (spatial..., c, units) tensors.  Returns (y, nz | None, stats), plus the workspace
+    tensor when `keep_workspace` (hand it to attention_bwd as `fwd_workspace`).
     `band=(Wk, wk_off)` selects band mode: k, v then have Wk columns."""
     require_cuda(q, k, v)
     q, k, v = _dense_ok(q), _dense_ok(k), _dense_ok(v)
@@ -175,14 +226,19 @@ def attention_fwd(kind, normalizer, q, k, v, ws, want_nz, scale=None, band=None)
     nz = jl.empty((m.Np * m.K, m.units), torch.float32, q.device) if want_nz else None
     stats = jl.empty((m.Np, m.units), torch.float32, q.device)
     nbytes = lib.ca_attention_fwd_workspace(d, int(want_nz))
-    wsb = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
     with torch.cuda.device(q.device):
+        _status_word(q.device)
+        if keep_workspace:
+            wsb = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
+        else:
+            wsb = _scratch("fwd", nbytes, q.device)
         check(lib.ca_attention_fwd(d, ptr(q), ptr(k), ptr(v), ptr(y), ptr(nz), ptr(stats), ptr(wsb), _stream()))
-    return y, nz, stats
+    return (y, nz, stats, wsb) if keep_workspace else (y, nz, stats)
 
 
-def attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=None, dA=None, scale=None):
-    """Fused backward.  Returns (dq, dk, dv)."""
+def attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=None, dA=None, scale=None, fwd_workspace=None):
+    """Fused backward.  Returns (dq, dk, dv).  `fwd_workspace`: the workspace kept from the matching
+    attention_fwd(keep_workspace=True) call, untouched since (spares packing k and v again)."""
     q, k, v, y, dy = (_dense_ok(t) for t in (q, k, v, y, dy))
     m = meta_of(q, ws)
     scale = 1.0 / math.sqrt(m.channels) if scale is None else scale
@@ -190,10 +246,11 @@ def attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=None, dA=None,
     dq, dk, dv = (jl.empty(q.shape, q.dtype, q.device) for _ in range(3))
     if dA is not None:
         dA = jl.colmajor(dA)
-    wsb = torch.empty(lib.ca_attention_bwd_workspace(d), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
+        _status_word(q.device)
+        wsb = _scratch("bwd", lib.ca_attention_bwd_workspace(d), q.device)
         check(lib.ca_attention_bwd(d, ptr(q), ptr(k), ptr(v), ptr(y), ptr(dy), ptr(stats), ptr(nz), ptr(dA),
-                                   ptr(dq), ptr(dk), ptr(dv), ptr(wsb), _stream()))
+                                   ptr(dq), ptr(dk), ptr(dv), ptr(wsb), ptr(fwd_workspace), _stream()))
     return dq, dk, dv
 
 

@@ -160,12 +160,19 @@ int ca_attention_fwd_static(const ca_desc* d, const void* q, const void* k, cons
  * similarity, softmax and apply: src/rrules.jl:1-72).  `dA` (nullable) is the
  * cotangent arriving on the returned A (CSR order); when it is given, `nz`
  * (the A saved by the forward) must be given as well.  `y` is the forward
- * output.  dq, dk, dv are overwritten.  Deterministic: no atomics. */
+ * output.  dq, dk, dv are overwritten.  Deterministic: no atomics.
+ * `fwd_workspace` (nullable) is the workspace the matching ca_attention_fwd
+ * call (same descriptor, same k and v) was given, left untouched since: the
+ * tiled softmax kernels then stream the packed copy of (k, v) the forward left
+ * there instead of packing k and v again.  The Julia counterpart is keeping a
+ * forward intermediate alive inside the pullback closure (src/rrules.jl:44-55
+ * keeps the softmax output that way). */
 size_t ca_attention_bwd_workspace(const ca_desc* d);
 int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void* v,
                      const void* y, const void* dy, const float* stats,
                      const float* nz, const float* dA,
-                     void* dq, void* dk, void* dv, void* workspace, void* stream);
+                     void* dq, void* dk, void* dv, void* workspace, const void* fwd_workspace,
+                     void* stream);
 
 /* The three stages of ca_attention_bwd, exposed separately for the band-split
  * (multi-GPU) path, where D and the query-side halos are exchanged between
@@ -186,10 +193,18 @@ int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const 
                           const void* dy, const float* stats, const float* D, const float* dA,
                           void* dk, void* dv, void* workspace, void* stream);
 
-/* Diagnostics (synchronises the device): number of thread blocks that gave up
- * waiting for a shared-memory stage copy since the library was loaded.  Every
- * device-side wait in the library is bounded; a non-zero count means results
- * of some call are invalid.  No counterpart in the reference. */
+/* Failure reporting of the device-side waits.  Every wait in the library's
+ * kernels (the shared-memory stage copies of the tiled kernels) is bounded.  A
+ * thread block whose wait runs out stops computing, stores NaN instead of
+ * results for its tile, bumps a per-device counter, and sets bit 0 of the
+ * status word registered by the host thread that made the call.
+ * ca_status_word registers a device int32 (zeroed by the caller) for all later
+ * calls of the calling host thread (NULL: none); the caller reads it at its
+ * own synchronisation points.  ca_stage_timeouts copies the counter of the
+ * current device to the host (it synchronises the device: a diagnostic, not
+ * for hot paths).  The reference has no counterpart: CUDA.jl kernels cannot
+ * time out, they hang (src/similarity.jl:47-51 launches without any bound). */
+int ca_status_word(int32_t* device_word);
 int ca_stage_timeouts(int32_t* count);
 
 /* ---------------------------------------------------------------- algebra on values

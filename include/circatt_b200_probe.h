@@ -24,6 +24,14 @@ int64_t ca_probe_tiled_launch_count(void);
  * blocks*256*iters*16*2 FMAs = twice that many flops. */
 int ca_probe_ffma(int32_t blocks, int32_t iters, float* sink, void* stream);
 
+/* Self test of the bounded device-side waits: launches one thread block that arms a stage
+ * barrier with 64 bytes and issues a 32-byte bulk copy, so the barrier can never complete.  The
+ * wait gives up after `max_tries` polls (1..2^20); the block then reports exactly like the tiled
+ * kernels (ca_stage_timeouts grows by one, bit 0 of the registered status word is set), writes
+ * 1 to `out` (nullable device int32; 0 would mean the wait completed) and returns.  Nothing
+ * traps, faults or waits without a limit. */
+int ca_probe_stage_timeout(int32_t max_tries, int32_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

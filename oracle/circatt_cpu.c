@@ -48,6 +48,10 @@ static inline int wrapi(int x, int X) {
     return x;
 }
 
+/* Work is shared between the threads as (unit, block of CA_CPU_BLOCK pixels) items, so that
+ * every thread has work even when there are fewer units than cores. */
+#define CA_CPU_BLOCK 256
+
 #define DEFINE_CPU(REAL, SUFFIX, EXP, LOG)                                                          \
     /* (Np, c) pixel-major copy of one unit so that the channel loop is contiguous */               \
     static void to_pixel_major_##SUFFIX(const REAL* x, REAL* t, int Np, int c) {                     \
@@ -73,31 +77,41 @@ static inline int wrapi(int x, int X) {
                                       REAL* y, REAL* lse) {                                         \
         const int Np = H * W, p = (ws - 1) / 2, wsw = ndim == 2 ? ws : 1, pw = ndim == 2 ? p : 0;   \
         if (ws % 2 != 1 || H < ws || (ndim == 2 && W < ws)) return -1;                              \
+        const size_t per = (size_t)Np * c, all = per * units;                                       \
+        const int nblk = (Np + CA_CPU_BLOCK - 1) / CA_CPU_BLOCK;                                    \
+        REAL* buf = (REAL*)malloc(sizeof(REAL) * all * 4);                                          \
+        if (!buf) return -2;                                                                        \
+        REAL *qt = buf, *kt = qt + all, *vt = kt + all, *yt = vt + all;                             \
         _Pragma("omp parallel")                                                                     \
         {                                                                                           \
-            REAL* qt = (REAL*)malloc(sizeof(REAL) * (size_t)Np * c * 4);                            \
-            REAL *kt = qt + (size_t)Np * c, *vt = kt + (size_t)Np * c, *yt = vt + (size_t)Np * c;   \
             REAL* sc = (REAL*)malloc(sizeof(REAL) * (size_t)ws * wsw);                              \
             _Pragma("omp for schedule(dynamic, 1)")                                                 \
-            for (int u = 0; u < units; ++u) {                                                       \
-                const size_t uo = (size_t)u * c * Np;                                               \
-                to_pixel_major_##SUFFIX(q + uo, qt, Np, c);                                         \
-                to_pixel_major_##SUFFIX(k + uo, kt, Np, c);                                         \
-                to_pixel_major_##SUFFIX(v + uo, vt, Np, c);                                         \
-                for (int j = 0; j < Np; ++j) {                                                      \
+            for (int t = 0; t < 3 * units; ++t) {                                                   \
+                const int u = t / 3, which = t % 3;                                                 \
+                const REAL* src = which == 0 ? q : (which == 1 ? k : v);                            \
+                REAL* dst = which == 0 ? qt : (which == 1 ? kt : vt);                               \
+                to_pixel_major_##SUFFIX(src + per * u, dst + per * u, Np, c);                       \
+            }                                                                                       \
+            _Pragma("omp for schedule(dynamic, 1)")                                                 \
+            for (int item = 0; item < units * nblk; ++item) {                                       \
+                const int u = item / nblk, j0 = (item % nblk) * CA_CPU_BLOCK;                       \
+                const int j1 = j0 + CA_CPU_BLOCK < Np ? j0 + CA_CPU_BLOCK : Np;                     \
+                const REAL *qu = qt + per * u, *ku = kt + per * u, *vu = vt + per * u;              \
+                REAL* yu = yt + per * u;                                                            \
+                for (int j = j0; j < j1; ++j) {                                                     \
                     const int h = j % H, w = j / H;                                                 \
-                    const REAL* qj = qt + (size_t)j * c;                                            \
+                    const REAL* qj = qu + (size_t)j * c;                                            \
                     REAL m = -INFINITY;                                                             \
                     int n = 0;                                                                      \
                     for (int dw = -pw; dw <= pw; ++dw)                                              \
                         for (int dh = -p; dh <= p; ++dh) {                                          \
                             const int i = wrapi(h + dh, H) + H * wrapi(w + dw, W);                  \
-                            const REAL s = score_##SUFFIX(qj, kt + (size_t)i * c, c, dist, scale);  \
+                            const REAL s = score_##SUFFIX(qj, ku + (size_t)i * c, c, dist, scale);  \
                             sc[n++] = s;                                                            \
                             if (s > m) m = s;                                                       \
                         }                                                                           \
                     REAL l = 0;                                                                     \
-                    REAL* yj = yt + (size_t)j * c;                                                  \
+                    REAL* yj = yu + (size_t)j * c;                                                  \
                     for (int mm = 0; mm < c; ++mm) yj[mm] = 0;                                      \
                     n = 0;                                                                          \
                     for (int dw = -pw; dw <= pw; ++dw)                                              \
@@ -105,18 +119,19 @@ static inline int wrapi(int x, int X) {
                             const int i = wrapi(h + dh, H) + H * wrapi(w + dw, W);                  \
                             const REAL e = EXP(sc[n++] - m);                                        \
                             l += e;                                                                 \
-                            const REAL* vi = vt + (size_t)i * c;                                    \
+                            const REAL* vi = vu + (size_t)i * c;                                    \
                             for (int mm = 0; mm < c; ++mm) yj[mm] += e * vi[mm];                    \
                         }                                                                           \
                     const REAL inv = (REAL)1 / l;                                                   \
                     for (int mm = 0; mm < c; ++mm) yj[mm] *= inv;                                   \
                     if (lse) lse[(size_t)u * Np + j] = m + LOG(l);                                  \
                 }                                                                                   \
-                from_pixel_major_##SUFFIX(yt, y + uo, Np, c);                                       \
             }                                                                                       \
-            free(qt);                                                                               \
+            _Pragma("omp for schedule(dynamic, 1)")                                                 \
+            for (int u = 0; u < units; ++u) from_pixel_major_##SUFFIX(yt + per * u, y + per * u, Np, c); \
             free(sc);                                                                               \
         }                                                                                           \
+        free(buf);                                                                                  \
         return 0;                                                                                   \
     }                                                                                               \
     /* Gradient: P from the saved log-sum-exp; dq is query-owned, dk and dv key-owned gathers */     \
@@ -127,38 +142,49 @@ static inline int wrapi(int x, int X) {
                                       REAL* dq, REAL* dk, REAL* dv) {                               \
         const int Np = H * W, p = (ws - 1) / 2, pw = ndim == 2 ? p : 0;                             \
         if (ws % 2 != 1 || H < ws || (ndim == 2 && W < ws)) return -1;                              \
+        const size_t per = (size_t)Np * c, all = per * units;                                       \
+        const int nblk = (Np + CA_CPU_BLOCK - 1) / CA_CPU_BLOCK;                                    \
+        REAL* buf = (REAL*)malloc(sizeof(REAL) * (all * 7 + (size_t)Np * units));                   \
+        if (!buf) return -2;                                                                        \
+        REAL *qt = buf, *kt = qt + all, *vt = kt + all, *dyt = vt + all, *dqt = dyt + all,          \
+             *dkt = dqt + all, *dvt = dkt + all, *Dall = dvt + all;                                 \
         _Pragma("omp parallel")                                                                     \
         {                                                                                           \
-            REAL* buf = (REAL*)malloc(sizeof(REAL) * ((size_t)Np * c * 7 + Np));                    \
-            REAL *qt = buf, *kt = qt + (size_t)Np * c, *vt = kt + (size_t)Np * c,                   \
-                 *dyt = vt + (size_t)Np * c, *dqt = dyt + (size_t)Np * c,                           \
-                 *dkt = dqt + (size_t)Np * c, *dvt = dkt + (size_t)Np * c, *D = dvt + (size_t)Np * c; \
             _Pragma("omp for schedule(dynamic, 1)")                                                 \
-            for (int u = 0; u < units; ++u) {                                                       \
-                const size_t uo = (size_t)u * c * Np;                                               \
-                const REAL* L = lse + (size_t)u * Np;                                               \
-                to_pixel_major_##SUFFIX(q + uo, qt, Np, c);                                         \
-                to_pixel_major_##SUFFIX(k + uo, kt, Np, c);                                         \
-                to_pixel_major_##SUFFIX(v + uo, vt, Np, c);                                         \
-                to_pixel_major_##SUFFIX(dy + uo, dyt, Np, c);                                       \
-                to_pixel_major_##SUFFIX(y + uo, dqt, Np, c);                                        \
+            for (int t = 0; t < 5 * units; ++t) {                                                   \
+                const int u = t / 5, which = t % 5;                                                 \
+                const REAL* src = which == 0 ? q : which == 1 ? k : which == 2 ? v : which == 3 ? dy : y; \
+                REAL* dst = which == 0 ? qt : which == 1 ? kt : which == 2 ? vt : which == 3 ? dyt : dqt; \
+                to_pixel_major_##SUFFIX(src + per * u, dst + per * u, Np, c);                       \
+            }                                                                                       \
+            _Pragma("omp for schedule(static)")                                                     \
+            for (int u = 0; u < units; ++u)                                                         \
                 for (int j = 0; j < Np; ++j) {                                                      \
                     REAL d = 0;                                                                     \
-                    for (int mm = 0; mm < c; ++mm) d += dyt[(size_t)j * c + mm] * dqt[(size_t)j * c + mm]; \
-                    D[j] = d;                                                                       \
+                    for (int mm = 0; mm < c; ++mm)                                                  \
+                        d += dyt[per * u + (size_t)j * c + mm] * dqt[per * u + (size_t)j * c + mm]; \
+                    Dall[(size_t)u * Np + j] = d;                                                   \
                 }                                                                                   \
-                for (int j = 0; j < Np; ++j) {                                                      \
+            _Pragma("omp for schedule(dynamic, 1)")                                                 \
+            for (int item = 0; item < units * nblk; ++item) {                                       \
+                const int u = item / nblk, j0 = (item % nblk) * CA_CPU_BLOCK;                       \
+                const int j1 = j0 + CA_CPU_BLOCK < Np ? j0 + CA_CPU_BLOCK : Np;                     \
+                const REAL* L = lse + (size_t)u * Np;                                               \
+                const REAL* D = Dall + (size_t)u * Np;                                              \
+                const REAL *qu = qt + per * u, *ku = kt + per * u, *vu = vt + per * u, *dyu = dyt + per * u; \
+                for (int j = j0; j < j1; ++j) {                                                     \
                     const int h = j % H, w = j / H;                                                 \
-                    const REAL *qj = qt + (size_t)j * c, *dyj = dyt + (size_t)j * c;                \
-                    const REAL *kj = kt + (size_t)j * c, *vj = vt + (size_t)j * c;                  \
-                    REAL *gq = dqt + (size_t)j * c, *gk = dkt + (size_t)j * c, *gv = dvt + (size_t)j * c; \
+                    const REAL *qj = qu + (size_t)j * c, *dyj = dyu + (size_t)j * c;                \
+                    const REAL *kj = ku + (size_t)j * c, *vj = vu + (size_t)j * c;                  \
+                    REAL *gq = dqt + per * u + (size_t)j * c, *gk = dkt + per * u + (size_t)j * c,  \
+                         *gv = dvt + per * u + (size_t)j * c;                                       \
                     REAL sq = 0, sk = 0;                                                            \
                     for (int mm = 0; mm < c; ++mm) gq[mm] = gk[mm] = gv[mm] = 0;                    \
                     for (int dw = -pw; dw <= pw; ++dw)                                              \
                         for (int dh = -p; dh <= p; ++dh) {                                          \
                             const int i = wrapi(h + dh, H) + H * wrapi(w + dw, W);                  \
-                            const REAL *ki = kt + (size_t)i * c, *vi = vt + (size_t)i * c;          \
-                            const REAL *qi = qt + (size_t)i * c, *dyi = dyt + (size_t)i * c;        \
+                            const REAL *ki = ku + (size_t)i * c, *vi = vu + (size_t)i * c;          \
+                            const REAL *qi = qu + (size_t)i * c, *dyi = dyu + (size_t)i * c;        \
                             /* row j, column i */                                                   \
                             REAL s = score_##SUFFIX(qj, ki, c, dist, scale), dp = 0;                \
                             for (int mm = 0; mm < c; ++mm) dp += dyj[mm] * vi[mm];                  \
@@ -180,12 +206,16 @@ static inline int wrapi(int x, int X) {
                         gk[mm] = scale * (gk[mm] - (dist ? sk * kj[mm] : 0));                       \
                     }                                                                               \
                 }                                                                                   \
-                from_pixel_major_##SUFFIX(dqt, dq + uo, Np, c);                                     \
-                from_pixel_major_##SUFFIX(dkt, dk + uo, Np, c);                                     \
-                from_pixel_major_##SUFFIX(dvt, dv + uo, Np, c);                                     \
             }                                                                                       \
-            free(buf);                                                                              \
+            _Pragma("omp for schedule(dynamic, 1)")                                                 \
+            for (int t = 0; t < 3 * units; ++t) {                                                   \
+                const int u = t / 3, which = t % 3;                                                 \
+                const REAL* src = which == 0 ? dqt : (which == 1 ? dkt : dvt);                      \
+                REAL* dst = which == 0 ? dq : (which == 1 ? dk : dv);                               \
+                from_pixel_major_##SUFFIX(src + per * u, dst + per * u, Np, c);                     \
+            }                                                                                       \
         }                                                                                           \
+        free(buf);                                                                                  \
         return 0;                                                                                   \
     }
 

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from oracle import circatt_oracle as orc
-from tests.helpers import KIND, TOL, randn, rel_err, up
+from tests.helpers import KIND, TOL, assert_close, randn, rel_err, up
 
 pytestmark = pytest.mark.gpu
 
@@ -91,11 +91,11 @@ def test_attention_forward_backward(ca, shape, ws, nheads, cplx, simname):
 
     yo, nzo = orc.mh_attention(KIND[simname], up(qn), up(kn), up(vn), ws, nheads)
     dqo, dko, dvo = orc.mh_attention_pullback(KIND[simname], up(qn), up(kn), up(vn), ws, nheads, up(rn))
-    assert rel_err(ca.jl.to_numpy(y), yo) < TOL
-    assert rel_err(ca.jl.to_numpy(A.nzVal), nzo) < TOL
-    assert rel_err(ca.jl.to_numpy(q.grad), dqo) < TOL
-    assert rel_err(ca.jl.to_numpy(k.grad), dko) < TOL
-    assert rel_err(ca.jl.to_numpy(v.grad), dvo) < TOL
+    assert_close(ca.jl.to_numpy(y), yo, "y")
+    assert_close(ca.jl.to_numpy(A.nzVal), nzo, "A")
+    assert_close(ca.jl.to_numpy(q.grad), dqo, "dq")
+    assert_close(ca.jl.to_numpy(k.grad), dko, "dk")
+    assert_close(ca.jl.to_numpy(v.grad), dvo, "dv")
 
 
 @pytest.mark.parametrize("simname", ["dot", "distance"])
@@ -404,4 +404,5 @@ def test_no_stage_copy_timed_out(ca):
     import ctypes
     n = ctypes.c_int32(-1)
     assert ca.lib.ca_stage_timeouts(ctypes.byref(n)) == 0
-    assert n.value == 0
+    # only the self test of the bounded wait (tests/test_gpu_timeout.py) may have bumped the counter
+    assert n.value == getattr(ca.ops, "probe_timeouts_provoked", 0)
