@@ -143,20 +143,228 @@ def reference_main(args):
 
 
 
-# --------------------------------------------------------------------------- other configurations (--extra)
-EXTRA_CONFIGS = {
-    # name: (Julia shape, ws, heads, similarity, normaliser, complex, A materialised)
-    "c1": ((32, 32, 16, 1), 7, 1, 0, 0, False, True),
-    "c2": ((128, 96, 64, 2), 15, 4, 0, 0, False, False),
-    "c3": ((16384, 64, 16), 127, 8, 1, 1, False, False),          # 1-D, Distance, entmax-1.5
-    "c4": ((320, 320, 32, 8), 7, 1, 0, 0, True, True),            # ComplexF32, A materialised
-    "c5_one_batch": ((1024, 1024, 128, 1), 21, 8, 0, 0, False, False),
+# --------------------------------------------------------------------------- other configurations
+OTHER_CONFIGS = {
+    # name: (Julia shape, ws, heads, similarity, normaliser, complex, A materialised, storage dtype)
+    "c1": ((32, 32, 16, 1), 7, 1, 0, 0, False, True, "f32"),
+    "c3": ((16384, 64, 16), 127, 8, 1, 1, False, False, "f32"),        # 1-D, Distance, entmax-1.5
+    "c4": ((320, 320, 32, 8), 7, 1, 0, 0, True, True, "c64"),          # ComplexF32, A materialised
+    "c5_one_batch_f32": ((1024, 1024, 128, 1), 21, 8, 0, 0, False, False, "f32"),
+    "c5_one_batch_bf16": ((1024, 1024, 128, 1), 21, 8, 0, 0, False, False, "bf16"),
 }
 
 
+def config_flops(shape, ws, kind, cplx):
+    """Algorithmic flops per query pixel (forward, backward): Dot 4*K*C / 10*K*C, Distance 5*K*C / 11*K*C,
+    complex channels counted twice."""
+    K = ws ** (len(shape) - 2)
+    C = shape[-2] * (2 if cplx else 1)
+    return (5 if kind else 4) * K * C, (11 if kind else 10) * K * C
+
+
+def make_timer(torch, flush):
+    def timed(fn, n=5, warm=2):
+        for _ in range(warm):
+            fn()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for a, b in evs:
+            flush.fill_(1)
+            a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        ts = sorted(a.elapsed_time(b) * 1e-3 for a, b in evs)
+        return ts[len(ts) // 2]
+    return timed
+
+
+def time_config(ca, torch, timed, gen, cfg, ffma_tflops):
+    """Forward and forward+backward of one BASELINE configuration through the ops layer (C ABI), device
+    resident, L2 flushed before every timed call."""
+    shape, ws, nh, kind, norm, cplx, want_nz, store = cfg
+    ops, jl = ca.ops, ca.jl
+    dt = torch.complex64 if cplx else torch.float32
+    q, k, v, dy = (ca.splitheads(jl.randn(*shape, generator=gen, dtype=dt), nh) for _ in range(4))
+    if store == "bf16":
+        q, k, v, dy = (t.to(torch.bfloat16) for t in (q, k, v, dy))
+    px = int(np.prod(shape[:-2])) * shape[-1]
+    res = {}
+
+    def fwd():
+        res["r"] = ops.attention_fwd(kind, norm, q, k, v, ws, want_nz, keep_workspace=True)
+    tf = timed(fwd)
+    y, nz, stats, fws = res["r"]
+    tb = timed(lambda: ops.attention_bwd(kind, norm, q, k, v, y, dy, stats, ws, nz=nz,
+                                         fwd_workspace=fws if norm == 0 else None))
+    fl_f, fl_b = config_flops(shape, ws, kind, cplx)
+    out = {"fwd_us": tf * 1e6, "bwd_us": tb * 1e6, "fwd_px_per_s": px / tf, "fwd_bwd_px_per_s": px / (tf + tb),
+           "fwd_tflops": px * fl_f / tf / 1e12, "bwd_tflops": px * fl_b / tb / 1e12,
+           "roofline_frac_ffma": px * (fl_f + fl_b) / (tf + tb) / 1e12 / ffma_tflops}
+    del q, k, v, dy, y, nz, stats, fws, res
+    ops.release_scratch()
+    torch.cuda.empty_cache()
+    return out
+
+
+# --------------------------------------------------------------------------- independent float64 check (torch)
+def sampled_reference(torch, q, k, v, dy, ws, pixels, unit):
+    """Float64 torch restatement of softmax circulant attention and its gradients at a few pixels of one
+    unit: y[j] and dq[j] need the window of j; dk[i] and dv[i] need every query whose window holds i,
+    each with its own window.  q, k, v, dy: (H, W, c, units) tensors of the FULL image.  Returns four
+    (len(pixels), c) float64 tensors."""
+    H, W, c = q.shape[0], q.shape[1], q.shape[2]
+    p = (ws - 1) // 2
+    scale = 1.0 / float(c) ** 0.5
+    Q, Kk, V, DY = (t[..., unit].double() for t in (q, k, v, dy))
+    d = torch.arange(-p, p + 1, device=q.device)
+
+    def windows(hs, ws_):
+        """key pixels of the queries (hs[n], ws_[n]): index tensors (n, K), w-major like the CSR order"""
+        hh = (hs[:, None] + d[None, :]) % H                      # (n, ws)
+        ww = (ws_[:, None] + d[None, :]) % W
+        return hh[:, None, :].expand(-1, ws, -1).reshape(len(hs), -1), ww[:, :, None].expand(-1, -1, ws).reshape(len(hs), -1)
+
+    def rows(hs, ws_):
+        hh, ww = windows(hs, ws_)
+        kw, vw = Kk[hh, ww], V[hh, ww]                           # (n, K, c)
+        qs, dys = Q[hs, ws_], DY[hs, ws_]                        # (n, c)
+        P = torch.softmax(scale * torch.einsum("nc,nkc->nk", qs, kw), dim=1)
+        dP = torch.einsum("nc,nkc->nk", dys, vw)
+        dS = P * (dP - (P * dP).sum(1, keepdim=True))
+        return P, dS, kw, vw, hh, ww
+
+    hs = torch.tensor([j % H for j in pixels], device=q.device)
+    wcol = torch.tensor([j // H for j in pixels], device=q.device)
+    P, dS, kw, vw, hh, ww = rows(hs, wcol)
+    y = torch.einsum("nk,nkc->nc", P, vw)
+    dq = scale * torch.einsum("nk,nkc->nc", dS, kw)
+    dk, dv = torch.zeros_like(y), torch.zeros_like(y)
+    for n in range(len(pixels)):
+        # the queries that see pixel n are the pixels of its own window (window symmetry)
+        hq, wq = hh[n], ww[n]
+        Pq, dSq, _, _, hhq, wwq = rows(hq, wq)
+        hit = (hhq == hs[n]) & (wwq == wcol[n])                  # position of pixel n inside each of those windows
+        dk[n] = scale * ((dSq * hit).sum(1)[:, None] * Q[hq, wq]).sum(0)
+        dv[n] = ((Pq * hit).sum(1)[:, None] * DY[hq, wq]).sum(0)
+    return y, dq, dk, dv
+
+
+def band_c5(ca, torch, dist, dev, world, rank, steps):
+    """One 1024 x 1024 x 128 image of BASELINE config 5 (ws 21, 8 heads, flash mode) cut into bands of columns
+    over the ranks: forward + backward with the halo exchanges (the circular wrap between the last and the
+    first rank included) inside the timed region, and a float64 check of rank 0's band at border pixels."""
+    jl, par = ca.jl, ca.parallel
+    H, W, C, ws, nh = 1024, 1024, 128, 21, 8
+    plan = par.BandPlan(W, world, ws)
+    start, width = plan.band(rank)
+    gen = torch.Generator(device=dev).manual_seed(1234)          # every rank draws the same full image
+    full = [ca.splitheads(jl.randn(H, W, C, 1, generator=gen, device=dev), nh) for _ in range(4)]
+    q, k, v, dy = (jl.colmajor(t.narrow(1, start, width).clone()) for t in full)
+    if rank != 0:
+        del full
+    out = {}
+
+    def step():
+        y, stats, k_ext, v_ext = par.band_attention_fwd(0, q, k, v, ws)
+        out["r"] = (y,) + tuple(par.band_attention_bwd(0, q, k, v, y, dy, stats, k_ext, v_ext, ws))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        step()
+    barrier()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        a.record(); step(); b.record()          # >= 67 MB per tensor and rank: larger than what stays in L2 between uses
+    barrier()
+    total = torch.tensor([sum(a.elapsed_time(b) for a, b in evs) * 1e-3], dtype=torch.float64, device=dev)
+    # exchange share: the same step with the exchanges alone (no kernels)
+    p = plan.p
+    ex_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    st0 = jl.empty((H, width, q.shape[-1]), torch.float32, dev)
+    for a, b in ex_evs:
+        a.record()
+        par.exchange_halos([k, v], p)
+        par.exchange_halos([q, dy, st0, st0], p)
+        b.record()
+    barrier()
+    ex_total = torch.tensor([sum(a.elapsed_time(b) for a, b in ex_evs) * 1e-3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+        dist.all_reduce(ex_total, op=dist.ReduceOp.MAX)
+    res = None
+    if rank == 0:
+        t = float(total.item()) / steps
+        cols = sorted({0, p - 1, p, width // 2, width - p - 1, width - 1})
+        rows_ = [0, 5, H // 2, H - 1]
+        pixels = [h + H * (start + w) for w in cols for h in rows_]
+        local = [h + H * w for w in cols for h in rows_]
+        err = 0.0
+        for unit in (0, nh - 1):
+            want = sampled_reference(torch, *full, ws, pixels, unit)
+            for got_t, want_t in zip(out["r"], want):
+                got = jl.reshape(got_t, (H * width, got_t.shape[-2], got_t.shape[-1]))[local, :, unit].double()
+                err = max(err, float((got - want_t).abs().max() / want_t.abs().max()))
+        res = {"workload": "one 1024x1024x128 image, ws=21, 8 heads, Dot, flash mode, band split over columns with "
+                           "halo exchange, fwd+bwd", "scaling": "strong", "steps": steps, "ms_per_step": t * 1e3,
+               "px_per_s": H * W / t, "band_columns": width, "halo_columns": p,
+               "exchange_ms_per_step": float(ex_total.item()) / steps * 1e3,
+               "exchange_share": float(ex_total.item()) / float(total.item()),
+               "parity": {"against": "float64 torch restatement at 24 pixels x 2 units of rank 0's band "
+                                     "(band borders and the wrap columns included): y, dq, dk, dv",
+                          "max_rel_err": err, "bar": 1e-5, "ok": bool(err < 1e-5)}}
+    del out, q, k, v, dy
+    ca.ops.release_scratch()
+    torch.cuda.empty_cache()
+    return res
+
+
+def units_c5(ca, torch, dist, dev, world, rank, steps):
+    """All of BASELINE config 5 (1024 x 1024 x 128, B = 16, ws 21, 8 heads = 128 independent units) sharded
+    over batch x heads units with no collective.  A rank walks through its units 16 at a time; the chunks
+    reuse one set of buffers (synthetic data: every chunk computes on the same values), which bounds the
+    memory to what a 16-unit chunk needs whatever the number of ranks."""
+    ops, jl, par = ca.ops, ca.jl, ca.parallel
+    H, W, c, ws, units, chunk = 1024, 1024, 16, 21, 128, 16
+    _, mine = par.shard_units(units, world, rank)
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    q, k, v, dy = (jl.randn(H, W, c, chunk, generator=gen, device=dev) for _ in range(4))
+    nchunks = max(1, (mine + chunk - 1) // chunk)
+
+    def step():
+        for _ in range(nchunks):
+            y, _, stats, fws = ops.attention_fwd(0, 0, q, k, v, ws, False, keep_workspace=True)
+            ops.attention_bwd(0, 0, q, k, v, y, dy, stats, ws, fwd_workspace=fws)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step()
+    barrier()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        a.record(); step(); b.record()          # 1 GB per tensor: far larger than L2
+    barrier()
+    total = torch.tensor([sum(a.elapsed_time(b) for a, b in evs) * 1e-3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    t = float(total.item()) / steps
+    del q, k, v, dy
+    ops.release_scratch()
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    return {"workload": "config 5 whole: 1024x1024x128, B=16, ws=21, 8 heads (128 units), Dot, flash mode, fwd+bwd, "
+                        "units sharded over ranks, 16 units per launch", "scaling": "strong", "steps": steps,
+            "ms_per_step": t * 1e3, "px_per_s": H * W * 16 / t, "units_per_rank": mine}
+
+
 def extra_main(args):
-    """Not the headline: forward / backward times of the other BASELINE configurations and of the
-    stand-alone operators at the bench shape, one JSON line.  L2 is flushed before every timed call."""
+    """Not the headline: the stand-alone operators at the bench shape, one JSON line (L2 flushed before every
+    timed call).  The other BASELINE configurations are part of the default run (`other_configs`)."""
     import torch
     from __graft_entry__ import load_package
     torch.cuda.set_device(0)
@@ -164,39 +372,8 @@ def extra_main(args):
     ops, jl = ca.ops, ca.jl
     gen = torch.Generator(device="cuda").manual_seed(0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-
-    def timed(fn, n=5):
-        fn(); fn()
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
-        for a, b in evs:
-            for _ in range(4):
-                flush.fill_(1)             # also lets the host run ahead of the device
-            a.record(); fn(); b.record()
-        torch.cuda.synchronize()
-        return sorted(a.elapsed_time(b) * 1e-3 for a, b in evs)[n // 2]
-
-    out = {"configs": {}, "operators_c2_us": {}}
-    for name, (shape, ws, nh, kind, norm, cplx, want_nz) in EXTRA_CONFIGS.items():
-        if args.extra == "operators":
-            break
-        dt = torch.complex64 if cplx else torch.float32
-        q, k, v, dy = (ca.splitheads(jl.randn(*shape, generator=gen, dtype=dt), nh) for _ in range(4))
-        C = shape[-2] * (2 if cplx else 1)
-        Np, K = int(np.prod(shape[:-2])), ws ** (len(shape) - 2)
-        px = Np * shape[-1]
-        res = {}
-        tf = timed(lambda: res.__setitem__("r", ops.attention_fwd(kind, norm, q, k, v, ws, want_nz)))
-        y, nz, stats = res["r"]
-        tb = timed(lambda: ops.attention_bwd(kind, norm, q, k, v, y, dy, stats, ws, nz=nz))
-        fl_f, fl_b = (5 if kind else 4) * K * C, (11 if kind else 10) * K * C
-        out["configs"][name] = {
-            "fwd_us": tf * 1e6, "bwd_us": tb * 1e6, "fwd_px_per_s": px / tf, "fwd_bwd_px_per_s": px / (tf + tb),
-            "fwd_tflops": px * fl_f / tf / 1e12, "bwd_tflops": px * fl_b / tb / 1e12}
-        del q, k, v, dy, y, nz, stats, res
-        torch.cuda.empty_cache()
-    if args.extra == "configs":
-        print(json.dumps(out))
-        return
+    timed = make_timer(torch, flush)
+    out = {"operators_c2_us": {}}
     H, W, C, B, ws, nh = (WORKLOAD[k_] for k_ in ("H", "W", "C", "B", "ws", "nheads"))
     q, k, v = (ca.splitheads(jl.randn(H, W, C, B, generator=gen), nh) for _ in range(3))
     nz = ops.similarity(0, q, k, ws)
@@ -219,60 +396,6 @@ def extra_main(args):
     print(json.dumps(out))
 
 
-
-# --------------------------------------------------------------------------- band split (--extra band)
-def band_main(args):
-    """Not the headline: one image of BASELINE config 5 (1024 x 1024 x 128, ws 21, 8 heads, flash mode) split
-    into bands of columns over the ranks, forward + backward including the halo exchanges (NCCL point to
-    point, the circular wrap between the last and the first rank).  One JSON line from rank 0."""
-    import torch
-    import torch.distributed as dist
-    from __graft_entry__ import load_package
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    ca = load_package()
-    jl, par = ca.jl, ca.parallel
-    H, W, C, B, ws, nh = 1024, 1024, 128, 1, 21, 8
-    plan = par.BandPlan(W, world, ws)
-    start, width = plan.band(rank)
-    gen = torch.Generator(device=dev).manual_seed(rank)
-    q, k, v, dy = (ca.splitheads(jl.randn(H, width, C, B, generator=gen, device=dev), nh) for _ in range(4))
-
-    def step():
-        y, stats, k_ext, v_ext = par.band_attention_fwd(0, q, k, v, ws)
-        return par.band_attention_bwd(0, q, k, v, y, dy, stats, k_ext, v_ext, ws)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    steps, warmup = max(1, min(args.steps, 10)), max(3, min(args.warmup, 5))
-    for _ in range(warmup):
-        step()
-    barrier()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    for a, b in evs:
-        a.record(); step(); b.record()          # 67 MB per tensor and rank at 8 ranks: larger than what stays in L2
-    barrier()
-    total = torch.tensor([sum(a.elapsed_time(b) for a, b in evs) * 1e-3], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(total, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        t = float(total.item()) / steps
-        print(json.dumps({
-            "workload": "one 1024x1024x128 image, ws=21, 8 heads, Dot, flash mode, band split over columns with "
-                        "halo exchange, fwd+bwd", "n_gpus": world, "scaling": "strong", "steps": steps,
-            "ms_per_step": t * 1e3, "px_per_s": H * W * B / t, "band_columns": width, "halo_columns": plan.p}))
-    if world > 1:
-        dist.destroy_process_group()
-
-
 # --------------------------------------------------------------------------- B200 arm
 def main():
     ap = argparse.ArgumentParser()
@@ -281,11 +404,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--extra", nargs="?", const="all", default=None, choices=["all", "configs", "operators", "band"],
-                    help="time the other configurations and/or the stand-alone operators instead of the headline step")
+    ap.add_argument("--extra", nargs="?", const="operators", default=None, choices=["operators"],
+                    help="time the stand-alone operators at the bench shape instead of the headline step")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the other BASELINE configurations and the "
+                    "sharded config-5 runs (they add a few seconds)")
     args = ap.parse_args()
-    if args.extra == "band":
-        return band_main(args)
     if args.extra:
         return extra_main(args)
     if args.impl == "reference":
@@ -445,66 +568,111 @@ def main():
         "stage_us": {k_: v_ * 1e6 for k_, v_ in stage_s.items()},
     }
 
-    # ---- end to end through the public API: every step copies its inputs from pinned host memory,
-    # runs circulant_mh_attention + backward, and copies the loss and the three gradients back.
-    # The three phases run on their own streams, double buffered, so that the copies of
-    # neighbouring steps overlap the compute (a training loop would prefetch the same way).
-    qh, kh, vh, rh = host
-    out_host = [torch.empty_like(qh).pin_memory() for _ in range(3)]
+    # ---- end to end through the public API: every step copies its inputs from pinned host memory (one
+    # staging buffer, one copy), runs circulant_mh_attention + backward, and copies the three gradients and
+    # the loss back (one buffer, one copy).  Copy-in, compute and copy-out run on their own streams, double
+    # buffered, so that the copies of neighbouring steps overlap the compute (a training loop would prefetch
+    # the same way).
+    shape_t = tuple(host[0].shape)                     # torch shape (B, C, W, H) = the Julia (H, W, C, B) bytes
+    n_el = host[0].numel()
+    host_in = torch.empty((4,) + shape_t, dtype=torch.float32).pin_memory()
+    for i_, t_ in enumerate(host):
+        host_in[i_].copy_(t_)
+    host_out = torch.empty(3 * n_el + 1, dtype=torch.float32).pin_memory()
     n_e2e = max(5, min(steps, 30))
-    loss_host = torch.zeros(n_e2e + 3, dtype=torch.float32).pin_memory()
     s_in, s_cmp, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
-    dev_in = [[torch.empty_like(t, device=dev) for t in host] for _ in range(2)]
+    dev_in = [torch.empty_like(host_in, device=dev) for _ in range(2)]
+    dev_out = [torch.empty(3 * n_el + 1, dtype=torch.float32, device=dev) for _ in range(2)]
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_cmp = [torch.cuda.Event() for _ in range(2)]
     ev_out = [torch.cuda.Event() for _ in range(2)]
     keep = [None, None]                 # tensors of a slot stay referenced until its copies have finished
+    host_busy = [0.0]                   # host time spent enqueueing (waits for the device excluded)
+    losses = []
 
     def e2e_step(i):
         slot = i % 2
         ev_out[slot].synchronize()      # the slot's previous outputs have left the device
+        losses.append(float(host_out[-1]))
+        t_h = time.perf_counter()
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_cmp[slot])                    # its previous inputs are no longer read
-            for dst, src in zip(dev_in[slot], host):
-                dst.copy_(src, non_blocking=True)
+            dev_in[slot].copy_(host_in, non_blocking=True)
             ev_in[slot].record(s_in)
         with torch.cuda.stream(s_cmp):
             s_cmp.wait_event(ev_in[slot])
+            s_cmp.wait_event(ev_out[slot])                   # dev_out[slot] has been copied out
             ins = [t.permute(3, 2, 1, 0) for t in dev_in[slot]]
             qd, kd, vd = (t.detach().requires_grad_(True) for t in ins[:3])
             yy, _ = ca.circulant_mh_attention(ca.DotSimilarity(), qd, kd, vd, ws, nheads, return_A=False)
             loss = (yy * ins[3]).sum()
             loss.backward()
-            grads = [jl.colmajor(t.grad).permute(3, 2, 1, 0) for t in (qd, kd, vd)]
+            for j_, t in enumerate((qd, kd, vd)):
+                dev_out[slot][j_ * n_el:(j_ + 1) * n_el].view(shape_t).copy_(jl.colmajor(t.grad).permute(3, 2, 1, 0))
+            dev_out[slot][3 * n_el:].copy_(loss.detach().reshape(1))
             ev_cmp[slot].record(s_cmp)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_cmp[slot])
-            for o, gr in zip(out_host, grads):
-                o.copy_(gr, non_blocking=True)
-            loss_host[i:i + 1].copy_(loss.detach().reshape(1), non_blocking=True)
+            host_out.copy_(dev_out[slot], non_blocking=True)
             ev_out[slot].record(s_out)
-        keep[slot] = (grads, loss, yy, qd, kd, vd)
+        keep[slot] = (yy, qd, kd, vd, loss)
+        host_busy[0] += time.perf_counter() - t_h
 
     for i in range(3):
         e2e_step(i)
     barrier()
+    host_busy[0] = 0.0
     t0 = time.perf_counter()
     for i in range(n_e2e):
         e2e_step(3 + i)
     barrier()
-    assert bool(torch.isfinite(loss_host).all())
-    e2e_t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    e2e_wall = time.perf_counter() - t0
+    losses.append(float(host_out[-1]))
+    assert all(np.isfinite(losses[2:])), "non-finite loss in the end-to-end loop"
+    ops.check_status(dev)
+    e2e_t = torch.tensor([e2e_wall], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_value = px_per_step * n_e2e * world / float(e2e_t.item())
-    nbytes = qh.numel() * 4
+    # the link alone: the same bytes in and out per step, both directions at once, nothing computed
+    def link_step():
+        with torch.cuda.stream(s_in):
+            dev_in[0].copy_(host_in, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            host_out.copy_(dev_out[0], non_blocking=True)
+    for _ in range(3):
+        link_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        link_step()
+    barrier()
+    link_t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(link_t, op=dist.ReduceOp.MAX)
+    link_bound = px_per_step * n_e2e * world / float(link_t.item())
+    nbytes = n_el * 4
     clocks = sampler.stop()
+
+    # ---- the other BASELINE configurations (one GPU) and the sharded config-5 runs (every N)
+    other, sharded = None, {}
+    if not args.no_other_configs:
+        del q, k, v, r, y, stats, D, sws, dq, dk, dv, dev_in, dev_out, keep
+        ops.release_scratch()
+        torch.cuda.empty_cache()
+        timed = make_timer(torch, flush)
+        if world == 1:
+            gen = torch.Generator(device=dev).manual_seed(0)
+            other = {name: time_config(ca, torch, timed, gen, cfg, ffma_tflops) for name, cfg in OTHER_CONFIGS.items()}
+        sharded["units_c5"] = units_c5(ca, torch, dist, dev, world, rank, 2)
+        sharded["band_c5"] = band_c5(ca, torch, dist, dev, world, rank, 3)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cv, cdt, threads = run_cpu(wl, 5, 1)
         cpu_baseline = {"value": cv, "unit": UNIT, "cores": threads, "kind": "port",
-                        "sample": "5 full steps (24576 query pixels each) of the C + OpenMP float32 restatement; "
+                        "sample": "5 full steps (24576 query pixels each) of the C + OpenMP float32 restatement, "
+                                  "work shared as (unit, 256-pixel block) items over all threads; "
                                   "the reference has no CPU path"}
 
     if rank == 0:
@@ -518,8 +686,14 @@ def main():
                        "sharding": "batch x heads units per rank, no collective"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "variants": variants,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 3 * nbytes + 4,
-                    "steps": n_e2e, "timing": "wall clock around the steps, synchronised on both sides, max over ranks; "
-                              "copy-in, compute and copy-out of neighbouring steps overlap on three streams"},
+                    "steps": n_e2e, "link_bound_px_per_s": link_bound, "frac_of_link_bound": e2e_value / link_bound,
+                    "link_gbs_h2d": 4 * nbytes * n_e2e * world / float(link_t.item()) / 1e9,
+                    "host_enqueue_ms_per_step": host_busy[0] / n_e2e * 1e3,
+                    "timing": "wall clock around the steps, synchronised on both sides, max over ranks; one pinned "
+                              "staging buffer and one copy per direction per step; copy-in, compute and copy-out of "
+                              "neighbouring steps overlap on three streams; link_bound = the same copies with "
+                              "nothing computed"},
+            "other_configs": other, **sharded,
             "gpu_launches": int(launches), "clocks": clocks,
         }
         print(json.dumps(line))

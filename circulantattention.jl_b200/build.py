@@ -26,6 +26,17 @@ def _stale():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def _obj_stale(src_path: str, obj: str) -> bool:
+    """An object is rebuilt when its own source, any header of csrc/ or the public headers are newer."""
+    if not os.path.exists(obj):
+        return True
+    t = os.path.getmtime(obj)
+    inc = os.path.join(PKG_DIR, "..", "include")
+    deps = [src_path] + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    deps += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return OUT
@@ -33,11 +44,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     for src in SOURCES:
         obj = os.path.join(CSRC, src[:-3] + ".o")
+        objs.append(obj)
+        if not force and not _obj_stale(os.path.join(CSRC, src), obj):
+            continue
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
-        objs.append(obj)
     for src, p in procs:
         out, _ = p.communicate()
         if verbose and out:

@@ -417,7 +417,12 @@ int ca_attention_bwd_pre(const ca_desc* d, const void* q, const void* k, const v
                          const void* y, const void* dy, const float* stats,
                          const float* nz, const float* dA, float* D, void* stream) {
     Geo g;
-    int rc = make_geo(d, &g, true);
+    if (!d) { set_error("descriptor is NULL"); return CA_ERR_NULL; }
+    ca_desc dd = *d;
+    // the softmax pre-pass without a cotangent on A is D = dy . y per pixel: it looks at no window, so a band
+    // narrower than the window (legal for the band split, whose halos come from the neighbours) is accepted
+    if (dd.normalizer == CA_SOFTMAX && !dA && dd.ws >= 1 && dd.ws % 2 == 1) dd.ws = 1;
+    int rc = make_geo(&dd, &g, true);
     if (rc) return rc;
     if (!dy || !D) { set_error("dy/D is NULL"); return CA_ERR_NULL; }
     if ((rc = no_bf16(g, "ca_attention_bwd_pre"))) return rc;

@@ -17,7 +17,13 @@ def _rev(n):
 
 
 def is_colmajor(t: torch.Tensor) -> bool:
-    return t.permute(_rev(t.ndim)).is_contiguous()
+    """True when the strides are those of a dense column-major array (extent-1 dims may carry any stride)."""
+    expect = 1
+    for n, st in zip(t.shape, t.stride()):
+        if n != 1 and st != expect:
+            return False
+        expect *= n
+    return True
 
 
 def colmajor(t: torch.Tensor) -> torch.Tensor:

@@ -4,6 +4,7 @@ side) and the ctypes calls.  No arithmetic happens here."""
 from __future__ import annotations
 
 import math
+import threading
 from dataclasses import dataclass
 
 import torch
@@ -55,8 +56,35 @@ def meta_of(x: torch.Tensor, ws: int) -> Meta:
     return Meta(tuple(x.shape[:-2]), x.shape[-2], x.shape[-1], int(ws), x.is_complex(), x.dtype == torch.bfloat16)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """Handle (cudaStream_t as an integer) of torch's current stream on the current device."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+class _on_device:
+    """`with _on_device(t.device)`: makes that device current for the C ABI calls inside, without the cost of
+    a device switch when it already is (the common case)."""
+    __slots__ = ("index", "prev")
+
+    def __init__(self, device):
+        self.index = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.index:
+            self.prev = cur
+            torch.cuda.set_device(self.index)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def require_cuda(*ts):
@@ -80,7 +108,7 @@ def structure(spatial, ws, batch, device):
     nb = int(math.prod(batch)) if batch else 1
     rowptr = jl.empty((Np + 1,) + tuple(batch), torch.int32, device)
     colval = jl.empty((Np * K,) + tuple(batch), torch.int32, device)
-    with torch.cuda.device(rowptr.device):
+    with _on_device(rowptr.device):
         check(lib.ca_structure(H, W, len(spatial), ws, nb, ptr(rowptr), ptr(colval), _stream()))
     return rowptr, colval
 
@@ -97,7 +125,7 @@ def similarity(kind, x, y, ws, scale=1.0):
     m = meta_of(x, ws)
     nz = jl.empty((m.Np * m.K, m.units), torch.float32, x.device)
     d = m.desc(similarity=kind, scale=scale)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         ws_buf = _operator_workspace(d, x.device)
         check(lib.ca_similarity(d, ptr(x), ptr(y), ptr(nz), ptr(ws_buf), _stream()))
     return nz
@@ -109,7 +137,7 @@ def similarity_bwd(kind, x, y, ws, dS, scale=1.0):
     m = meta_of(x, ws)
     dx, dy = jl.empty(x.shape, x.dtype, x.device), jl.empty(y.shape, y.dtype, y.device)
     d = m.desc(similarity=kind, scale=scale)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         ws_buf = _operator_workspace(d, x.device)
         check(lib.ca_similarity_bwd(d, ptr(x), ptr(y), ptr(dS), ptr(dx), ptr(dy), ptr(ws_buf), _stream()))
     return dx, dy
@@ -126,7 +154,7 @@ def row_normalize(nz, spatial, ws, normalizer, out=None, want_stats=False):
     m = _nz_meta(spatial, ws, units)
     out = jl.empty(nz.shape, torch.float32, nz.device) if out is None else out
     stats = jl.empty((m.Np, units), torch.float32, nz.device) if want_stats else None
-    with torch.cuda.device(nz.device):
+    with _on_device(nz.device):
         check(lib.ca_row_normalize(m.desc(normalizer=normalizer), ptr(nz), ptr(out), ptr(stats), _stream()))
     return (out, stats) if want_stats else out
 
@@ -136,7 +164,7 @@ def row_normalize_bwd(p, dp, spatial, ws, normalizer):
     units = p.numel() // p.shape[0]
     m = _nz_meta(spatial, ws, units)
     ds = jl.empty(p.shape, torch.float32, p.device)
-    with torch.cuda.device(p.device):
+    with _on_device(p.device):
         check(lib.ca_row_normalize_bwd(m.desc(normalizer=normalizer), ptr(p), ptr(dp), ptr(ds), _stream()))
     return ds
 
@@ -155,7 +183,7 @@ def apply(nz, v, ws, transpose=False, out=None):
     if out is None:
         out = jl.empty(tuple(v.shape[:-1]) + (units,), v.dtype, v.device)
     d = m.desc(units=units)
-    with torch.cuda.device(v.device):
+    with _on_device(v.device):
         ws_buf = _operator_workspace(d, v.device)
         check(lib.ca_apply(d, ptr(nz), ptr(v), ptr(out), int(transpose), int(ua == 1 and units > 1),
                            int(m.units == 1 and units > 1), ptr(ws_buf), _stream()))
@@ -171,7 +199,7 @@ _SCRATCH = {}
 def _scratch(purpose, nbytes, device):
     if not nbytes:
         return None
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream, purpose)
+    key = (device.index, _stream(), purpose)
     buf = _SCRATCH.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
@@ -186,15 +214,20 @@ def release_scratch():
 
 # ------------------------------------------------------------------ device-side failure reporting
 _STATUS = {}
+_REGISTERED = threading.local()
 
 
 def _status_word(device):
-    """Registers (once per device and host thread use) the int32 the kernels flag a timed-out wait in."""
+    """The int32 on `device` in which kernels flag a wait that ran out; registered with the library for
+    the calling host thread (the registration is per thread, so it is redone when the thread last
+    registered another device's word)."""
     w = _STATUS.get(device.index)
     if w is None:
         w = torch.zeros(1, dtype=torch.int32, device=device)
         _STATUS[device.index] = w
-    check(lib.ca_status_word(ptr(w)))
+    if getattr(_REGISTERED, "index", None) != device.index:
+        check(lib.ca_status_word(ptr(w)))
+        _REGISTERED.index = device.index
     return w
 
 
@@ -226,7 +259,7 @@ def attention_fwd(kind, normalizer, q, k, v, ws, want_nz, scale=None, band=None,
     nz = jl.empty((m.Np * m.K, m.units), torch.float32, q.device) if want_nz else None
     stats = jl.empty((m.Np, m.units), torch.float32, q.device)
     nbytes = lib.ca_attention_fwd_workspace(d, int(want_nz))
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         _status_word(q.device)
         if keep_workspace:
             wsb = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
@@ -246,7 +279,7 @@ def attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=None, dA=None,
     dq, dk, dv = (jl.empty(q.shape, q.dtype, q.device) for _ in range(3))
     if dA is not None:
         dA = jl.colmajor(dA)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         _status_word(q.device)
         wsb = _scratch("bwd", lib.ca_attention_bwd_workspace(d), q.device)
         check(lib.ca_attention_bwd(d, ptr(q), ptr(k), ptr(v), ptr(y), ptr(dy), ptr(stats), ptr(nz), ptr(dA),
@@ -260,7 +293,7 @@ def axpby(alpha, x, beta=0.0, y=None):
     x = jl.colmajor(x)
     y = jl.colmajor(y) if y is not None else None
     out = jl.empty(x.shape, torch.float32, x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         check(lib.ca_axpby(x.numel(), float(alpha), ptr(x), float(beta), ptr(y), ptr(out), _stream()))
     return out
 
@@ -281,7 +314,7 @@ def scale_batch(c, nz):
     o1, o2 = max(a1, c1), max(a2, c2)
     nb = max(nz.ndim - 1, c.ndim)
     out = jl.empty((nz.shape[0],) + (o1, o2)[:nb], torch.float32, nz.device)
-    with torch.cuda.device(nz.device):
+    with _on_device(nz.device):
         check(lib.ca_scale_batch(nz.shape[0], o1, o2, ptr(nz), a1, a2, ptr(c), c1, c2, ptr(out), _stream()))
     return out
 
@@ -299,7 +332,7 @@ def dot_batch(x, y=None):
     o1, o2 = max(x1, y1), max(x2, y2)
     nb = max(x.ndim, y.ndim if y is not None else 0) - 1
     out = jl.empty((o1, o2)[:nb] if nb else (1,), torch.float32, x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         check(lib.ca_dot_batch(x.shape[0], o1, o2, ptr(x), x1, x2, ptr(y), y1, y2, ptr(out), _stream()))
     return out
 
@@ -310,7 +343,7 @@ def sum_batch(nz, sum1, sum2):
     b1, b2 = _b12(nz.shape[1:])
     o = (1 if sum1 else b1, 1 if sum2 else b2)[:nz.ndim - 1]
     out = jl.empty((nz.shape[0],) + o, torch.float32, nz.device)
-    with torch.cuda.device(nz.device):
+    with _on_device(nz.device):
         check(lib.ca_sum_batch(nz.shape[0], b1, b2, int(sum1), int(sum2), ptr(nz), ptr(out), _stream()))
     return out
 
@@ -321,7 +354,7 @@ def sum_rows(nz, spatial, ws):
     units = nz.numel() // nz.shape[0]
     m = _nz_meta(spatial, ws, units)
     out = jl.empty((m.Np, 1) + tuple(nz.shape[1:]), torch.float32, nz.device)
-    with torch.cuda.device(nz.device):
+    with _on_device(nz.device):
         check(lib.ca_sum_rows(m.desc(), ptr(nz), ptr(out), _stream()))
     return out
 
@@ -332,7 +365,7 @@ def sum_cols(nz, spatial, ws):
     units = nz.numel() // nz.shape[0]
     m = _nz_meta(spatial, ws, units)
     out = jl.empty((1, m.Np) + tuple(nz.shape[1:]), torch.float32, nz.device)
-    with torch.cuda.device(nz.device):
+    with _on_device(nz.device):
         check(lib.ca_sum_cols(m.desc(), ptr(nz), ptr(out), _stream()))
     return out
 
@@ -350,7 +383,7 @@ def attention_bwd_pre(kind, normalizer, q, k, v, y, dy, stats, ws, scale=None):
     scale = 1.0 / math.sqrt(m.channels) if scale is None else scale
     d = m.desc(similarity=kind, normalizer=normalizer, scale=scale)
     D = jl.empty((m.Np, m.units), torch.float32, q.device)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         check(lib.ca_attention_bwd_pre(d, ptr(q), ptr(k), ptr(v), ptr(y), ptr(dy), ptr(stats), None, None, ptr(D),
                                        _stream()))
     return D
@@ -365,7 +398,7 @@ def attention_bwd_dq(kind, normalizer, q, k, v, dy, stats, D, ws, scale=None, ba
     d = m.desc(similarity=kind, normalizer=normalizer, scale=scale, Wk=Wk, wk_off=wk_off)
     dq = jl.empty(q.shape, q.dtype, q.device)
     wsb = _stage_ws(d, q.device)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         check(lib.ca_attention_bwd_dq(d, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(stats), ptr(D), None, ptr(dq),
                                       ptr(wsb), _stream()))
     return dq
@@ -380,7 +413,7 @@ def attention_bwd_dkdv(kind, normalizer, q, k, v, dy, stats, D, ws, scale=None, 
     d = m.desc(similarity=kind, normalizer=normalizer, scale=scale, Wk=Wk, wk_off=wk_off)
     dk, dv = jl.empty(k.shape, k.dtype, k.device), jl.empty(k.shape, k.dtype, k.device)
     wsb = _stage_ws(d, k.device)
-    with torch.cuda.device(k.device):
+    with _on_device(k.device):
         check(lib.ca_attention_bwd_dkdv(d, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(stats), ptr(D), None, ptr(dk),
                                         ptr(dv), ptr(wsb), _stream()))
     return dk, dv

@@ -9,9 +9,11 @@ single-device package):
 * for images too large for one GPU the slow spatial axis W is cut into bands
   (`BandPlan`).  A rank then needs `p = (ws-1)/2` columns of the key-side
   tensors from its two neighbours `r-1` and `r+1` (mod R: the modulo is the
-  circular wrap of the window); `exchange_halo` does that with point-to-point
-  sends (NCCL over NVLink on GPUs, gloo on CPU ranks) into the rank's own halo
-  buffer, and the kernels run in band mode on the extended slab.
+  circular wrap of the window); `exchange_halos` does that with point-to-point
+  sends (NCCL over NVLink on GPUs, gloo on CPU ranks): all tensors of one
+  exchange travel as one message per neighbour, land in the rank's own staging
+  buffer first, and the kernels run in band mode on the extended slabs, every
+  thread block reading local memory only.
 """
 from __future__ import annotations
 
@@ -85,30 +87,67 @@ def _cview(x: torch.Tensor) -> torch.Tensor:
     return x.permute(tuple(range(x.ndim - 1, -1, -1)))
 
 
-def exchange_halo(x: torch.Tensor, p: int, group=None) -> torch.Tensor:
-    """Extended slab (H, Wb + 2p, ...) of the band-local (H, Wb, ...) tensor: `p` columns
-    from the left neighbour, the band, `p` columns from the right neighbour.  Without an
-    initialised process group (or world size 1) the band is the whole image and the halos are
-    its own wrapped columns."""
-    if x.ndim < 2:
-        raise ValueError("expected a (H, W, ...) tensor")
-    Wb = x.shape[1]
-    if p < 1 or Wb < p:
-        raise ValueError(f"band of {Wb} columns cannot supply a halo of {p}")
-    t = _cview(x)                                            # (..., Wb, H)
-    ext = torch.empty(t.shape[:-2] + (Wb + 2 * p, t.shape[-1]), dtype=t.dtype, device=t.device)
-    ext.narrow(-2, p, Wb).copy_(t)
-    left_halo, right_halo = ext.narrow(-2, 0, p), ext.narrow(-2, p + Wb, p)
+# Staging buffers of the exchange, kept per (direction, size, dtype, device): the halos of all tensors of
+# one exchange travel as ONE message per neighbour, so the buffers are reused step after step.
+_STAGING = {}
+
+
+def _staging(tag, numel, dtype, device):
+    key = (tag, numel, dtype, str(device))
+    buf = _STAGING.get(key)
+    if buf is None:
+        buf = torch.empty(numel, dtype=dtype, device=device)
+        _STAGING[key] = buf
+    return buf
+
+
+def exchange_halos(xs, p: int, group=None):
+    """Extended slabs (H, Wb + 2p, ...) of the band-local (H, Wb, ...) tensors `xs` (same dtype and device):
+    `p` columns from the left neighbour, the band, `p` columns from the right neighbour.
+
+    All tensors of the call share one exchange: their outgoing halos are gathered into one contiguous
+    message per neighbour (two sends and two receives in one grouped point-to-point call, whatever the
+    number of tensors), and the incoming ones are scattered into the slabs.  Without an initialised
+    process group (or world size 1) the band is the whole image and the halos are its own wrapped
+    columns."""
+    xs = list(xs)
+    if not xs:
+        return []
+    ts, exts = [], []
+    for x in xs:
+        if x.ndim < 2:
+            raise ValueError("expected a (H, W, ...) tensor")
+        Wb = x.shape[1]
+        if p < 1 or Wb < p:
+            raise ValueError(f"band of {Wb} columns cannot supply a halo of {p}")
+        if x.dtype != xs[0].dtype or x.device != xs[0].device:
+            raise TypeError("tensors of one exchange must share dtype and device")
+        t = _cview(x)                                        # (..., Wb, H)
+        ext = torch.empty(t.shape[:-2] + (Wb + 2 * p, t.shape[-1]), dtype=t.dtype, device=t.device)
+        ext.narrow(-2, p, Wb).copy_(t)
+        ts.append(t)
+        exts.append(ext)
     world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
     if world == 1:
-        left_halo.copy_(t.narrow(-2, Wb - p, p))
-        right_halo.copy_(t.narrow(-2, 0, p))
+        for t, ext in zip(ts, exts):
+            Wb = t.shape[-2]
+            ext.narrow(-2, 0, p).copy_(t.narrow(-2, Wb - p, p))
+            ext.narrow(-2, p + Wb, p).copy_(t.narrow(-2, 0, p))
     else:
+        dtype, device = ts[0].dtype, ts[0].device
+        sizes = [t.numel() // t.shape[-2] * p for t in ts]
+        total = sum(sizes)
+        to_right, to_left = _staging("to_right", total, dtype, device), _staging("to_left", total, dtype, device)
+        from_left, from_right = _staging("from_left", total, dtype, device), _staging("from_right", total, dtype, device)
+        off = 0
+        for t, n in zip(ts, sizes):
+            Wb = t.shape[-2]
+            shape = t.shape[:-2] + (p, t.shape[-1])
+            to_right[off:off + n].view(shape).copy_(t.narrow(-2, Wb - p, p))   # the right neighbour's left halo
+            to_left[off:off + n].view(shape).copy_(t.narrow(-2, 0, p))         # the left neighbour's right halo
+            off += n
         rank = dist.get_rank(group)
         left, right = (rank - 1) % world, (rank + 1) % world
-        to_right = t.narrow(-2, Wb - p, p).contiguous()      # becomes the right neighbour's left halo
-        to_left = t.narrow(-2, 0, p).contiguous()            # becomes the left neighbour's right halo
-        from_left, from_right = torch.empty_like(to_right), torch.empty_like(to_left)
         peer = lambda r: dist.get_global_rank(group, r) if group is not None else r
         reqs = dist.batch_isend_irecv([
             dist.P2POp(dist.isend, to_right, peer(right), group, tag=0),
@@ -118,31 +157,47 @@ def exchange_halo(x: torch.Tensor, p: int, group=None) -> torch.Tensor:
         ])
         for r in reqs:
             r.wait()
-        left_halo.copy_(from_left)
-        right_halo.copy_(from_right)
-    return ext.permute(tuple(range(ext.ndim - 1, -1, -1)))
+        off = 0
+        for t, ext, n in zip(ts, exts, sizes):
+            Wb = t.shape[-2]
+            shape = t.shape[:-2] + (p, t.shape[-1])
+            ext.narrow(-2, 0, p).copy_(from_left[off:off + n].view(shape))
+            ext.narrow(-2, p + Wb, p).copy_(from_right[off:off + n].view(shape))
+            off += n
+    return [ext.permute(tuple(range(ext.ndim - 1, -1, -1))) for ext in exts]
+
+
+def exchange_halo(x: torch.Tensor, p: int, group=None) -> torch.Tensor:
+    """Extended slab of one tensor (see exchange_halos)."""
+    return exchange_halos([x], p, group)[0]
 
 
 def band_attention_fwd(kind, q, k, v, ws, group=None, normalizer=0):
-    """Forward on this rank's band of head-split (H, Wb, c, units) tensors.
-    Returns (y, stats, k_ext, v_ext); the extended slabs are reused by the backward."""
+    """Forward on this rank's band of head-split (H, Wb, c, units) tensors: one exchange (k and v
+    together), one kernel call.  Returns (y, stats, k_ext, v_ext); the extended slabs are reused by
+    the backward."""
     p = (ws - 1) // 2
-    k_ext, v_ext = exchange_halo(k, p, group), exchange_halo(v, p, group)
+    k_ext, v_ext = exchange_halos([k, v], p, group)
     y, _, stats = ops.attention_fwd(kind, normalizer, q, k_ext, v_ext, ws, False, band=(k_ext.shape[1], p))
     return y, stats, k_ext, v_ext
 
 
 def band_attention_bwd(kind, q, k, v, y, dy, stats, k_ext, v_ext, ws, group=None, normalizer=0):
-    """Backward on this rank's band.  One more exchange: q, dy, stats and D of the
-    neighbouring columns feed the key-owned dk/dv sweep."""
+    """Backward on this rank's band.  One more exchange: q, dy, stats and D of the neighbouring columns
+    (one message per neighbour) feed the key-owned dk/dv sweep.  The dq sweep needs nothing from the
+    neighbours beyond the forward's k and v slabs, so it is queued before the exchange is waited for."""
     p = (ws - 1) // 2
     Wb = q.shape[1]
+    H, units = q.shape[0], q.shape[-1]
     D = ops.attention_bwd_pre(kind, normalizer, q, k, v, y, dy, stats, ws)
     dq = ops.attention_bwd_dq(kind, normalizer, q, k_ext, v_ext, dy, stats, D, ws, band=(Wb + 2 * p, p))
-    H, units = q.shape[0], q.shape[-1]
-    q_ext, dy_ext = exchange_halo(q, p, group), exchange_halo(dy, p, group)
-    stats_ext = exchange_halo(jl.reshape(stats, (H, Wb, units)), p, group)
-    D_ext = exchange_halo(jl.reshape(D, (H, Wb, units)), p, group)
+    if q.dtype == torch.float32:
+        # the two scalar planes ride in the same message as q and dy
+        q_ext, dy_ext, stats_ext, D_ext = exchange_halos(
+            [q, dy, jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group)
+    else:
+        q_ext, dy_ext = exchange_halos([q, dy], p, group)
+        stats_ext, D_ext = exchange_halos([jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group)
     dk, dv = ops.attention_bwd_dkdv(kind, normalizer, q_ext, k, v, dy_ext,
                                     jl.reshape(stats_ext, (H * (Wb + 2 * p), units)),
                                     jl.reshape(D_ext, (H * (Wb + 2 * p), units)), ws, band=(Wb + 2 * p, p))

@@ -78,6 +78,13 @@ def _worker(rank, world, port, W, p, out):
         ext = ca.jl.to_numpy(ca.parallel.exchange_halo(band, p))
         cols = [(c % W) for c in range(start - p, start + width + p)]
         ok = np.array_equal(ext, full[:, cols])
+        # several tensors of different trailing shapes in ONE exchange (one message per neighbour),
+        # twice, so that the reused staging buffers are exercised
+        full2 = np.asfortranarray(-np.arange(4 * W * 5, dtype=np.float32).reshape((4, W, 5), order="F"))
+        band2 = ca.jl.from_numpy(np.asfortranarray(full2[:, start:start + width]), "cpu")
+        for _ in range(2):
+            e1, e2 = ca.parallel.exchange_halos([band, band2], p)
+            ok = ok and np.array_equal(ca.jl.to_numpy(e1), full[:, cols]) and np.array_equal(ca.jl.to_numpy(e2), full2[:, cols])
         out[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
