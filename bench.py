@@ -451,7 +451,7 @@ def main():
     stats_ = jl.empty((m_.Np, m_.units), torch.float32, dev)
     grads_ = [jl.empty(q.shape, q.dtype, dev) for _ in range(3)]
     wsf_ = torch.empty(max(lib.ca_attention_fwd_workspace(d_, 0), 16), dtype=torch.uint8, device=dev)
-    wsb_ = torch.empty(max(lib.ca_attention_bwd_workspace(d_), 16), dtype=torch.uint8, device=dev)
+    wsb_ = torch.empty(max(lib.ca_attention_bwd_workspace(d_, 0), 16), dtype=torch.uint8, device=dev)
     ptr_, check_ = ca.ops.ptr, ca._lib.check
     fwd_args = (d_, ptr_(q), ptr_(k), ptr_(v), ptr_(y_), None, ptr_(stats_), ptr_(wsf_))
     bwd_args = (d_, ptr_(q), ptr_(k), ptr_(v), ptr_(y_), ptr_(r), ptr_(stats_), None, None,

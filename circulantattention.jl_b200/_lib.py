@@ -57,7 +57,7 @@ PROTOTYPES = {
     "ca_attention_fwd": (C.c_int, [_D, _p, _p, _p, _p, _p, _p, _p, _p]),
     "ca_static_scratch_bytes": (C.c_size_t, []),
     "ca_attention_fwd_static": (C.c_int, [_D, _p, _p, _p, _p, _p, _p, _p]),
-    "ca_attention_bwd_workspace": (C.c_size_t, [_D]),
+    "ca_attention_bwd_workspace": (C.c_size_t, [_D, _i32]),
     "ca_attention_bwd": (C.c_int, [_D] + [_p] * 14),
     "ca_attention_bwd_pre": (C.c_int, [_D] + [_p] * 10),
     "ca_attention_bwd_stage_workspace": (C.c_size_t, [_D]),

@@ -315,15 +315,15 @@ static size_t score_bytes(const Geo& g) {
 
 // Attention as a chain of the tiled operators (similarity -> row normaliser -> apply, and the
 // reference's own pullback chain of src/rrules.jl backwards) with the scores in scratch memory.
-// Used where no fused tiled kernel exists: 32 or 64 real channels per unit, and entmax.  The
-// scratch is A-sized, so the chain is taken only while A fits Int32 indexing and 4 GiB.
-static bool composed_path(const ca_desc* d, const Geo& g, bool backward = false) {
+// Used where no fused tiled kernel exists: entmax (forward; backward of wide or 1-D units) and a
+// cotangent on A.  The scratch is A-sized, so the chain is taken only while A fits Int32 indexing and 4 GiB.
+static bool composed_path(const ca_desc* d, const Geo& g, bool backward = false, bool has_dA = false) {
     if (g.bf16 || g.Wk != g.W || !tiled_operator_workspace(g)) return false;
     // 1-D windows are long (the scores of a row do not stay in cache between the operators): the
     // backward of narrow units is faster on the generic kernels, which recompute instead
     if (backward && g.wsw == 1 && g.cr <= 16) return false;
     if ((int64_t)g.Np * g.K > INT32_MAX || score_bytes(g) > ((size_t)4 << 30)) return false;
-    return d->normalizer == CA_ENTMAX15 || g.cr > 16;
+    return d->normalizer == CA_ENTMAX15 || has_dA;
 }
 
 size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {
@@ -390,12 +390,12 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
 
 static size_t d_bytes(const Geo& g) { return (((size_t)g.Npk * g.units * sizeof(float)) + 255) & ~(size_t)255; }
 
-size_t ca_attention_bwd_workspace(const ca_desc* d) {
+size_t ca_attention_bwd_workspace(const ca_desc* d, int32_t with_dA) {
     Geo g;
     if (make_geo(d, &g, false)) return 0;
     // D, then the larger of the two scratch layouts the shape can take (fused tiled kernels; operator chain)
     const size_t fused = tiled_bwd_workspace(g);
-    const size_t chain = composed_path(d, g, true) ? 2 * score_bytes(g) + tiled_operator_workspace(g) : 0;
+    const size_t chain = composed_path(d, g, true, with_dA != 0) ? 2 * score_bytes(g) + tiled_operator_workspace(g) : 0;
     return d_bytes(g) + (fused > chain ? fused : chain);
 }
 
@@ -517,7 +517,7 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
                                         (float*)dv, (char*)workspace + d_bytes(g), as_stream(stream));
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
-    if (composed_path(d, g, true)) {
+    if (composed_path(d, g, true, dA != nullptr)) {
         // the pullback chain of src/rrules.jl:42-72 on the tiled operators:
         //   P (saved, or recomputed from q, k) ; dv = P^T dy ; dP = Re(dy . conj(v)) on the window (+ dA) ;
         //   dS = normaliser pullback ; (dq, dk) = similarity pullback

@@ -69,6 +69,14 @@ __device__ __forceinline__ float hsum2(u64 v) {
     return a + b;
 }
 
+// Sum of a per-lane partial over the NS lanes that share a pixel (NS = 1: nothing to do).
+template <int NS>
+__device__ __forceinline__ float lane_sum(float x) {
+#pragma unroll
+    for (int m = 1; m < NS; m <<= 1) x += __shfl_xor_sync(0xffffffffu, x, m);
+    return x;
+}
+
 struct TileArgs {
     Geo g;
     float scale;
@@ -357,23 +365,28 @@ __device__ __forceinline__ void store_centre(float* dst, const Geo& g, int u, in
 // of the chunk reveals; with O(1) scores that happens almost never after the
 // first key.  2^-kHeadroom only rescales p, l and acc together; it cancels in y.
 constexpr float kHeadroom = 12.f;
-template <int DC, bool DIST, int MASK, bool EXACT, int NQ>
+// NS lanes share a pixel (units of 16*NS real channels): every lane holds one 16-channel slab of q and
+// of the accumulator, scores are the lane sums of the per-slab partial dot products, and the terms that
+// enter a score once (the running reference, in nm2) sit on slab 0 only.
+template <int DC, bool DIST, int MASK, bool EXACT, int NQ, int NS = 1>
 __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[NQ][8],
-                                          u64 (&acc)[NQ][8], u64 (&nm2)[NQ], float (&l)[NQ], const float (&bq)[NQ]) {
+                                          u64 (&acc)[NQ][8], u64 (&nm2)[NQ], float (&l)[NQ], const float (&bq)[NQ],
+                                          int slab = 0) {
+    constexpr int RB = kRowBytes * NS;
     for (int c0 = 0; c0 < ws; c0 += DC) {
-        const uint32_t cb = rowbase + c0 * kRowBytes;
+        const uint32_t cb = rowbase + c0 * RB;
         float sc[NQ][DC];
         // one vector ahead: the next key (or the first v) is requested before this key's FMAs
         u64 nxt[8];
-        lds_vec16(cb, 0, nxt);
+        lds_slab16<NS>(cb, 0, slab, nxt);
 #pragma unroll
         for (int t = 0; t < DC; ++t) {
             if (EXACT || c0 + t < ws) {
                 u64 k2[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) k2[i] = nxt[i];
-                if (t + 1 < DC && (EXACT || c0 + t + 1 < ws)) lds_vec16(cb + (t + 1) * kRowBytes, 0, nxt);
-                else lds_vec16(cb, 1, nxt);
+                if (t + 1 < DC && (EXACT || c0 + t + 1 < ws)) lds_slab16<NS>(cb + (t + 1) * RB, 0, slab, nxt);
+                else lds_slab16<NS>(cb, 1, slab, nxt);
                 float bk = 0.f;
                 if (DIST) {
                     u64 n = zero2();
@@ -394,7 +407,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
 #pragma unroll
                         for (int r = 0; r < NQ; ++r) sa[r] = fma2(q[r][i], k2[i], sa[r]);
 #pragma unroll
-                    for (int r = 0; r < NQ; ++r) sc[r][t] = hsum2(sa[r]);
+                    for (int r = 0; r < NQ; ++r) sc[r][t] = lane_sum<NS>(hsum2(sa[r]));
                 } else {
 #pragma unroll
                     for (int r = 0; r < NQ; ++r)
@@ -403,7 +416,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                             if (DIST) sa = add2(sa, pack2(bq[r] + bk, 0.f));
 #pragma unroll
                             for (int i = 0; i < 8; ++i) sa = fma2(q[r][i], k2[i], sa);
-                            sc[r][t] = hsum2(sa);
+                            sc[r][t] = lane_sum<NS>(hsum2(sa));       // rm is warp-uniform: all lanes shuffle
                         } else {
                             sc[r][t] = -INFINITY;
                         }
@@ -430,7 +443,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                     const float corr = fast_exp2(-cm);
                     float nm, zero;
                     unpack2(nm2[r], nm, zero);
-                    nm2[r] = pack2(nm - cm, 0.f);
+                    nm2[r] = pack2(nm - (NS == 1 || slab == 0 ? cm : 0.f), 0.f);
                     l[r] *= corr;
                     const u64 c2 = pack2(corr, corr);
 #pragma unroll
@@ -446,7 +459,7 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                 u64 v2[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v2[i] = nxt[i];
-                if (t + 1 < DC && (EXACT || c0 + t + 1 < ws)) lds_vec16(cb + (t + 1) * kRowBytes, 1, nxt);
+                if (t + 1 < DC && (EXACT || c0 + t + 1 < ws)) lds_slab16<NS>(cb + (t + 1) * RB, 1, slab, nxt);
 #pragma unroll
                 for (int r = 0; r < NQ; ++r)
                     if (CA_ON(r)) {
@@ -463,11 +476,11 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
 
 // First score of each centre pixel that starts in this stage: the reference
 // point of its running maximum.
-template <bool DIST, int NQ>
+template <bool DIST, int NQ, int NS = 1>
 __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float sl2, const u64 (&q)[NQ][8],
-                                             u64 (&nm2)[NQ], const float (&bq)[NQ]) {
+                                             u64 (&nm2)[NQ], const float (&bq)[NQ], int slab = 0) {
     u64 k2[8];
-    lds_vec16(rowbase, 0, k2);
+    lds_slab16<NS>(rowbase, 0, slab, k2);
     float bk = 0.f;
     if (DIST) {
         u64 n = zero2();
@@ -481,7 +494,8 @@ __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float s
             u64 sa = zero2();
 #pragma unroll
             for (int i = 0; i < 8; ++i) sa = fma2(q[r][i], k2[i], sa);
-            nm2[r] = pack2(-(hsum2(sa) + (DIST ? bq[r] + bk : 0.f)) - kHeadroom, 0.f);
+            const float s0 = lane_sum<NS>(hsum2(sa) + (DIST ? bq[r] + bk : 0.f));     // init is warp-uniform
+            nm2[r] = pack2((NS == 1 || slab == 0) ? -s0 - kHeadroom : 0.f, 0.f);
         }
 }
 
@@ -489,20 +503,25 @@ __device__ __forceinline__ void fwd_init_max(uint32_t rowbase, int init, float s
     if ((mask) == (FULL)) { constexpr int MK = (FULL); CALL; }      \
     else { constexpr int MK = 0; CALL; }
 
-template <int DC, bool DIST, int CPE, bool EXACT, int NQ>
+// NCRT = real channels per unit the kernel is compiled for: 16 (also runs 8-channel units, zero-extended),
+// 32 or 64 (NS = 2 or 4 lanes per pixel, one 16-channel slab each; launched without a stage split).
+template <int DC, bool DIST, int CPE, bool EXACT, int NQ, int NCRT = 16>
 __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) fwd_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                            const __grid_constant__ CUtensorMap msc) {
+    constexpr int NS = NCRT <= 16 ? 1 : NCRT / 16;
+    constexpr int RB = kRowBytes * NS;
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
     const int NSTAGES = g.wsw + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = a.scale * kLog2e;
     CA_PIPE_PROLOGUE(false)
-    const int lr = lt, h = h0 + lr;
+    const int slab = NS == 1 ? 0 : (lt % NS);
+    const int lr = NS == 1 ? lt : (lt >> 5) * (32 / NS) + (lt & 31) / NS, h = h0 + lr;
     const bool active = h < g.H;
 
     u64 q[NQ][8], acc[NQ][8];
-    load_centre<CPE, NQ>(a.c0, g, u, h, w0, active, sl2, q);
+    load_centre<CPE, NQ, NCRT>(a.c0, g, u, h, w0, active, sl2, q, 16 * slab);
     u64 nm2[NQ];
     float l[NQ], bq[NQ];
 #pragma unroll
@@ -522,11 +541,11 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) fwd_tiled_kernel(TileA
 
     CA_PIPE_LOOP({
         const int mask = stage_mask<NQ>(s, radius_w(g));
-        const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes;
+        const uint32_t rowbase = smem_u32(pipe.vec(buf)) + (lr + a.roff) * RB;
         // pixels whose first stage (of this part) is s
         const int init = (s == s_begin) ? mask : (mask & ~stage_mask<NQ>(s - 1, radius_w(g)));
-        if (init) fwd_init_max<DIST, NQ>(rowbase, init, sl2, q, nm2, bq);
-        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (fwd_stage<DC, DIST, MK, EXACT, NQ>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq)));
+        if (init) fwd_init_max<DIST, NQ, NS>(rowbase, init, sl2, q, nm2, bq, slab);
+        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (fwd_stage<DC, DIST, MK, EXACT, NQ, NS>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq, slab)));
     })
 
     float nm[NQ];
@@ -570,20 +589,33 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) fwd_tiled_kernel(TileA
             }
         }
     }
-    CA_BF_DISPATCH(
-        _Pragma("unroll")
+    if (NS == 1) {
+        CA_BF_DISPATCH(
+            _Pragma("unroll")
+            for (int r = 0; r < NQ; ++r) {
+                const float inv = 1.f / l[r] + ca_poison;
+                _Pragma("unroll")
+                for (int i = 0; i < 8; ++i) {
+                    float x, y;
+                    unpack2(acc[r][i], x, y);
+                    store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x * inv, y * inv);
+                }
+            })
+    } else {
+#pragma unroll
         for (int r = 0; r < NQ; ++r) {
             const float inv = 1.f / l[r] + ca_poison;
-            _Pragma("unroll")
+#pragma unroll
             for (int i = 0; i < 8; ++i) {
                 float x, y;
                 unpack2(acc[r][i], x, y);
-                store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x * inv, y * inv);
+                store_centre<CPE, NCRT>(a.o0, g, u, h, w0, active, r, i, x * inv, y * inv, 16 * slab);
             }
-        })
+        }
+    }
 #pragma unroll
     for (int r = 0; r < NQ; ++r)
-        if (a.ostats && active && w0 + r < g.W)
+        if (a.ostats && active && slab == 0 && w0 + r < g.W)
             a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = (log2f(l[r]) - nm[r]) * kLn2 + ca_poison;
 }
 
@@ -976,29 +1008,29 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
 // =====================================================================
 // MODE 0: softmax, P = 2^chain.  MODE 1: 1.5-entmax, g = max(chain, 0) with the chain = s/2 - tau, dS = g*(dP - D).
 // MODE 2: the entmax pre-pass: only num += g*dP and den += g (in aux and sumds), D = num/den.
-template <bool DIST, int MASK, int NQ, int MODE>
+template <bool DIST, int MASK, int NQ, int MODE, int NS = 1>
 __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[NQ][8],
                                          const u64 (&dy)[NQ][8], u64 (&dq)[NQ][8], const u64 (&nL2)[NQ],
                                          const u64 (&nD2)[NQ], const float (&bq)[NQ], float (&sumds)[NQ],
-                                         float (&aux)[NQ]) {
+                                         float (&aux)[NQ], int slab = 0) {
 #pragma unroll 1
     for (int di = 0; di < ws; ++di) {
-        const uint32_t a0 = rowbase + di * kRowBytes;
+        const uint32_t a0 = rowbase + di * (kRowBytes * NS);
         float dp[NQ];
         {
             u64 v2[8];
-            lds_vec16(a0, 1, v2);
+            lds_slab16<NS>(a0, 1, slab, v2);
 #pragma unroll
             for (int r = 0; r < NQ; ++r)
                 if (CA_ON(r)) {
                     u64 t = nD2[r];                               // (-D, 0)
 #pragma unroll
                     for (int i = 0; i < 8; ++i) t = fma2(dy[r][i], v2[i], t);
-                    dp[r] = hsum2(t);
+                    dp[r] = lane_sum<NS>(hsum2(t));              // -D sits on slab 0 only; rm is warp-uniform
                 }
         }
         u64 k2[8];
-        lds_vec16(a0, 0, k2);
+        lds_slab16<NS>(a0, 0, slab, k2);
         float bk = 0.f;
         if (DIST) {
             u64 n = zero2();
@@ -1013,12 +1045,13 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
                 if (DIST) t = add2(t, pack2(bq[r] + bk, 0.f));
 #pragma unroll
                 for (int i = 0; i < 8; ++i) t = fma2(q[r][i], k2[i], t);
+                const float chain = lane_sum<NS>(hsum2(t));
                 if (MODE == 2) {
-                    const float gg = fmaxf(hsum2(t), 0.f);
+                    const float gg = fmaxf(chain, 0.f);
                     aux[r] = fmaf(gg, dp[r], aux[r]);
                     sumds[r] += gg;
                 } else {
-                    const float ds = (MODE == 0 ? fast_exp2(hsum2(t)) : fmaxf(hsum2(t), 0.f)) * dp[r];
+                    const float ds = (MODE == 0 ? fast_exp2(chain) : fmaxf(chain, 0.f)) * dp[r];
                     if (DIST) sumds[r] += ds;
                     const u64 d2 = pack2(ds, ds);
 #pragma unroll
@@ -1028,26 +1061,28 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
     }
 }
 
-template <bool DIST, int CPE, int NQ, int MODE>
+template <bool DIST, int CPE, int NQ, int MODE, int NCRT = 16>
 __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                           const __grid_constant__ CUtensorMap msc) {
+    constexpr int NS = NCRT <= 16 ? 1 : NCRT / 16;
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
     const int NSTAGES = g.wsw + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = MODE ? 0.5f * a.scale : a.scale * kLog2e;     // entmax: the chain is s/2 - tau
     CA_PIPE_PROLOGUE(false)
-    const int lr = lt, h = h0 + lr;
+    const int slab = NS == 1 ? 0 : (lt % NS);
+    const int lr = NS == 1 ? lt : (lt >> 5) * (32 / NS) + (lt & 31) / NS, h = h0 + lr;
     const bool active = h < g.H;
 
     u64 q[NQ][8], dy[NQ][8], dq[NQ][8];
-    load_centre<CPE, NQ>(a.c0, g, u, h, w0, active, sl2, q);
-    load_centre<CPE, NQ>(a.c1, g, u, h, w0, active, 1.f, dy);
+    load_centre<CPE, NQ, NCRT>(a.c0, g, u, h, w0, active, sl2, q, 16 * slab);
+    load_centre<CPE, NQ, NCRT>(a.c1, g, u, h, w0, active, 1.f, dy, 16 * slab);
     u64 nL2[NQ], nD2[NQ];
     float bq[NQ], sumds[NQ], aux[NQ];
 #pragma unroll
     for (int r = 0; r < NQ; ++r) {
-        const bool ok = active && (w0 + r < g.W);
+        const bool ok = active && (w0 + r < g.W) && slab == 0;       // row scalars enter the lane sums once
         const int64_t o = (int64_t)u * g.Np + h + g.H * (w0 + r);
         nL2[r] = pack2(ok ? -__ldg(a.cs0 + o) * (MODE ? 1.f : kLog2e) : 0.f, 0.f);
         nD2[r] = pack2((ok && MODE != 2) ? -__ldg(a.cs1 + o) : 0.f, 0.f);
@@ -1066,15 +1101,15 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
 
     CA_PIPE_LOOP({
         const int mask = stage_mask<NQ>(s, radius_w(g));
-        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dq_stage<DIST, MK, NQ, MODE>(smem_u32(pipe.vec(buf)) + (lr + a.roff) * kRowBytes, g.ws, mask,
-                                                     sl2, q, dy, dq, nL2, nD2, bq, sumds, aux)));
+        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dq_stage<DIST, MK, NQ, MODE, NS>(smem_u32(pipe.vec(buf)) + (lr + a.roff) * (kRowBytes * NS), g.ws, mask,
+                                                     sl2, q, dy, dq, nL2, nD2, bq, sumds, aux, slab)));
     })
 
     if (MODE == 2) {
         // pre-pass of the entmax pullback: D = sum g*dP / sum g per query row (launched without a stage split)
 #pragma unroll
         for (int r = 0; r < NQ; ++r)
-            if (active && w0 + r < g.W)
+            if (active && slab == 0 && w0 + r < g.W)
                 a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = (sumds[r] > 0.f ? aux[r] / sumds[r] : 0.f) + ca_poison;
         return;
     }
@@ -1105,36 +1140,52 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
     }
     // dq = scale * (sum ds*k - [distance] sum(ds) * q);  q registers hold q*scale*log2(e) (entmax: q*scale/2)
     const float qfac = MODE ? 2.f : kLn2;
-    CA_BF_DISPATCH(
-        _Pragma("unroll")
-        for (int r = 0; r < NQ; ++r) {
+    if (NS == 1) {
+        CA_BF_DISPATCH(
             _Pragma("unroll")
+            for (int r = 0; r < NQ; ++r) {
+                _Pragma("unroll")
+                for (int i = 0; i < 8; ++i) {
+                    float x, y, qx, qy;
+                    unpack2(dq[r][i], x, y);
+                    unpack2(q[r][i], qx, qy);
+                    x = a.scale * x - (DIST ? sumds[r] * qx * qfac : 0.f) + ca_poison;
+                    y = a.scale * y - (DIST ? sumds[r] * qy * qfac : 0.f) + ca_poison;
+                    store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
+                }
+            })
+    } else {
+#pragma unroll
+        for (int r = 0; r < NQ; ++r) {
+#pragma unroll
             for (int i = 0; i < 8; ++i) {
                 float x, y, qx, qy;
                 unpack2(dq[r][i], x, y);
                 unpack2(q[r][i], qx, qy);
                 x = a.scale * x - (DIST ? sumds[r] * qx * qfac : 0.f) + ca_poison;
                 y = a.scale * y - (DIST ? sumds[r] * qy * qfac : 0.f) + ca_poison;
-                store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
+                store_centre<CPE, NCRT>(a.o0, g, u, h, w0, active, r, i, x, y, 16 * slab);
             }
-        })
+        }
+    }
 }
 
 // =====================================================================
 // Backward, key-owned: dk and dv of three key pixels per thread.  The stage
 // rows carry (q | dy) of the query pixels plus their L and D.
 // =====================================================================
-template <bool DIST, int MASK, int NQ, bool ENT>
+template <bool DIST, int MASK, int NQ, bool ENT, int NS = 1>
 __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const float* Db, int row0, int ws, int rm,
                                            float sl2, const u64 (&k)[NQ][8], const u64 (&v)[NQ][8], u64 (&dk)[NQ][8],
-                                           u64 (&dv)[NQ][8], const float (&bk)[NQ], float (&sumds)[NQ]) {
+                                           u64 (&dv)[NQ][8], const float (&bk)[NQ], float (&sumds)[NQ], int slab = 0) {
 #pragma unroll 1
     for (int di = 0; di < ws; ++di) {
         const int row = row0 + di;
-        const uint32_t a0 = base + row * kRowBytes;
-        const float nLj = -Lb[row], nDj = -Db[row];
+        const uint32_t a0 = base + row * (kRowBytes * NS);
+        // the row scalars enter the lane sums once: on slab 0
+        const float nLj = (NS == 1 || slab == 0) ? -Lb[row] : 0.f, nDj = (NS == 1 || slab == 0) ? -Db[row] : 0.f;
         u64 y2[8];
-        lds_vec16(a0, 1, y2);
+        lds_slab16<NS>(a0, 1, slab, y2);
         float dp[NQ];
 #pragma unroll
         for (int r = 0; r < NQ; ++r)
@@ -1142,10 +1193,10 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
                 u64 t = pack2(nDj, 0.f);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) t = fma2(v[r][i], y2[i], t);
-                dp[r] = hsum2(t);
+                dp[r] = lane_sum<NS>(hsum2(t));
             }
         u64 q2[8];
-        lds_vec16(a0, 0, q2);
+        lds_slab16<NS>(a0, 0, slab, q2);
         float bqj = 0.f;
         if (DIST) {
             u64 n = zero2();
@@ -1159,12 +1210,13 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
                 u64 t = pack2(DIST ? nLj + bk[r] + bqj : nLj, 0.f);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) t = fma2(k[r][i], q2[i], t);
+                const float chain = lane_sum<NS>(hsum2(t));
                 float P, ds;
                 if (!ENT) {
-                    P = fast_exp2(hsum2(t));
+                    P = fast_exp2(chain);
                     ds = P * dp[r];
                 } else {                                     // g = max(s/2 - tau, 0): P = g^2, dS = g*(dP - D)
-                    const float gg = fmaxf(hsum2(t), 0.f);
+                    const float gg = fmaxf(chain, 0.f);
                     P = gg * gg;
                     ds = gg * dp[r];
                 }
@@ -1179,21 +1231,23 @@ __device__ __forceinline__ void dkdv_stage(uint32_t base, const float* Lb, const
     }
 }
 
-template <bool DIST, int CPE, int NQ, bool ENT>
+template <bool DIST, int CPE, int NQ, bool ENT, int NCRT = 16>
 __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(TileArgs a, const __grid_constant__ CUtensorMap mv,
                                                             const __grid_constant__ CUtensorMap msc) {
+    constexpr int NS = NCRT <= 16 ? 1 : NCRT / 16;
     const Geo& g = a.g;
     const int ROWS = a.TH + 2 * (g.p + a.roff);
     const int NSTAGES = g.wsw + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = ENT ? 0.5f * a.scale : a.scale * kLog2e;      // entmax: the chain is s/2 - tau
     CA_PIPE_PROLOGUE(true)
-    const int lr = lt, h = h0 + lr;
+    const int slab = NS == 1 ? 0 : (lt % NS);
+    const int lr = NS == 1 ? lt : (lt >> 5) * (32 / NS) + (lt & 31) / NS, h = h0 + lr;
     const bool active = h < g.H;
 
     u64 k[NQ][8], v[NQ][8], dk[NQ][8], dv[NQ][8];
-    load_centre<CPE, NQ>(a.c0, g, u, h, w0, active, sl2, k);
-    load_centre<CPE, NQ>(a.c1, g, u, h, w0, active, 1.f, v);
+    load_centre<CPE, NQ, NCRT>(a.c0, g, u, h, w0, active, sl2, k, 16 * slab);
+    load_centre<CPE, NQ, NCRT>(a.c1, g, u, h, w0, active, 1.f, v, 16 * slab);
     float bk[NQ], sumds[NQ];
 #pragma unroll
     for (int r = 0; r < NQ; ++r) {
@@ -1214,8 +1268,8 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
 
     CA_PIPE_LOOP({
         const int mask = stage_mask<NQ>(s, radius_w(g));
-        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dkdv_stage<DIST, MK, NQ, ENT>(smem_u32(pipe.vec(buf)), pipe.sc0(buf), pipe.sc1(buf),
-                                                      lr + a.roff, g.ws, mask, sl2, k, v, dk, dv, bk, sumds)));
+        CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dkdv_stage<DIST, MK, NQ, ENT, NS>(smem_u32(pipe.vec(buf)), pipe.sc0(buf), pipe.sc1(buf),
+                                                      lr + a.roff, g.ws, mask, sl2, k, v, dk, dv, bk, sumds, slab)));
     })
 
     if (a.nsplit == 2) {
@@ -1249,10 +1303,26 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
         }
     }
     // dk = scale * (sum ds*q - [distance] sum(ds) * k);  k registers hold k*scale*log2(e)
-    CA_BF_DISPATCH(
-        _Pragma("unroll")
-        for (int r = 0; r < NQ; ++r) {
+    if (NS == 1) {
+        CA_BF_DISPATCH(
             _Pragma("unroll")
+            for (int r = 0; r < NQ; ++r) {
+                _Pragma("unroll")
+                for (int i = 0; i < 8; ++i) {
+                    float x, y, kx, ky, vx, vy;
+                    unpack2(dk[r][i], x, y);
+                    unpack2(k[r][i], kx, ky);
+                    unpack2(dv[r][i], vx, vy);
+                    x = a.scale * x - (DIST ? sumds[r] * kx * (ENT ? 2.f : kLn2) : 0.f) + ca_poison;
+                    y = a.scale * y - (DIST ? sumds[r] * ky * (ENT ? 2.f : kLn2) : 0.f) + ca_poison;
+                    store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
+                    store_centre<CPE, NCRV, BF>(a.o1, g, u, h, w0, active, r, i, vx + ca_poison, vy + ca_poison);
+                }
+            })
+    } else {
+#pragma unroll
+        for (int r = 0; r < NQ; ++r) {
+#pragma unroll
             for (int i = 0; i < 8; ++i) {
                 float x, y, kx, ky, vx, vy;
                 unpack2(dk[r][i], x, y);
@@ -1260,10 +1330,11 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dkdv_tiled_kernel(Tile
                 unpack2(dv[r][i], vx, vy);
                 x = a.scale * x - (DIST ? sumds[r] * kx * (ENT ? 2.f : kLn2) : 0.f) + ca_poison;
                 y = a.scale * y - (DIST ? sumds[r] * ky * (ENT ? 2.f : kLn2) : 0.f) + ca_poison;
-                store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
-                store_centre<CPE, NCRV, BF>(a.o1, g, u, h, w0, active, r, i, vx + ca_poison, vy + ca_poison);
+                store_centre<CPE, NCRT>(a.o0, g, u, h, w0, active, r, i, x, y, 16 * slab);
+                store_centre<CPE, NCRT>(a.o1, g, u, h, w0, active, r, i, vx + ca_poison, vy + ca_poison, 16 * slab);
             }
-        })
+        }
+    }
 }
 
 // =====================================================================
@@ -1356,7 +1427,7 @@ __device__ __forceinline__ void pack_body(const PackArgs& a) {
         if (a.Din) {
             D = __ldg(a.Din + so);
         } else {
-            constexpr int NC = NCR < 16 ? NCR : 16;             // planes exist for one-slab units only
+            constexpr int NC = NCR;                             // D = dy . y over all real channels of the unit
             float dyv[NC], yv[NC];
 #pragma unroll
             for (int cc = 0; cc < NC; ++cc) {
@@ -1401,9 +1472,10 @@ Padded padded_of(const Geo& g) {
 }
 
 bool tiled_shape_ok(const Geo& g) {
-    // 16 real channels per unit, or 8 zero-extended to 16 (half of the FMAs are then spent on zeros)
-    return (g.cr == 16 || g.cr == 8) && (g.wsw == g.ws || g.wsw == 1) && g.ws >= 3 && g.H >= 16 &&
-           g.ws <= (g.wsw == 1 ? 127 : 63);
+    // 16 real channels per unit, 8 zero-extended to 16 (half of the FMAs are then spent on zeros), or 32 / 64
+    // (2 / 4 lanes per pixel; Float32 storage only)
+    const bool chan = g.cr == 16 || g.cr == 8 || ((g.cr == 32 || g.cr == 64) && !g.bf16);
+    return chan && (g.wsw == g.ws || g.wsw == 1) && g.ws >= 3 && g.H >= 16 && g.ws <= (g.wsw == 1 ? 127 : 63);
 }
 
 // The stand-alone operator kernels also take 8 (zero-extended), 32 or 64 real channels per unit
@@ -1458,7 +1530,6 @@ int launch_pack(const PackArgs& a, cudaStream_t st) {
     const int cr = a.g.cr;
     // beyond the grid limits (very long folded 1-D signals, very many units) the generic kernels run
     if (grid.y > 65535u || grid.z > 65535u) return CA_ERR_UNSUPPORTED;
-    if (a.planes && cr > 16) { set_error("scalar planes are packed for one-slab units only"); return CA_ERR_UNSUPPORTED; }
 #define CA_PACK(CPEV)                                                        \
     do {                                                                     \
         if (cr == 8) pack_kernel<CPEV, 8><<<grid, 128, 0, st>>>(a);          \
@@ -1533,6 +1604,7 @@ int prepare(const Geo& g, const Padded& P, int nq, int xch_floats, const char* e
     const size_t xch = (size_t)xch_floats * 32 * warps * sizeof(float);
     if (nsplit == 2 && xch > smem) smem = xch;
     L->smem = smem + 1024;
+    if (L->smem > 220 * 1024) return CA_ERR_UNSUPPORTED;     // window too large for the stage ring: generic kernels
     const uint64_t dims[4] = {(uint64_t)rf, (uint64_t)P.Hp, (uint64_t)g.Wk, (uint64_t)g.units};
     const uint64_t strides[3] = {(uint64_t)rb, (uint64_t)P.Hp * rb, (uint64_t)P.Hp * rb * g.Wk};
     const uint32_t box[4] = {(uint32_t)rf, (uint32_t)ROWS, 1, 1};
@@ -1577,14 +1649,14 @@ int set_smem(K kernel, size_t bytes) {
         }                                                                             \
     } while (0)
 
-#define CA_DIST_CPE_NQ(KERNEL_T, dist, cpe, NQV, XV, L, st)                           \
+#define CA_DIST_CPE_NQ(KERNEL_T, dist, cpe, NQV, XV, NCRV_, L, st)                    \
     do {                                                                              \
         if ((cpe) == 1) {                                                             \
-            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 1, NQV, XV>), L, st);           \
-            else CA_LAUNCH_TILED((KERNEL_T<false, 1, NQV, XV>), L, st);               \
+            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 1, NQV, XV, NCRV_>), L, st);    \
+            else CA_LAUNCH_TILED((KERNEL_T<false, 1, NQV, XV, NCRV_>), L, st);        \
         } else {                                                                      \
-            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 2, NQV, XV>), L, st);           \
-            else CA_LAUNCH_TILED((KERNEL_T<false, 2, NQV, XV>), L, st);               \
+            if (dist) CA_LAUNCH_TILED((KERNEL_T<true, 2, NQV, XV, NCRV_>), L, st);    \
+            else CA_LAUNCH_TILED((KERNEL_T<false, 2, NQV, XV, NCRV_>), L, st);        \
         }                                                                             \
     } while (0)
 
@@ -1602,14 +1674,20 @@ int pick_nq(const Geo& g, int wide, int narrow, const char* env) {
 int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q, const float* dy, const float* stats,
            const float* D, const float* kv, float* dq, cudaStream_t st, int mode = 0, float* Dout = nullptr) {
     Launch L{};
-    const int nq = mode ? 4 : pick_nq(g, 4, 2, "CIRCATT_DQ_NQ");
-    int rc = prepare(g, P, nq, 17 * nq, "CIRCATT_DQ_WARPS", kv, nullptr, &L, mode == 0);
+    const int ns = slabs_of(g);
+    if (ns > 1 && mode) return CA_ERR_UNSUPPORTED;             // the entmax variants exist for one-slab units
+    const int nq = mode ? 4 : (ns > 1 ? (g.ws <= 9 ? 2 : 4) : pick_nq(g, 4, 2, "CIRCATT_DQ_NQ"));
+    int rc = prepare(g, P, nq, 17 * nq, "CIRCATT_DQ_WARPS", kv, nullptr, &L, mode == 0 && ns == 1, 4, ns);
     if (rc) return rc;
     L.a.scale = scale; L.a.c0 = q; L.a.c1 = dy; L.a.cs0 = stats; L.a.cs1 = D; L.a.o0 = dq; L.a.ostats = Dout;
-    if (mode == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 2, L, st);
-    else if (mode == 1) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 1, L, st);
-    else if (nq == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 2, 0, L, st);
-    else CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 0, L, st);
+    if (ns == 2 && nq == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 2, 0, 32, L, st);
+    else if (ns == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 0, 32, L, st);
+    else if (ns == 4 && nq == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 2, 0, 64, L, st);
+    else if (ns == 4) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 0, 64, L, st);
+    else if (mode == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 2, 16, L, st);
+    else if (mode == 1) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 1, 16, L, st);
+    else if (nq == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 2, 0, 16, L, st);
+    else CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 0, 16, L, st);
     CA_CHECK_LAUNCH("tiled dq kernel");
     return CA_OK;
 }
@@ -1617,12 +1695,16 @@ int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q,
 int run_dkdv(const Geo& g, const Padded& P, float scale, int dist, const float* k, const float* v, const float* qdy,
              const float* planes, float* dk, float* dv, cudaStream_t st, bool entmax = false) {
     Launch L{};
+    const int ns = slabs_of(g);
+    if (ns > 1 && entmax) return CA_ERR_UNSUPPORTED;
     const int nq = 3;
-    int rc = prepare(g, P, nq, 33 * nq, "CIRCATT_DKDV_WARPS", qdy, planes, &L);
+    int rc = prepare(g, P, nq, 33 * nq, "CIRCATT_DKDV_WARPS", qdy, planes, &L, ns == 1, 4, ns);
     if (rc) return rc;
     L.a.scale = scale; L.a.c0 = k; L.a.c1 = v; L.a.o0 = dk; L.a.o1 = dv;
-    if (entmax) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, true, L, st);
-    else CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, false, L, st);
+    if (ns == 2) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, false, 32, L, st);
+    else if (ns == 4) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, false, 64, L, st);
+    else if (entmax) CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, true, 16, L, st);
+    else CA_DIST_CPE_NQ(dkdv_tiled_kernel, dist, g.cpe, 3, false, 16, L, st);
     CA_CHECK_LAUNCH("tiled dk/dv kernel");
     return CA_OK;
 }
@@ -1709,31 +1791,38 @@ int tiled_attention_fwd(const Geo& gin, float scale, int dist, const float* q, c
     int rc = launch_pack(pa, st);
     if (rc) return rc;
     Launch L{};
-    const int nq = pick_nq(g, 4, 2, "CIRCATT_FWD_NQ");
-    if ((rc = prepare(g, P, nq, 18 * nq, "CIRCATT_FWD_WARPS", kv, nullptr, &L))) return rc;
+    const int ns = slabs_of(g);
+    // wide units: four columns per thread, or two when the window is short (with ws <= 9 most stages of a
+    // four-column tile pair with only some of its columns)
+    const int nq = ns > 1 ? (g.ws <= 9 ? 2 : 4) : pick_nq(g, 4, 2, "CIRCATT_FWD_NQ");
+    if ((rc = prepare(g, P, nq, 18 * nq, "CIRCATT_FWD_WARPS", kv, nullptr, &L, ns == 1, 4, ns))) return rc;
     L.a.scale = scale; L.a.c0 = q; L.a.o0 = y; L.a.ostats = stats;
-    const int dc = pick_dc(g.ws);
-#define CA_FWD2(DCV, EX, NQV)                                                               \
+    const int dc = ns > 1 ? 4 : pick_dc(g.ws);
+#define CA_FWD2(DCV, EX, NQV, NCRV_)                                                            \
     do {                                                                                 \
         if (g.cpe == 1) {                                                                \
-            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 1, EX, NQV>), L, st); \
-            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 1, EX, NQV>), L, st);     \
+            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 1, EX, NQV, NCRV_>), L, st); \
+            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 1, EX, NQV, NCRV_>), L, st);     \
         } else {                                                                         \
-            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 2, EX, NQV>), L, st); \
-            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 2, EX, NQV>), L, st);     \
+            if (dist) CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, true, 2, EX, NQV, NCRV_>), L, st); \
+            else CA_LAUNCH_TILED((fwd_tiled_kernel<DCV, false, 2, EX, NQV, NCRV_>), L, st);     \
         }                                                                                \
     } while (0)
 #define CA_FWD(DCV)                                                                      \
     do {                                                                                 \
         if (nq == 2) {                                                                   \
-            if (g.ws % DCV == 0) CA_FWD2(DCV, true, 2);                                  \
-            else CA_FWD2(DCV, false, 2);                                                 \
+            if (g.ws % DCV == 0) CA_FWD2(DCV, true, 2, 16);                              \
+            else CA_FWD2(DCV, false, 2, 16);                                             \
         } else {                                                                         \
-            if (g.ws % DCV == 0) CA_FWD2(DCV, true, 4);                                  \
-            else CA_FWD2(DCV, false, 4);                                                 \
+            if (g.ws % DCV == 0) CA_FWD2(DCV, true, 4, 16);                              \
+            else CA_FWD2(DCV, false, 4, 16);                                             \
         }                                                                                \
     } while (0)
-    switch (dc) {
+    if (ns == 2 && nq == 2) CA_FWD2(4, false, 2, 32);   // wide units: one chunk length, bounds checked
+    else if (ns == 2) CA_FWD2(4, false, 4, 32);
+    else if (ns == 4 && nq == 2) CA_FWD2(4, false, 2, 64);
+    else if (ns == 4) CA_FWD2(4, false, 4, 64);
+    else switch (dc) {
         case 3: CA_FWD(3); break;
         case 4: CA_FWD(4); break;
         case 7: CA_FWD(7); break;

@@ -281,7 +281,7 @@ def attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=None, dA=None,
         dA = jl.colmajor(dA)
     with _on_device(q.device):
         _status_word(q.device)
-        wsb = _scratch("bwd", lib.ca_attention_bwd_workspace(d), q.device)
+        wsb = _scratch("bwd", lib.ca_attention_bwd_workspace(d, int(dA is not None)), q.device)
         check(lib.ca_attention_bwd(d, ptr(q), ptr(k), ptr(v), ptr(y), ptr(dy), ptr(stats), ptr(nz), ptr(dA),
                                    ptr(dq), ptr(dk), ptr(dv), ptr(wsb), ptr(fwd_workspace), _stream()))
     return dq, dk, dv

@@ -166,8 +166,10 @@ int ca_attention_fwd_static(const ca_desc* d, const void* q, const void* k, cons
  * tiled softmax kernels then stream the packed copy of (k, v) the forward left
  * there instead of packing k and v again.  The Julia counterpart is keeping a
  * forward intermediate alive inside the pullback closure (src/rrules.jl:44-55
- * keeps the softmax output that way). */
-size_t ca_attention_bwd_workspace(const ca_desc* d);
+ * keeps the softmax output that way).  The workspace size depends on whether
+ * a cotangent on A will be passed (`with_dA`): that case runs the reference's
+ * pullback chain on A-sized scratch. */
+size_t ca_attention_bwd_workspace(const ca_desc* d, int32_t with_dA);
 int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void* v,
                      const void* y, const void* dy, const float* stats,
                      const float* nz, const float* dA,

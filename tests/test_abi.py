@@ -71,7 +71,7 @@ def test_null_pointers_are_rejected(ca):
     from circatt_b200._lib import lib, last_error
     assert lib.ca_similarity(_desc(ca), None, None, None, None, None) == -3
     assert "NULL" in last_error()
-    assert lib.ca_attention_bwd_workspace(_desc(ca)) == 8 * 8 * 2 * 4
+    assert lib.ca_attention_bwd_workspace(_desc(ca), 0) == 8 * 8 * 2 * 4
     assert lib.ca_attention_fwd_workspace(_desc(ca, normalizer=1), 0) == 64 * 25 * 2 * 4
     assert lib.ca_attention_fwd_workspace(_desc(ca), 0) == 0
 

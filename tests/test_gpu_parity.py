@@ -72,6 +72,9 @@ CASES = [
     ((37, 29, 16, 2), 9, 2, False),      # 8 channels per head: fused kernels on zero-extended units
     ((40, 21, 8, 2), 7, 2, True),        # 4 complex = 8 real channels per head
     ((256, 16, 2), 9, 2, False),         # 1-D, 8 channels per head
+    ((32, 30, 32, 1), 29, 1, False),     # 32 channels per unit, window 29: wide units on the fused kernels
+    ((34, 33, 64, 1), 31, 1, False),     # 64 channels per unit, window 31
+    ((128, 32, 2), 33, 1, False),        # 1-D, 32 channels per unit
 ]
 
 
@@ -116,7 +119,8 @@ def test_flash_mode_equals_materialised(ca, simname):
         assert rel_err(a, b.astype(np.float64)) < TOL
 
 
-@pytest.mark.parametrize("shape,ws,nheads", [((12, 10, 8, 2), 5, 2), ((20, 12, 64, 2), 5, 2)])
+@pytest.mark.parametrize("shape,ws,nheads", [((12, 10, 8, 2), 5, 2), ((20, 12, 64, 2), 5, 2), ((40, 24, 16, 2), 7, 1),
+                                             ((32, 30, 32, 1), 29, 1), ((34, 33, 64, 1), 31, 1)])
 def test_cotangent_on_returned_A(ca, shape, ws, nheads):
     """Loss uses both y and A (e.g. sparsity penalties): dA flows into the fused backward."""
     rng = np.random.default_rng(2)
@@ -126,7 +130,7 @@ def test_cotangent_on_returned_A(ca, shape, ws, nheads):
     dAn = np.asfortranarray(rng.standard_normal(tuple(A.nzVal.shape)).astype(np.float32))
     ((y * ca.jl.from_numpy(rn)).sum() + (A.nzVal * ca.jl.from_numpy(dAn)).sum()).backward()
     K = ws * ws
-    dA64 = dAn.astype(np.float64).reshape((K, shape[0] * shape[1], nheads * 2), order="F")
+    dA64 = dAn.astype(np.float64).reshape((K, shape[0] * shape[1], nheads * shape[-1]), order="F")
     dqo, dko, dvo = orc.mh_attention_pullback(orc.DISTANCE, up(qn), up(kn), up(vn), ws, nheads, up(rn), dA64)
     assert rel_err(ca.jl.to_numpy(q.grad), dqo) < TOL
     assert rel_err(ca.jl.to_numpy(k.grad), dko) < TOL
