@@ -362,6 +362,28 @@ def units_c5(ca, torch, dist, dev, world, rank, steps):
             "ms_per_step": t * 1e3, "px_per_s": H * W * 16 / t, "units_per_rank": mine}
 
 
+SLICES = {
+    # small cases of the same kernels for profiler captures: name -> a time_config tuple
+    "c2": ((128, 96, 64, 2), 15, 4, 0, 0, False, False, "f32"),
+    "c4": ((320, 320, 32, 2), 7, 1, 0, 0, True, True, "c64"),
+    "c5": ((1024, 1024, 32, 1), 21, 2, 0, 0, False, False, "f32"),       # two units of config 5 (0.13 GB per tensor)
+}
+
+
+def slice_main(args):
+    """Not the headline: a few forward + backward passes of a small slice of a BASELINE configuration (same
+    kernels, same window, few units), for profiler captures that must end by themselves.  One JSON line."""
+    import torch
+    from __graft_entry__ import load_package
+    torch.cuda.set_device(0)
+    ca = load_package()
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    timed = make_timer(torch, flush)
+    res = time_config(ca, torch, lambda fn: timed(fn, n=3, warm=2), gen, SLICES[args.slice], NOMINAL_FFMA_TFLOPS)
+    print(json.dumps({"slice": args.slice, "config": SLICES[args.slice][:5], **res}))
+
+
 def extra_main(args):
     """Not the headline: the stand-alone operators at the bench shape, one JSON line (L2 flushed before every
     timed call).  The other BASELINE configurations are part of the default run (`other_configs`)."""
@@ -408,7 +430,11 @@ def main():
                     help="time the stand-alone operators at the bench shape instead of the headline step")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the other BASELINE configurations and the "
                     "sharded config-5 runs (they add a few seconds)")
+    ap.add_argument("--slice", default=None, choices=sorted(SLICES),
+                    help="run a few passes of a small slice of a configuration (for profiler captures) and exit")
     args = ap.parse_args()
+    if args.slice:
+        return slice_main(args)
     if args.extra:
         return extra_main(args)
     if args.impl == "reference":

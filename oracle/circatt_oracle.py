@@ -384,17 +384,23 @@ def scale_pullback(c, nz, dB):
 
 
 # --------------------------------------------------------------------------
-# Sampled-pixel mode for sizes where the full oracle is too slow (2-D, real or
-# complex, softmax).  y[j] and dq[j] depend only on the window of j; dk[i] and
-# dv[i] only on the queries whose window contains i, each with its own window.
-# Same arithmetic as `attention` / `attention_pullback`, restricted to the
-# requested pixels.  q, k, v, dy: head-split (H, W, c, units) arrays.
+# Sampled-pixel mode for sizes where the full oracle is too slow (1-D or 2-D,
+# real or complex, softmax or entmax-1.5).  y[j], the row A[j, :] and dq[j]
+# depend only on the window of j; dk[i] and dv[i] only on the queries whose
+# window contains i, each with its own window.  Same arithmetic as `attention`
+# / `attention_pullback`, restricted to the requested pixels.  q, k, v, dy:
+# head-split (spatial..., c, units) arrays.
 # --------------------------------------------------------------------------
-def _window_pixels(h, w, H, W, p):
+def _window_pixels(j, spatial, p):
+    """key pixels of query pixel j (linear index) in ascending window-offset order: dw-major, dh-minor
+    in 2-D (the CSR order of an interior row; border rows of the CSR are rotations of it)."""
     d = np.arange(-p, p + 1)
-    hh = (h + d) % H
-    ww = (w + d) % W
-    return (hh[None, :] + H * ww[:, None]).reshape(-1)          # (K,) key pixels of query (h, w)
+    if len(spatial) == 1:
+        return (j + d) % spatial[0]
+    H, W = spatial
+    hh = (j % H + d) % H
+    ww = (j // H + d) % W
+    return (hh[None, :] + H * ww[:, None]).reshape(-1)
 
 
 def _row(kind, qj, Kwin, scale):
@@ -404,26 +410,40 @@ def _row(kind, qj, Kwin, scale):
     return -0.5 * scale * (np.abs(qj[None, :] - Kwin) ** 2).sum(axis=1)
 
 
-def sampled_attention(kind, q, k, v, ws, pixels, unit):
-    """y at the given linear pixels of one unit -> (len(pixels), c)."""
-    Q, spatial = _flat(q); Kk, _ = _flat(k); V, _ = _flat(v)
-    H, W = spatial
-    c = Q.shape[1]
-    scale = 1.0 / np.sqrt(float(c))
+def _normalize_row(norm, s):
+    if norm == SOFTMAX:
+        pr = np.exp(s - s.max())
+        return pr / pr.sum()
+    return row_entmax15(s[:, None])[:, 0]
+
+
+def sampled_rows(kind, q, k, ws, pixels, unit, norm=SOFTMAX):
+    """(window key pixels, normalised weights) of the rows A[j, :] at the given pixels of one unit,
+    each (len(pixels), K), in window-offset order (not the sorted CSR order)."""
+    Q, spatial = _flat(q); Kk, _ = _flat(k)
+    scale = 1.0 / np.sqrt(float(Q.shape[1]))
     p = (ws - 1) // 2
-    out = np.zeros((len(pixels), c), dtype=np.result_type(V.dtype, np.float64))
-    for n, j in enumerate(pixels):
-        win = _window_pixels(j % H, j // H, H, W, p)
-        s = _row(kind, Q[j, :, unit], Kk[win, :, unit], scale)
-        pr = np.exp(s - s.max()); pr /= pr.sum()
-        out[n] = pr @ V[win, :, unit]
+    wins, rows = [], []
+    for j in pixels:
+        win = _window_pixels(int(j), spatial, p)
+        wins.append(win)
+        rows.append(_normalize_row(norm, _row(kind, Q[j, :, unit], Kk[win, :, unit], scale)))
+    return np.array(wins), np.array(rows)
+
+
+def sampled_attention(kind, q, k, v, ws, pixels, unit, norm=SOFTMAX):
+    """y at the given linear pixels of one unit -> (len(pixels), c)."""
+    V, _ = _flat(v)
+    wins, rows = sampled_rows(kind, q, k, ws, pixels, unit, norm)
+    out = np.zeros((len(pixels), V.shape[1]), dtype=np.result_type(V.dtype, np.float64))
+    for n in range(len(pixels)):
+        out[n] = rows[n] @ V[wins[n], :, unit]
     return out
 
 
-def sampled_attention_pullback(kind, q, k, v, dy, ws, pixels, unit):
+def sampled_attention_pullback(kind, q, k, v, dy, ws, pixels, unit, norm=SOFTMAX):
     """(dq, dk, dv) rows at the given pixels of one unit, each (len(pixels), c)."""
     Q, spatial = _flat(q); Kk, _ = _flat(k); V, _ = _flat(v); DY, _ = _flat(dy)
-    H, W = spatial
     c = Q.shape[1]
     scale = 1.0 / np.sqrt(float(c))
     p = (ws - 1) // 2
@@ -432,16 +452,16 @@ def sampled_attention_pullback(kind, q, k, v, dy, ws, pixels, unit):
     def row_terms(j):
         """window, P and dS of query row j."""
         if j not in cache:
-            win = _window_pixels(j % H, j // H, H, W, p)
-            s = _row(kind, Q[j, :, unit], Kk[win, :, unit], scale)
-            P = np.exp(s - s.max()); P /= P.sum()
+            win = _window_pixels(j, spatial, p)
+            P = _normalize_row(norm, _row(kind, Q[j, :, unit], Kk[win, :, unit], scale))
             dP = np.real(V[win, :, unit].conj() @ DY[j, :, unit])
-            dS = P * (dP - (P * dP).sum())
+            dS = row_normalize_pullback(norm, P[:, None], dP[:, None])[:, 0]
             cache[j] = (win, P, dS)
         return cache[j]
 
     dq = np.zeros((len(pixels), c), dtype=Q.dtype); dk = np.zeros_like(dq); dv = np.zeros_like(dq)
     for n, j in enumerate(pixels):
+        j = int(j)
         win, P, dS = row_terms(j)
         dq[n] = scale * (dS @ Kk[win, :, unit])
         if kind == DISTANCE:

@@ -1,17 +1,40 @@
 """The BASELINE configurations at (or near) their full sizes.
 
-Config 2 runs at full size against the full oracle.  Config 5 (1024 x 1024, ws 21, 16 channels
-per head) runs at full spatial size with fewer units and is checked at sampled pixels: every
-corner, border and tile seam plus random interior pixels, for y, dq, dk and dv (each value
-depends only on windows around the sampled pixel).  Config 3 (1-D, entmax-1.5, Distance) and
-config 4 (ComplexF32 + Circulant algebra) run at reduced extents against the full oracle, and
-at larger extents through size-independent properties."""
+Config 2 runs at full size against the full oracle.  Configs 3 (1-D, entmax-1.5, Distance), 4
+(ComplexF32, A materialised) and 5 (1024 x 1024, ws 21, Float32 and BFloat16 storage) run at
+their full extents and are checked at sampled pixels: every end / corner / border / tile seam
+plus random interior pixels, for y, dq, dk and dv and (config 4) the rows of A; each of those
+values depends only on windows around the sampled pixel, which the oracle evaluates exactly.
+Configs 3 and 4 also run at reduced extents against the full oracle (with the Circulant
+algebra of config 4), and config 3 through size-independent properties."""
 import numpy as np
 import pytest
 import torch
 
 from oracle import circatt_oracle as orc
 from tests.helpers import KIND, TOL, randn, rel_err, up
+
+
+def _sampled_check(ca, kind, norm, q, k, v, r, outs, ws, nheads, pixels, units, tol, A=None):
+    """outs = (y, dq, dk, dv) (and the rows of A) at `pixels` of `units` against the sampled-pixel oracle."""
+    qs, ks, vs, rs = (orc.splitheads(up(ca.jl.to_numpy(t)), nheads) for t in (q, k, v, r))
+    flat = lambda t: orc._flat(orc.splitheads(ca.jl.to_numpy(t).astype(np.complex128 if t.is_complex() else np.float64), nheads))[0]
+    Y, DQ, DK, DV = (flat(t) for t in outs)
+    nz = None
+    if A is not None:
+        nz = ca.jl.to_numpy(A.nzVal)
+        nz = nz.reshape((-1, Y.shape[0], nz.size // nz.shape[0]), order="F")       # (K, Np, units)
+    for unit in units:
+        ys = orc.sampled_attention(kind, qs, ks, vs, ws, pixels, unit, norm)
+        dq, dk, dv = orc.sampled_attention_pullback(kind, qs, ks, vs, rs, ws, pixels, unit, norm)
+        for name, got, want in (("y", Y, ys), ("dq", DQ, dq), ("dk", DK, dk), ("dv", DV, dv)):
+            err = np.abs(got[pixels, :, unit] - want).max() / max(1e-30, np.abs(want).max())
+            assert err < tol, f"{name} unit {unit}: {err:.3g}"
+        if nz is not None:
+            wins, rows = orc.sampled_rows(kind, qs, ks, ws, pixels, unit, norm)
+            for n, j in enumerate(pixels):
+                order = np.argsort(wins[n], kind="stable")                           # CSR rows are sorted by column
+                assert np.abs(nz[:, j, unit] - rows[n][order]).max() < tol * max(1e-30, rows[n].max())
 
 pytestmark = pytest.mark.gpu
 
@@ -60,6 +83,63 @@ def test_config5_spatial_size_sampled(ca):
         dq, dk, dv = orc.sampled_attention_pullback(orc.DOT, qs, ks, vs, rs, ws, pixels, unit)
         for got, want in ((Y, ys), (DQ, dq), (DK, dk), (DV, dv)):
             assert np.abs(got[pixels, :, unit] - want).max() < TOL * max(1.0, np.abs(want).max())
+
+
+def test_config5_eight_units_and_bfloat16(ca):
+    """Config 5 with 8 units (one batch element, 128 channels, 8 heads) in Float32, and the same in
+    BFloat16 storage (bar 1e-2 of the largest value, against the oracle on the rounded inputs)."""
+    H = W = 1024
+    ws, nheads, C = 21, 8, 128
+    g = torch.Generator(device="cuda").manual_seed(55)
+    base = [ca.jl.randn(H, W, C, 1, generator=g) for _ in range(4)]
+    rng = np.random.default_rng(55)
+    edge = [0, 9, 10, 127, 128, 1013, 1023]
+    pixels = [h + H * w for h in edge[::2] for w in edge[1::2]] + [int(x) for x in rng.integers(0, H * W, 12)]
+    for dtype, tol in ((torch.float32, TOL), (torch.bfloat16, 1e-2)):
+        q, k, v, r = (t.detach().to(dtype) for t in base)
+        q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+        y, A = ca.circulant_mh_attention(ca.DotSimilarity(), q, k, v, ws, nheads, return_A=False)
+        (y.float() * r.float()).sum().backward()
+        torch.cuda.synchronize()
+        f32 = lambda t: t.detach().float()
+        _sampled_check(ca, orc.DOT, orc.SOFTMAX, f32(q), f32(k), f32(v), f32(r),
+                       (f32(y), f32(q.grad), f32(k.grad), f32(v.grad)), ws, nheads, pixels, (0, 5, 7), tol)
+        del q, k, v, r, y
+        ca.ops.release_scratch()
+        torch.cuda.empty_cache()
+
+
+def test_config3_full_size_sampled(ca):
+    """Config 3 at its full size: N = 16384, C = 64, B = 16, ws 127, 8 heads, Distance + entmax-1.5,
+    forward + backward, checked at sampled pixels (both ends of the signal, fold seams, random)."""
+    g = torch.Generator(device="cuda").manual_seed(33)
+    q, k, v, r = (ca.jl.randn(16384, 64, 16, generator=g) for _ in range(4))
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    y, A = ca.circulant_mh_attention(ca.DistanceSimilarity(), q, k, v, 127, 8, normalizer=ca.ENTMAX15, return_A=False)
+    (y * r).sum().backward()
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(33)
+    pixels = [0, 1, 62, 63, 64, 127, 128, 129, 8191, 8192, 16320, 16321, 16383] + [int(x) for x in rng.integers(0, 16384, 12)]
+    _sampled_check(ca, orc.DISTANCE, orc.ENTMAX15, q.detach(), k.detach(), v.detach(), r, (y, q.grad, k.grad, v.grad),
+                   127, 8, pixels, (0, 77, 127), 2 * TOL)
+
+
+def test_config4_full_size_sampled(ca):
+    """Config 4 at its full size: ComplexF32, H = W = 320, C = 32, B = 8, ws 7, one head, Dot, A
+    materialised; y, the rows of A and the gradients at sampled pixels."""
+    g = torch.Generator(device="cuda").manual_seed(44)
+    q, k, v, r = (ca.jl.randn(320, 320, 32, 8, generator=g, dtype=torch.complex64) for _ in range(4))
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    y, A = ca.circulant_attention(ca.DotSimilarity(), q, k, v, 7)
+    assert A.shape == (102400, 102400, 1, 8)
+    (y * r.conj()).real.sum().backward()
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(44)
+    H = 320
+    edge = [0, 2, 3, 31, 32, 316, 317, 319]
+    pixels = [h + H * w for h in edge[::2] for w in edge[1::2]] + [int(x) for x in rng.integers(0, H * H, 16)]
+    _sampled_check(ca, orc.DOT, orc.SOFTMAX, q.detach(), k.detach(), v.detach(), r, (y, q.grad, k.grad, v.grad),
+                   7, 1, pixels, (0, 7), TOL, A=A)
 
 
 def test_config3_1d_entmax_distance(ca):

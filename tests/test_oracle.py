@@ -292,3 +292,36 @@ def test_sampled_oracle_matches_full_oracle():
             np.testing.assert_allclose(sq, DQ[pixels, :, unit], rtol=1e-10, atol=1e-13)
             np.testing.assert_allclose(sk, DK[pixels, :, unit], rtol=1e-10, atol=1e-13)
             np.testing.assert_allclose(sv, DV[pixels, :, unit], rtol=1e-10, atol=1e-13)
+
+
+@pytest.mark.parametrize("shape,ws,nheads,cplx,norm", [
+    ((40, 6, 2), 9, 2, False, "entmax"),        # 1-D, entmax-1.5
+    ((40, 6, 2), 9, 1, True, "softmax"),        # 1-D, complex
+    ((9, 8, 4, 2), 5, 1, True, "softmax"),      # 2-D, complex
+    ((9, 8, 6, 2), 5, 2, False, "entmax"),      # 2-D, entmax-1.5
+])
+def test_sampled_oracle_1d_entmax_complex(shape, ws, nheads, cplx, norm):
+    """The sampled-pixel mode (used at the full BASELINE sizes) against the full oracle on small cases:
+    1-D signals, the entmax normaliser, complex inputs, and the rows of A themselves."""
+    rng = np.random.default_rng(21)
+    nrm = orc.ENTMAX15 if norm == "entmax" else orc.SOFTMAX
+    q, k, v, dy = (randn(rng, shape, cplx) for _ in range(4))
+    qs, ks, vs, dys = (orc.splitheads(t.astype(np.complex128 if cplx else np.float64), nheads) for t in (q, k, v, dy))
+    Np = int(np.prod(shape[:-2]))
+    pixels = [0, 1, Np // 2, Np - 2, Np - 1, 7]
+    for kind in (orc.DOT, orc.DISTANCE):
+        y, P = orc.attention(kind, qs, ks, vs, ws, nrm)
+        dq, dk, dv = orc.attention_pullback(kind, qs, ks, vs, ws, dys, norm=nrm)
+        Y, _ = orc._flat(y); DQ, _ = orc._flat(dq); DK, _ = orc._flat(dk); DV, _ = orc._flat(dv)
+        for unit in (0, qs.shape[-1] - 1):
+            ys = orc.sampled_attention(kind, qs, ks, vs, ws, pixels, unit, nrm)
+            sq, sk, sv = orc.sampled_attention_pullback(kind, qs, ks, vs, dys, ws, pixels, unit, nrm)
+            np.testing.assert_allclose(ys, Y[pixels, :, unit], rtol=1e-10, atol=1e-12)
+            np.testing.assert_allclose(sq, DQ[pixels, :, unit], rtol=1e-9, atol=1e-12)
+            np.testing.assert_allclose(sk, DK[pixels, :, unit], rtol=1e-9, atol=1e-12)
+            np.testing.assert_allclose(sv, DV[pixels, :, unit], rtol=1e-9, atol=1e-12)
+            # rows of A: the sampled row holds the same values as the CSR row, which is sorted by column
+            wins, rows = orc.sampled_rows(kind, qs, ks, ws, pixels, unit, nrm)
+            for n, j in enumerate(pixels):
+                order = np.argsort(wins[n], kind="stable")
+                np.testing.assert_allclose(rows[n][order], P[:, j, unit], rtol=1e-10, atol=1e-13)
