@@ -3,8 +3,9 @@
 # kernels, cuSPARSE and NNlib.
 #
 # STATUS: written without a Julia toolchain (none exists where this library is built), so it
-# has never been parsed or run.  It documents the binding precisely; the Python package next
-# to it is the binding that is tested.  Names, signatures and assertion messages follow the
+# has never been parsed or run.  It documents the binding precisely and defines every method the
+# reference's own tests call (test/rrule.jl, test/grad.jl); the Python package next to it is the
+# binding that is tested.  Names, signatures and assertion messages follow the
 # reference (file:line citations are to CirculantAttention.jl v1.0.1).
 module CirculantAttentionB200
 
@@ -18,6 +19,7 @@ export circulant_attention, circulant_mh_attention, circulant_mh_adjacency, ⊗,
 using CUDA, CUDA.CUSPARSE
 using LinearAlgebra
 using NNlib
+import Adapt
 import ChainRulesCore as CRC
 import Zygote
 
@@ -101,6 +103,19 @@ CUDA.unsafe_free!(A::Circulant) = CUDA.unsafe_free!(nzval(A))
 function Base.show(io::IOContext, m::MIME"text/plain", A::Circulant{T,N,M}) where {T,N,M}
     print(io, typeof(A), " with kernel-length $M, spatial-size $(spatial_size(A)), and data,\n")
     show(io, m, A.data)
+end
+
+# src/array.jl:22-25: moving a Circulant between array back ends moves its CSR container
+Adapt.adapt_structure(to, A::Circulant{T,N,M}) where {T,N,M} =
+    Circulant(Adapt.adapt_structure(to, A.data), M, A.spatial_size)
+
+# src/array.jl:87-117: equal axes, window, spatial size, values and structure
+function Base.:(==)(A::Circulant, B::Circulant)
+    axes(A) == axes(B) && spatial_size(A) == spatial_size(B) && kernel_length(A) == kernel_length(B) || return false
+    nzval(A) == nzval(B) || return false
+    # structures of equal (window, spatial size, batch size) come out of the same cache entry
+    (A.data.rowPtr === B.data.rowPtr && A.data.colVal === B.data.colVal) ||
+        (A.data.rowPtr == B.data.rowPtr && A.data.colVal == B.data.colVal)
 end
 
 function Base.reshape(A::Circulant{T,N,M}, dims::Union{Colon,Int}...) where {T,N,M}
@@ -201,31 +216,35 @@ function fused_forward(simfun, q::T, k::T, v::T, W::Int, nheads::Int, return_A::
                 (Ref{CaDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Float32}, CuPtr{Float32},
                  CuPtr{Cvoid}, Ptr{Cvoid}),
                 d, qr, kr, vr, y, return_A ? nzval(A) : CU_NULL, stats, work, stream()))
-    return reshape(y, size(q)...), A, stats
+    # `work` holds the packed copy of (k, v); the pullback closure keeps it alive and hands it back
+    return reshape(y, size(q)...), A, stats, work
 end
 
-function fused_backward(simfun, q::T, k::T, v::T, y, dy, stats, A, dA, W::Int, nheads::Int) where {Tv,N,T<:AnyCuArray{Tv,N}}
+function fused_backward(simfun, q::T, k::T, v::T, y, dy, stats, A, dA, fwdwork, W::Int, nheads::Int) where {Tv,N,T<:AnyCuArray{Tv,N}}
     qr, kr, vr, yr, dyr = splitheads.((q, k, v, y, dy), nheads)
     d = desc(qr, W; sim=simcode(simfun), scale=1f0 / sqrt(Float32(size(kr, N - 1))))
     dq, dk, dv = similar(qr), similar(kr), similar(vr)
-    work = CuVector{UInt8}(undef, ccall((:ca_attention_bwd_workspace, LIB), Csize_t, (Ref{CaDesc},), d))
+    work = CuVector{UInt8}(undef, ccall((:ca_attention_bwd_workspace, LIB), Csize_t, (Ref{CaDesc}, Int32), d, dA !== nothing))
     check(ccall((:ca_attention_bwd, LIB), Cint,
                 (Ref{CaDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Float32},
-                 CuPtr{Float32}, CuPtr{Float32}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, Ptr{Cvoid}),
-                d, qr, kr, vr, yr, dyr, stats, dA === nothing ? CU_NULL : nzval(A),
-                dA === nothing ? CU_NULL : nzval(dA), dq, dk, dv, work, stream()))
+                 CuPtr{Float32}, CuPtr{Float32}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, Ptr{Cvoid}),
+                d, qr, kr, vr, yr, dyr, stats, A === nothing ? CU_NULL : nzval(A),
+                dA === nothing ? CU_NULL : nzval(dA), dq, dk, dv, work, fwdwork === nothing ? CU_NULL : fwdwork, stream()))
+    CUDA.unsafe_free!(work)
     return reshape(dq, size(q)...), reshape(dk, size(k)...), reshape(dv, size(v)...)
 end
 
 function circulant_attention(simfun::AbstractSimilarity, q::T, k::T, v::T, W::Int) where {Tv,N,T<:AbstractArray{Tv,N}}
-    y, A, _ = fused_forward(simfun, q, k, v, W, 1, true)
+    y, A, _, work = fused_forward(simfun, q, k, v, W, 1, true)
+    CUDA.unsafe_free!(work)
     return y, A
 end
 circulant_attention(q::T, k::T, v::T, W::Int) where T = circulant_attention(DotSimilarity(), q, k, v, W)
 
 # simfun is honoured (src/attention.jl:40 drops it) and the 5-argument form works (:43 does not).
 function circulant_mh_attention(simfun::AbstractSimilarity, q::T, k::T, v::T, W::Int, nheads::Int) where {Tv,N,T<:AbstractArray{Tv,N}}
-    y, A, _ = fused_forward(simfun, q, k, v, W, nheads, true)
+    y, A, _, work = fused_forward(simfun, q, k, v, W, nheads, true)
+    CUDA.unsafe_free!(work)
     return y, A
 end
 circulant_mh_attention(q::T, k::T, v::T, W::Int, nheads::Int) where T =
@@ -235,17 +254,125 @@ circulant_mh_attention(q::T, k::T, v::T, W::Int, nheads::Int) where T =
 for (f, extra) in ((:circulant_attention, ()), (:circulant_mh_attention, (:nheads,)))
     @eval function CRC.rrule(::typeof($f), simfun::AbstractSimilarity, q, k, v, W::Int, $(extra...))
         nh = $(isempty(extra) ? 1 : :nheads)
-        y, A, stats = fused_forward(simfun, q, k, v, W, nh, true)
+        y, A, stats, work = fused_forward(simfun, q, k, v, W, nh, true)
         function attention_pullback(Δ)
             dy, dA = CRC.unthunk(Δ[1]), CRC.unthunk(Δ[2])
             dy = dy isa CRC.AbstractZero ? zero(y) : dy
             dA = dA isa Circulant ? dA : nothing
-            dq, dk, dv = fused_backward(simfun, q, k, v, y, dy, stats, A, dA, W, nh)
+            dq, dk, dv = fused_backward(simfun, q, k, v, y, dy, stats, A, dA, work, W, nh)
             return (CRC.NoTangent(), CRC.NoTangent(), dq, dk, dv, CRC.NoTangent(), $(map(_ -> :(CRC.NoTangent()), extra)...))
         end
         return (y, A), attention_pullback
     end
 end
+
+# ------------------------------------------------------------------ piecewise rrules (src/rrules.jl:1-114)
+# The reference composes these from batched SpMMs; here each pullback is one or two C ABI calls.
+# They exist so that code written against the reference's pieces (test/rrule.jl:18-22, test/grad.jl) keeps
+# differentiating; the fused entry points above have their own direct pullback.
+function similarity_pullback(simfun, x, y, dS::Circulant)
+    d = desc(x, kernel_length(dS); sim=simcode(simfun))
+    dx, dy = similar(x), similar(y)
+    ws = operator_workspace(d)
+    check(ccall((:ca_similarity_bwd, LIB), Cint,
+                (Ref{CaDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Float32}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, Ptr{Cvoid}),
+                d, x, y, nzval(dS), dx, dy, ws, stream()))
+    CUDA.unsafe_free!(ws)
+    return dx, dy
+end
+
+function CRC.rrule(::typeof(circulant_similarity), simfun::AbstractSimilarity, x::AbstractArray{T,N}, y::AbstractArray{T,N}, W) where {T,N}
+    S = circulant_similarity(simfun, x, y, W)                      # src/rrules.jl:1-32 (Distance :1-16, Dot :18-32)
+    function similarity_pb(dS)
+        dx, dy = similarity_pullback(simfun, x, y, CRC.unthunk(dS))
+        return (CRC.NoTangent(), CRC.NoTangent(), dx, dy, CRC.NoTangent())
+    end
+    return S, similarity_pb
+end
+
+function CRC.rrule(::typeof(_circulant_reshape), X::Circulant, dims...)      # src/rrules.jl:34-40
+    reshape_pb(dX) = (CRC.NoTangent(), reshape(CRC.unthunk(dX), size(X)...), map(_ -> CRC.NoTangent(), dims)...)
+    return reshape(X, dims...), reshape_pb
+end
+
+function CRC.rrule(::typeof(NNlib.softmax), X::Circulant)                  # src/rrules.jl:42-56
+    Y = NNlib.softmax(X)
+    function softmax_pb(dY)
+        ΔY = CRC.unthunk(dY)
+        dS = similar(nzval(Y))
+        d = nzdesc(spatial_size(X), kernel_length(X), prod(size(X)[3:end]))
+        check(ccall((:ca_row_normalize_bwd, LIB), Cint, (Ref{CaDesc}, CuPtr{Float32}, CuPtr{Float32}, CuPtr{Float32}, Ptr{Cvoid}),
+                    d, nzval(Y), nzval(ΔY), dS, stream()))
+        return (CRC.NoTangent(), withnz(X, dS))                     # cotangent shares the primal's structure (:51)
+    end
+    return Y, softmax_pb
+end
+
+function CRC.rrule(::typeof(circulant_attention), A::Circulant{T,N,M}, b::AbstractArray) where {T,N,M}   # src/rrules.jl:58-72
+    function otimes_pb(dc)
+        Δc = CRC.unthunk(dc)
+        ∂A = CRC.@thunk reshape(circulant_similarity(DotSimilarity(), Δc, b, M), size(A)...)
+        ∂b = CRC.@thunk circulant_transposed_attention(A, Δc)
+        return (CRC.NoTangent(), ∂A, ∂b)
+    end
+    return A ⊗ b, otimes_pb
+end
+
+function CRC.rrule(::typeof(circulant_transposed_attention), A::Circulant{T,N,M}, b::AbstractArray) where {T,N,M}   # :74-88
+    function otimes_t_pb(dc)
+        Δc = CRC.unthunk(dc)
+        ∂A = CRC.@thunk reshape(circulant_similarity(DotSimilarity(), b, Δc, M), size(A)...)
+        ∂b = CRC.@thunk circulant_attention(A, Δc)
+        return (CRC.NoTangent(), ∂A, ∂b)
+    end
+    return circulant_transposed_attention(A, b), otimes_t_pb
+end
+
+LinearAlgebra.dot(X::Circulant, Y::Circulant) = sum(withnz(X, nzval(X) .* nzval(Y)))            # src/array.jl:83-85
+LinearAlgebra.dot(f::Zygote.FillArrays.Fill, A::Circulant) = f.value * sum(A)                   # src/rrules.jl:90-92
+
+_scale_collectnz(X::Circulant) = nzval(X)
+_scale_collectnz(X::Zygote.FillArrays.Fill) = X.value
+
+function CRC.rrule(::typeof(scale), c::AbstractArray, A::Circulant)        # src/rrules.jl:97-114
+    function scale_pb(dB)
+        ΔB = CRC.unthunk(dB)
+        ∂c = CRC.@thunk begin
+            # per-slice sum of ΔB∘A (ca_dot_batch), then summed over the batch dims where c has extent 1
+            prodnz = withnz(A, _scale_collectnz(ΔB) .* nzval(A))
+            s = sum(prodnz; dims=(1, 2))
+            sumdims = filter(d -> size(c, d) == 1 && size(s, d) > 1, 3:ndims(c))
+            reshape(isempty(sumdims) ? s : sum(s; dims=sumdims), size(c)...)
+        end
+        ∂A = CRC.@thunk begin
+            full = scale(c, ΔB)
+            sumdims = filter(d -> size(A, d) == 1 && size(full, d) > 1, 3:ndims(A))
+            isempty(sumdims) ? full : sum(full; dims=Tuple(sumdims))
+        end
+        return (CRC.NoTangent(), ∂c, ∂A)
+    end
+    return scale(c, A), scale_pb
+end
+
+# NNlib.batched_mul(!) on Circulant and its lazy transposes (src/batchedmul.jl:13-35): the reference sends
+# A.data to cuSPARSE; here the same products are ca_apply on (Np, c, batch) arrays.
+const CircOrT = Union{Circulant, NNlib.BatchedTranspose{<:Any,<:Circulant}, NNlib.BatchedAdjoint{<:Any,<:Circulant}}
+_parent(A::Circulant) = (A, false)
+_parent(A::Union{NNlib.BatchedTranspose,NNlib.BatchedAdjoint}) = (A.parent, true)   # values of A are real: adjoint == transpose
+function NNlib.batched_mul!(C::AnyCuArray, A::CircOrT, B::AnyCuArray)
+    P, tr = _parent(A)
+    sp = spatial_size(P)
+    x = reshape(B, sp..., size(B, 2), size(B, 3))
+    apply!(reshape(C, sp..., size(C, 2), size(C, 3)), reshape(P, size(P, 1), size(P, 2), :), x, tr)
+    return C
+end
+function NNlib.batched_mul(A::CircOrT, B::AnyCuArray{T}) where T
+    P, _ = _parent(A)
+    nb = max(prod(size(P)[3:end]), size(B, 3))
+    NNlib.batched_mul!(similar(B, T, (size(P, 1), size(B, 2), nb)), A, B)
+end
+
+Zygote.accum(x::T, y::T, z::T...) where T <: Circulant = Zygote.accum(Zygote.accum(x, y), z...)   # src/zygote.jl:7
 
 # ------------------------------------------------------------------ algebra and sums (src/array.jl:66-189)
 function axpby(α, X::Circulant, β, Y::Union{Circulant,Nothing})
