@@ -65,6 +65,10 @@ PROTOTYPES = {
     "ca_attention_bwd_dkdv": (C.c_int, [_D] + [_p] * 11),
     "ca_status_word": (C.c_int, [_p]),
     "ca_stage_timeouts": (C.c_int, [C.POINTER(C.c_int32)]),
+    "ca_comm_unique_id": (C.c_int, [_p]),
+    "ca_comm_init": (C.c_int, [_i32, _i32, _p, C.POINTER(C.c_void_p)]),
+    "ca_comm_destroy": (C.c_int, [_p]),
+    "ca_halo_exchange": (C.c_int, [_p, _p, _p, _p, _p, C.c_size_t, _p]),
     "ca_axpby": (C.c_int, [_i64, _f32, _p, _f32, _p, _p, _p]),
     "ca_scale_batch": (C.c_int, [_i64, _i32, _i32, _p, _i32, _i32, _p, _i32, _i32, _p, _p]),
     "ca_dot_batch": (C.c_int, [_i64, _i32, _i32, _p, _i32, _i32, _p, _i32, _i32, _p, _p]),

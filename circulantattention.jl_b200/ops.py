@@ -10,7 +10,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib, jl
-from ._lib import CA_BF16, CA_C64, CA_F32, ca_desc, check, lib, ptr
+from ._lib import CA_BF16, CA_C64, CA_F32, ca_desc, check, lib, ptr  # noqa: F401  (re-exported: parallel.py uses ops.lib / ops.check)
 
 
 @dataclass(frozen=True)

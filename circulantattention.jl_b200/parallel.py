@@ -101,7 +101,39 @@ def _staging(tag, numel, dtype, device):
     return buf
 
 
-def exchange_halos(xs, p: int, group=None):
+class Ring:
+    """The ring of bands through the library's own NCCL binding (ca_comm_* / ca_halo_exchange of the C ABI):
+    the path a host without torch.distributed (the Julia package) uses.  Rank 0 creates the 128-byte id with
+    `Ring.unique_id()` and hands it to the other ranks by any means; every rank then constructs
+    `Ring(rank, world, id)` with its GPU current."""
+
+    def __init__(self, rank: int, world: int, unique_id: bytes = None):
+        import ctypes
+        self.rank, self.world = int(rank), int(world)
+        self._h = ctypes.c_void_p()
+        buf = ctypes.create_string_buffer(bytes(unique_id), 128) if unique_id is not None else None
+        ops.check(ops.lib.ca_comm_init(self.rank, self.world, buf, ctypes.byref(self._h)))
+
+    @staticmethod
+    def unique_id() -> bytes:
+        import ctypes
+        buf = ctypes.create_string_buffer(128)
+        ops.check(ops.lib.ca_comm_unique_id(buf))
+        return buf.raw
+
+    def exchange(self, send_left, send_right, recv_left, recv_right):
+        """Contiguous device buffers of equal size; ordered on torch's current stream."""
+        n = send_left.numel() * send_left.element_size()
+        ops.check(ops.lib.ca_halo_exchange(self._h, ops.ptr(send_left), ops.ptr(send_right), ops.ptr(recv_left),
+                                           ops.ptr(recv_right), n, ops._stream()))
+
+    def close(self):
+        if self._h:
+            ops.check(ops.lib.ca_comm_destroy(self._h))
+            self._h = None
+
+
+def exchange_halos(xs, p: int, group=None, ring: "Ring" = None):
     """Extended slabs (H, Wb + 2p, ...) of the band-local (H, Wb, ...) tensors `xs` (same dtype and device):
     `p` columns from the left neighbour, the band, `p` columns from the right neighbour.
 
@@ -127,7 +159,10 @@ def exchange_halos(xs, p: int, group=None):
         ext.narrow(-2, p, Wb).copy_(t)
         ts.append(t)
         exts.append(ext)
-    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    if ring is not None:
+        world = ring.world
+    else:
+        world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
     if world == 1:
         for t, ext in zip(ts, exts):
             Wb = t.shape[-2]
@@ -146,17 +181,20 @@ def exchange_halos(xs, p: int, group=None):
             to_right[off:off + n].view(shape).copy_(t.narrow(-2, Wb - p, p))   # the right neighbour's left halo
             to_left[off:off + n].view(shape).copy_(t.narrow(-2, 0, p))         # the left neighbour's right halo
             off += n
-        rank = dist.get_rank(group)
-        left, right = (rank - 1) % world, (rank + 1) % world
-        peer = lambda r: dist.get_global_rank(group, r) if group is not None else r
-        reqs = dist.batch_isend_irecv([
-            dist.P2POp(dist.isend, to_right, peer(right), group, tag=0),
-            dist.P2POp(dist.isend, to_left, peer(left), group, tag=1),
-            dist.P2POp(dist.irecv, from_left, peer(left), group, tag=0),
-            dist.P2POp(dist.irecv, from_right, peer(right), group, tag=1),
-        ])
-        for r in reqs:
-            r.wait()
+        if ring is not None:
+            ring.exchange(to_left, to_right, from_left, from_right)
+        else:
+            rank = dist.get_rank(group)
+            left, right = (rank - 1) % world, (rank + 1) % world
+            peer = lambda r: dist.get_global_rank(group, r) if group is not None else r
+            reqs = dist.batch_isend_irecv([
+                dist.P2POp(dist.isend, to_right, peer(right), group, tag=0),
+                dist.P2POp(dist.isend, to_left, peer(left), group, tag=1),
+                dist.P2POp(dist.irecv, from_left, peer(left), group, tag=0),
+                dist.P2POp(dist.irecv, from_right, peer(right), group, tag=1),
+            ])
+            for r in reqs:
+                r.wait()
         off = 0
         for t, ext, n in zip(ts, exts, sizes):
             Wb = t.shape[-2]
@@ -172,17 +210,17 @@ def exchange_halo(x: torch.Tensor, p: int, group=None) -> torch.Tensor:
     return exchange_halos([x], p, group)[0]
 
 
-def band_attention_fwd(kind, q, k, v, ws, group=None, normalizer=0):
+def band_attention_fwd(kind, q, k, v, ws, group=None, normalizer=0, ring=None):
     """Forward on this rank's band of head-split (H, Wb, c, units) tensors: one exchange (k and v
     together), one kernel call.  Returns (y, stats, k_ext, v_ext); the extended slabs are reused by
     the backward."""
     p = (ws - 1) // 2
-    k_ext, v_ext = exchange_halos([k, v], p, group)
+    k_ext, v_ext = exchange_halos([k, v], p, group, ring)
     y, _, stats = ops.attention_fwd(kind, normalizer, q, k_ext, v_ext, ws, False, band=(k_ext.shape[1], p))
     return y, stats, k_ext, v_ext
 
 
-def band_attention_bwd(kind, q, k, v, y, dy, stats, k_ext, v_ext, ws, group=None, normalizer=0):
+def band_attention_bwd(kind, q, k, v, y, dy, stats, k_ext, v_ext, ws, group=None, normalizer=0, ring=None):
     """Backward on this rank's band.  One more exchange: q, dy, stats and D of the neighbouring columns
     (one message per neighbour) feed the key-owned dk/dv sweep.  The dq sweep needs nothing from the
     neighbours beyond the forward's k and v slabs, so it is queued before the exchange is waited for."""
@@ -194,10 +232,10 @@ def band_attention_bwd(kind, q, k, v, y, dy, stats, k_ext, v_ext, ws, group=None
     if q.dtype == torch.float32:
         # the two scalar planes ride in the same message as q and dy
         q_ext, dy_ext, stats_ext, D_ext = exchange_halos(
-            [q, dy, jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group)
+            [q, dy, jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group, ring)
     else:
-        q_ext, dy_ext = exchange_halos([q, dy], p, group)
-        stats_ext, D_ext = exchange_halos([jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group)
+        q_ext, dy_ext = exchange_halos([q, dy], p, group, ring)
+        stats_ext, D_ext = exchange_halos([jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group, ring)
     dk, dv = ops.attention_bwd_dkdv(kind, normalizer, q_ext, k, v, dy_ext,
                                     jl.reshape(stats_ext, (H * (Wb + 2 * p), units)),
                                     jl.reshape(D_ext, (H * (Wb + 2 * p), units)), ws, band=(Wb + 2 * p, p))

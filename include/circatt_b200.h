@@ -45,7 +45,8 @@ typedef enum ca_status {
     CA_ERR_UNSUPPORTED = -2,   /* legal but not implemented combination */
     CA_ERR_NULL = -3,          /* a required pointer is NULL */
     CA_ERR_CUDA = -4,          /* a CUDA runtime call or launch failed */
-    CA_ERR_TOO_LARGE = -5      /* a size exceeds a documented limit */
+    CA_ERR_TOO_LARGE = -5,     /* a size exceeds a documented limit */
+    CA_ERR_COMM = -6           /* NCCL is missing or an NCCL call failed */
 } ca_status;
 
 enum { CA_F32 = 0, CA_C64 = 1, CA_BF16 = 2 }; /* element type of dense tensors; CA_BF16 (storage only: all
@@ -208,6 +209,24 @@ int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const 
  * time out, they hang (src/similarity.jl:47-51 launches without any bound). */
 int ca_status_word(int32_t* device_word);
 int ca_stage_timeouts(int32_t* count);
+
+/* ---------------------------------------------------------------- multi-GPU halo exchange
+ * Band split of very large images (no counterpart in the reference, which is a
+ * single-device package): one process per GPU owns a band of columns and needs
+ * p = (ws-1)/2 columns of the key-side tensors from the ranks r-1 and r+1
+ * (mod world: the circular wrap).  ca_comm_unique_id fills 128 bytes that rank 0
+ * hands to the other ranks by any means; ca_comm_init joins the ring on the
+ * current device (world == 1 needs no NCCL); ca_halo_exchange sends
+ * `send_right` to rank r+1 and `send_left` to rank r-1 and receives the
+ * neighbours' counterparts into `recv_left` / `recv_right` (nbytes each,
+ * contiguous device buffers of the caller: gather the halo columns of all
+ * tensors of one exchange into one message), ordered on `stream`.  NCCL is
+ * bound at run time; CA_ERR_COMM reports a missing library or a failed call. */
+int ca_comm_unique_id(void* id128);
+int ca_comm_init(int32_t rank, int32_t world, const void* id128, void** comm);
+int ca_comm_destroy(void* comm);
+int ca_halo_exchange(void* comm, const void* send_left, const void* send_right,
+                     void* recv_left, void* recv_right, size_t nbytes, void* stream);
 
 /* ---------------------------------------------------------------- algebra on values
  * out[n,i,j] = alpha*x[n,i,j] + beta*y[n,i,j] over a flat length (X+Y, X-Y, c*X:

@@ -374,6 +374,21 @@ end
 
 Zygote.accum(x::T, y::T, z::T...) where T <: Circulant = Zygote.accum(Zygote.accum(x, y), z...)   # src/zygote.jl:7
 
+# ------------------------------------------------------------------ multi-GPU ring (no counterpart in the reference)
+# One Julia process per GPU (e.g. under MPI.jl or Distributed): rank 0 makes the id, passes it on, every rank joins.
+ring_unique_id() = (id = zeros(UInt8, 128); check(ccall((:ca_comm_unique_id, LIB), Cint, (Ptr{UInt8},), id)); id)
+function ring_init(rank::Integer, world::Integer, id::Vector{UInt8})
+    h = Ref{Ptr{Cvoid}}(C_NULL)
+    check(ccall((:ca_comm_init, LIB), Cint, (Int32, Int32, Ptr{UInt8}, Ref{Ptr{Cvoid}}), rank, world, id, h))
+    h[]
+end
+ring_destroy(h) = check(ccall((:ca_comm_destroy, LIB), Cint, (Ptr{Cvoid},), h))
+# contiguous device buffers of equal length: my last / first p columns out, the neighbours' in
+halo_exchange!(h, send_left::CuArray, send_right::CuArray, recv_left::CuArray, recv_right::CuArray) =
+    check(ccall((:ca_halo_exchange, LIB), Cint,
+                (Ptr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, Csize_t, Ptr{Cvoid}),
+                h, send_left, send_right, recv_left, recv_right, sizeof(send_left), stream()))
+
 # ------------------------------------------------------------------ algebra and sums (src/array.jl:66-189)
 function axpby(α, X::Circulant, β, Y::Union{Circulant,Nothing})
     out = similar(nzval(X))
