@@ -8,7 +8,7 @@ the work over GPUs.  There is no CPU or PyTorch fallback.
 from . import jl, ops, parallel  # noqa: F401
 from ._lib import CircAttError, LIB_PATH, lib  # noqa: F401
 from .api import (  # noqa: F401
-    AbstractSimilarity, BatchedTranspose, Circulant, CuSparseArrayCSR, DistanceSimilarity, DotSimilarity,
+    AbstractSimilarity, BatchedTranspose, Circulant, LazyAdjacency, CuSparseArrayCSR, DistanceSimilarity, DotSimilarity,
     ENTMAX15, SOFTMAX, Otimes, batched_adjoint, batched_mul, batched_transpose, cat, circulant,
     circulant_adjacency, circulant_adjacency_, circulant_attention, circulant_attention_,
     circulant_mh_adjacency, circulant_mh_attention, circulant_mh_transposed_attention, mix_otimes,

@@ -327,27 +327,27 @@ class _AttentionFn(torch.autograd.Function):
     equal to the composition of the reference's rrules (src/rrules.jl:1-72)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, kind, ws, normalizer, want_A):
+    def forward(ctx, q, k, v, kind, ws, normalizer, want_A, scale=None):
         # the forward's workspace (the packed copy of k and v) is kept for the pullback, like the
         # intermediates the reference's pullback closures capture (src/rrules.jl:44-55)
-        y, nz, stats, fws = ops.attention_fwd(kind, normalizer, q, k, v, ws, want_A, keep_workspace=True)
+        y, nz, stats, fws = ops.attention_fwd(kind, normalizer, q, k, v, ws, want_A, scale=scale, keep_workspace=True)
         ctx.set_materialize_grads(False)      # an unused A must arrive as None, not as zeros, in backward
         ctx.save_for_backward(q, k, v, y, stats, nz if want_A else None)
         ctx.fws = fws if normalizer == 0 else None
-        ctx.cfg = (kind, ws, normalizer, want_A)
+        ctx.cfg = (kind, ws, normalizer, want_A, scale)
         return (y, nz) if want_A else (y, None)
 
     @staticmethod
     def backward(ctx, dy, dnz):
         q, k, v, y, stats, nz = ctx.saved_tensors
-        kind, ws, normalizer, want_A = ctx.cfg
+        kind, ws, normalizer, want_A, scale = ctx.cfg
         if dy is None:
             dy = jl.zeros(y.shape, y.dtype, y.device)
         # the saved A (when the forward materialised it) spares the operator-chain backward a recomputation
-        dq, dk, dv = ops.attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=nz, dA=dnz,
+        dq, dk, dv = ops.attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=nz, dA=dnz, scale=scale,
                                        fwd_workspace=ctx.fws)
         ctx.fws = None
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None
 
 
 # ----------------------------------------------------------------- L2: similarity / adjacency
@@ -400,8 +400,13 @@ def entmax15(A: Circulant) -> Circulant:
     return softmax(A, normalizer=ENTMAX15)
 
 
-def circulant_adjacency(simfun, x, y, W: int, normalizer=SOFTMAX) -> Circulant:
-    """(softmax ∘ circulant_similarity)(simfun, x, y, W)  (src/similarity.jl:157-161)."""
+def circulant_adjacency(simfun, x, y, W: int, normalizer=SOFTMAX, lazy=False):
+    """(softmax ∘ circulant_similarity)(simfun, x, y, W)  (src/similarity.jl:157-161).
+    `lazy=True` returns a LazyAdjacency: nothing is computed until the result is applied or inspected."""
+    if lazy:
+        _check_odd(W)
+        _check_xy(x, y)
+        return LazyAdjacency([(1, simfun, x, y, normalizer)], W, 1, tuple(x.shape[:-2]), x.shape[-1], False)
     return softmax(circulant_similarity(simfun, x, y, W), normalizer)
 
 
@@ -464,8 +469,13 @@ def circulant_mh_attention(*args, normalizer=SOFTMAX, return_A=True):
     return _fused(simfun, q, k, v, W, int(nheads), normalizer, return_A)
 
 
-def circulant_mh_adjacency(simfun, x, y, W: int, nheads: int, normalizer=SOFTMAX) -> Circulant:
-    """src/attention.jl:46-51."""
+def circulant_mh_adjacency(simfun, x, y, W: int, nheads: int, normalizer=SOFTMAX, lazy=False):
+    """src/attention.jl:46-51.  `lazy=True` returns a LazyAdjacency (see there)."""
+    if lazy:
+        _check_odd(W)
+        _check_xy(x, y)
+        assert x.shape[-2] % nheads == 0, f"channels ({x.shape[-2]}) must be divisible by nheads ({nheads})"
+        return LazyAdjacency([(1, simfun, x, y, normalizer)], W, nheads, tuple(x.shape[:-2]), x.shape[-1], True)
     xr, yr = splitheads(x, nheads), splitheads(y, nheads)
     A = circulant_adjacency(simfun, xr, yr, W, normalizer)
     return _circulant_reshape(A, nheads, x.shape[-1])
@@ -487,6 +497,10 @@ def _apply(A: Circulant, x, transpose):
 
 def otimes(A: Circulant, x):
     """y = A ⊗ x (src/attention.jl:53-70)."""
+    if isinstance(A, LazyAdjacency):
+        if A.mh:
+            raise TypeError("A ⊗ x needs a single-head adjacency; use ⨷ (Otimes) for a multi-head one")
+        return A.apply(x)
     return _apply(A, x, False)
 
 
@@ -508,6 +522,10 @@ def circulant_transposed_attention_(y, A: Circulant, x):
 
 def Otimes(A: Circulant, x):
     """y = A ⨷ x: multi-head apply, nheads = size(A, 3) (src/attention.jl:89-94)."""
+    if isinstance(A, LazyAdjacency):
+        if not A.mh:
+            raise TypeError("A ⨷ x needs a 4-dimensional Circulant (Np, Np, nheads, B)")
+        return A.apply(x)
     if A.ndim != 4:
         raise TypeError("A ⨷ x needs a 4-dimensional Circulant (Np, Np, nheads, B)")
     xr = splitheads(x, A.size(3))
@@ -556,6 +574,106 @@ def mix_otimes(terms, x):
     return out
 
 
+class LazyAdjacency:
+    """A linear combination sum_i c_i * adjacency(simfun_i, x_i, y_i) that is only written to memory when
+    somebody looks at its values.
+
+    `circulant_mh_adjacency(..., lazy=True)` / `circulant_adjacency(..., lazy=True)` return one term.  `c * A`,
+    `A * c`, `A + B`, `A - B`, `-A` and `scale(c, A)` (c a number or an array of size (1, 1, h', b') as in
+    src/array.jl:179-186) stay lazy.  Applying the result with `⨷` / `⊗` (Otimes / otimes /
+    circulant_(mh_)attention(A, x)) evaluates sum_i c_i * (A_i applied to x) with the fused flash kernels,
+    i.e. as attention with an unscaled similarity: neither the A_i nor their combination ever exist in memory.
+    This is the pattern of the reference's gradient test and of GroupCDL-style models
+    (test/grad.jl:17-21, 34-38, README.md:126-136), where the reference writes and re-reads three A-sized
+    arrays.  Gradients flow to every x_i, y_i, c_i and to x through the fused pullback.
+    `materialize()` (also taken by `.nzVal`, `.data` and `sum`) builds the ordinary Circulant."""
+
+    def __init__(self, terms, W, nheads, spatial, batch, mh):
+        self.terms = terms                # [(coefficient, simfun, x, y, normalizer)]
+        self.kernel_length, self.nheads, self.spatial_size, self.batch, self.mh = int(W), int(nheads), spatial, batch, mh
+        self._cache = None
+
+    # -- algebra that stays lazy
+    def _with(self, terms):
+        return LazyAdjacency(terms, self.kernel_length, self.nheads, self.spatial_size, self.batch, self.mh)
+
+    def _check(self, other):
+        if not isinstance(other, LazyAdjacency):
+            raise TypeError("a lazy adjacency combines with lazy adjacencies only: materialize() it first")
+        if (other.kernel_length, other.nheads, other.spatial_size, other.batch, other.mh) != \
+                (self.kernel_length, self.nheads, self.spatial_size, self.batch, self.mh):
+            raise TypeError("Circulants must have equal window, spatial size and batch dims")
+
+    @staticmethod
+    def _times(c, d):
+        return d if isinstance(c, (int, float)) and c == 1 else (c if isinstance(d, (int, float)) and d == 1 else c * d)
+
+    def __mul__(self, c):
+        if isinstance(c, torch.Tensor) and c.ndim > 0:
+            if c.ndim != 4 or c.shape[0] != 1 or c.shape[1] != 1:
+                raise TypeError(f"coefficient of size {tuple(c.shape)} does not scale the batch dims of A")
+        return self._with([(self._times(c, term[0]),) + tuple(term[1:]) for term in self.terms])
+
+    __rmul__ = __mul__
+
+    def __neg__(self):
+        return self * -1.0
+
+    def __add__(self, other):
+        self._check(other)
+        return self._with(self.terms + other.terms)
+
+    def __sub__(self, other):
+        return self + (-other)
+
+    # -- evaluation
+    def _units_coeff(self, c, like):
+        """coefficient as one value per unit (head fastest), broadcastable against (spatial..., c, units)"""
+        if not (isinstance(c, torch.Tensor) and c.ndim > 0):
+            return c
+        cb = c[0, 0].expand(self.nheads, self.batch)            # (heads, B); a single-head adjacency has heads == 1
+        cu = cb.t().reshape(-1)                                  # one value per unit, head fastest
+        return cu.reshape((1,) * (like.ndim - 1) + (-1,))
+
+    def apply(self, x):
+        """sum_i c_i * (A_i ⨷ x) on the fused flash kernels (unscaled similarity: the adjacency has no 1/sqrt(c))."""
+        xr = splitheads(x, self.nheads) if self.mh else x
+        out = None
+        for c, simfun, a, b, normalizer in self.terms:
+            ar, br = (splitheads(t, self.nheads) for t in (a, b)) if self.mh else (a, b)
+            y, _ = _AttentionFn.apply(ar, br, xr, _kind(simfun), self.kernel_length, normalizer, False, 1.0)
+            cu = self._units_coeff(c, y)
+            y = y * cu if not (isinstance(cu, (int, float)) and cu == 1) else y
+            out = y if out is None else out + y
+        return jl.reshape(out, tuple(x.shape)) if self.mh else out
+
+    def materialize(self) -> "Circulant":
+        if self._cache is None:
+            out = None
+            for c, simfun, a, b, normalizer in self.terms:
+                A = (circulant_mh_adjacency(simfun, a, b, self.kernel_length, self.nheads, normalizer) if self.mh
+                     else circulant_adjacency(simfun, a, b, self.kernel_length, normalizer))
+                A = scale(c, A) if isinstance(c, torch.Tensor) and c.ndim > 0 else (A if c == 1 else c * A)
+                out = A if out is None else out + A
+            self._cache = out
+        return self._cache
+
+    @property
+    def nzVal(self):
+        return self.materialize().nzVal
+
+    @property
+    def data(self):
+        return self.materialize().data
+
+    @property
+    def shape(self):
+        Np = 1
+        for n in self.spatial_size:
+            Np *= n
+        return (Np, Np, self.nheads, self.batch) if self.mh else (Np, Np, 1, self.batch)
+
+
 class BatchedTranspose:
     """NNlib.batched_transpose(A::Circulant) marker (src/batchedmul.jl:13-19)."""
 
@@ -584,6 +702,8 @@ def batched_mul(A, B):
 # ----------------------------------------------------------------- algebra, sums, cat
 def scale(c, A: Circulant) -> Circulant:
     """scale(c, A): c of size (1, 1, h', b') (src/array.jl:179-186)."""
+    if isinstance(A, LazyAdjacency):
+        return A * c
     if not isinstance(c, torch.Tensor):
         return c * A                                                     # src/array.jl:187
     if c.ndim == 0:
@@ -605,6 +725,8 @@ def dot(X: Circulant, Y: Circulant):
 
 def sum(A: Circulant, dims=None):
     """Base.sum(A::Circulant; dims) (src/array.jl:156-177); dims are 1-based."""
+    if isinstance(A, LazyAdjacency):
+        A = A.materialize()
     nz = A.nzVal
     if dims is None:
         return ops.dot_batch(jl.reshape(nz, (-1,)))[0]

@@ -146,3 +146,47 @@ def test_mix_otimes_equals_materialised_sum(ca):
     assert rel_err(ca.jl.to_numpy(y), ca.jl.to_numpy(y_ref).astype(np.float64)) < TOL
     for a, b in zip(g, g_ref):
         assert rel_err(a, b.astype(np.float64)) < TOL
+
+
+@pytest.mark.parametrize("mh", [False, True])
+@pytest.mark.parametrize("simname", ["dot", "distance"])
+def test_lazy_adjacency_mix_equals_materialised(ca, mh, simname):
+    """The pattern of the reference's gradient test (test/grad.jl:17-21, 34-38): C = α*A + (1-α)*B, z = C ⨷ v.
+    With lazy adjacencies nothing A-sized is ever written; z and every gradient equal the materialised path."""
+    rng = np.random.default_rng(17)
+    shape, W, nheads = (20, 18, 32, 2), 5, (2 if mh else 1)
+    sim = ca.DotSimilarity() if simname == "dot" else ca.DistanceSimilarity()
+    data = [randn(rng, shape, scale=0.5) for _ in range(4)]
+    rn = randn(rng, shape)
+    an = np.asfortranarray(np.array([0.8, 0.3], dtype=np.float32).reshape(1, 1, 1, 2))
+    outs = []
+    for lazy in (False, True):
+        k, q, xx, v = (ca.jl.from_numpy(t).requires_grad_(True) for t in data)
+        alpha = ca.jl.from_numpy(an).requires_grad_(True)
+        before = ca.lib.ca_probe_launch_count()
+        if mh:
+            A = ca.circulant_mh_adjacency(sim, k, q, W, nheads, lazy=lazy)
+            B = ca.circulant_mh_adjacency(sim, xx, xx, W, nheads, lazy=lazy)
+            z = ca.Otimes(alpha * A + (1.0 - alpha) * B, v)
+        else:
+            A = ca.circulant_adjacency(sim, k, q, W, lazy=lazy)
+            B = ca.circulant_adjacency(sim, xx, xx, W, lazy=lazy)
+            z = ca.otimes(alpha * A + (1.0 - alpha) * B, v)
+        (z * ca.jl.from_numpy(rn)).sum().backward()
+        outs.append([ca.jl.to_numpy(t) for t in (z, k.grad, q.grad, xx.grad, v.grad, alpha.grad)])
+        if lazy:
+            assert isinstance(A, ca.LazyAdjacency) and A._cache is None and B._cache is None     # never materialised
+    for name, a, b in zip(("z", "dk", "dq", "dxx", "dv", "dalpha"), *outs):
+        assert rel_err(b, a.astype(np.float64)) < 5 * TOL, name
+
+
+def test_lazy_adjacency_materialises_on_demand(ca):
+    rng = np.random.default_rng(18)
+    x, y = (ca.jl.from_numpy(randn(rng, (12, 10, 8, 2))) for _ in range(2))
+    L = ca.circulant_mh_adjacency(ca.DotSimilarity(), x, y, 5, 2, lazy=True)
+    A = ca.circulant_mh_adjacency(ca.DotSimilarity(), x, y, 5, 2)
+    assert L.shape == tuple(A.shape)
+    assert rel_err(ca.jl.to_numpy((2.0 * L).nzVal), 2.0 * ca.jl.to_numpy(A.nzVal).astype(np.float64)) < TOL
+    assert np.abs(ca.jl.to_numpy(ca.sum(L, dims=2)) - 1.0).max() < 1e-5
+    with pytest.raises(TypeError, match="materialize"):
+        L + A
