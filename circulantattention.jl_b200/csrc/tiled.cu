@@ -1451,6 +1451,94 @@ __global__ void __launch_bounds__(128) pack_kernel(PackArgs a) {
     else pack_body<CPE, NCRT, false>(a);
 }
 
+// Pair packing for one-slab units (8 or 16 real channels) through shared memory: a block gathers 128
+// packed rows of one (column, unit, pair) -- every thread the 2 x NCR channel values of its row, 32
+// independent coalesced loads -- into a [128][36] tile, and the block writes the tile out as one contiguous
+// run of 16-byte stores (consecutive lanes on consecutive addresses: full sectors), where the direct form
+// above writes 64-byte pieces 144 bytes apart.  z slots: one per pair and unit, plus one for the planes.
+template <int CPE, int NCRT, bool BF>
+__device__ __forceinline__ void pack_rows_body(const PackArgs& a, float (*tile)[kRowFloats]) {
+    const Geo& g = a.g;
+    const int rr0 = blockIdx.x * 128, rr = rr0 + threadIdx.x;
+    const int w = blockIdx.y;
+    const int slots = a.npairs + (a.planes ? 1 : 0);
+    const int u = blockIdx.z / slots, slot = blockIdx.z % slots;
+    const bool in_rows = rr < a.Hp;
+    const bool real_row = in_rows && rr < g.H + 2 * a.pp;
+    int pix = 0;
+    if (real_row) {
+        if (g.wsw == 1) {
+            pix = (g.H * w + rr - a.pp) % g.Npk;
+            if (pix < 0) pix += g.Npk;
+        } else {
+            pix = (rr - a.pp + g.H) % g.H + g.H * w;
+        }
+    }
+    if (slot < a.npairs) {
+        float4 vals[8];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const float* src = a.src[2 * slot + t];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int cc = 4 * c;
+                if (!real_row || cc >= NCRT) {
+                    vals[4 * t + c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else if (CPE == 1) {
+                    const int64_t o = goff<1, NCRT>(u, cc, g.Npk, pix);
+                    vals[4 * t + c] = make_float4(ld_real<BF>(src, o), ld_real<BF>(src, o + g.Npk),
+                                                  ld_real<BF>(src, o + 2 * (int64_t)g.Npk),
+                                                  ld_real<BF>(src, o + 3 * (int64_t)g.Npk));
+                } else {
+                    const float2 lo = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCRT>(u, cc, g.Npk, pix)));
+                    const float2 hi = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCRT>(u, cc + 2, g.Npk, pix)));
+                    vals[4 * t + c] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                }
+            }
+        }
+        float4* trow = reinterpret_cast<float4*>(tile[threadIdx.x]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) trow[i] = vals[i];
+        trow[8] = make_float4(0.f, 0.f, 0.f, 0.f);                       // padding words
+        __syncthreads();
+        const int nrows = min(128, a.Hp - rr0);
+        float4* out = reinterpret_cast<float4*>(a.dst[slot] + (((int64_t)u * g.Wk + w) * a.Hp + rr0) * kRowFloats);
+        const float4* tin = reinterpret_cast<const float4*>(&tile[0][0]);
+        for (int i = threadIdx.x; i < nrows * (kRowFloats / 4); i += 128) out[i] = tin[i];
+        return;
+    }
+    if (!in_rows) return;
+    float L = 0.f, D = 0.f;
+    if (real_row) {
+        const int64_t so = (int64_t)u * g.Npk + pix;
+        L = __ldg(a.stats + so) * a.stat_mul;
+        if (a.Din) {
+            D = __ldg(a.Din + so);
+        } else {
+            float dyv[NCRT], yv[NCRT];
+#pragma unroll
+            for (int cc = 0; cc < NCRT; ++cc) {
+                const int64_t o = goff<CPE, NCRT>(u, cc, g.Npk, pix);
+                dyv[cc] = ld_real<BF>(a.dy, o);
+                yv[cc] = ld_real<BF>(a.y, o);
+            }
+#pragma unroll
+            for (int cc = 0; cc < NCRT; ++cc) D = fmaf(dyv[cc], yv[cc], D);
+            if (a.Dout && rr >= a.pp && rr < a.pp + g.H) a.Dout[so] = D;
+        }
+    }
+    const int64_t plane = (int64_t)g.Wk * a.Hp;
+    a.planes[(2 * (int64_t)u) * plane + (int64_t)w * a.Hp + rr] = L;
+    a.planes[(2 * (int64_t)u + 1) * plane + (int64_t)w * a.Hp + rr] = D;
+}
+
+template <int CPE, int NCRT>
+__global__ void __launch_bounds__(128) pack_rows_kernel(PackArgs a) {
+    __shared__ __align__(16) float tile[128][kRowFloats];
+    if (CPE == 1 && a.g.bf16) pack_rows_body<CPE, NCRT, true>(a, tile);
+    else pack_rows_body<CPE, NCRT, false>(a, tile);
+}
+
 // ---------------------------------------------------------------- host side
 struct Padded {
     int pp, Hp;
@@ -1530,6 +1618,19 @@ int launch_pack(const PackArgs& a, cudaStream_t st) {
     const int cr = a.g.cr;
     // beyond the grid limits (very long folded 1-D signals, very many units) the generic kernels run
     if (grid.y > 65535u || grid.z > 65535u) return CA_ERR_UNSUPPORTED;
+    if (!a.single && cr <= 16) {
+        // one-slab pairs: the shared-memory form (one z slot per pair instead of one per tensor)
+        dim3 grid2(grid.x, grid.y, a.g.units * (a.npairs + (a.planes ? 1 : 0)));
+        if (a.g.cpe == 1) {
+            if (cr == 8) pack_rows_kernel<1, 8><<<grid2, 128, 0, st>>>(a);
+            else pack_rows_kernel<1, 16><<<grid2, 128, 0, st>>>(a);
+        } else {
+            if (cr == 8) pack_rows_kernel<2, 8><<<grid2, 128, 0, st>>>(a);
+            else pack_rows_kernel<2, 16><<<grid2, 128, 0, st>>>(a);
+        }
+        CA_CHECK_LAUNCH("pack kernel");
+        return CA_OK;
+    }
 #define CA_PACK(CPEV)                                                        \
     do {                                                                     \
         if (cr == 8) pack_kernel<CPEV, 8><<<grid, 128, 0, st>>>(a);          \
