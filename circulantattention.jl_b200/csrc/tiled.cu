@@ -2021,15 +2021,16 @@ int tiled_attention_bwd_dkdv(const Geo& gin, float scale, int dist, const float*
     return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st);
 }
 
-// Helper stream (one per device) on which the dk/dv sweep of a small problem runs
+// Helper stream (one per host thread and device) on which the dk/dv sweep of a small problem runs
 // next to the dq sweep: neither fills the GPU alone.  It is forked from and joined
-// back to the caller's stream with events, so the caller sees ordinary stream order.
+// back to the caller's stream with events, so the caller sees ordinary stream order.  The
+// stream and its two events belong to the calling host thread, so callers on different threads
+// (and streams) neither share them nor wait for each other.
 struct ForkJoin {
     cudaStream_t side = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr;
 };
-static std::mutex g_fork_mutex;
-static ForkJoin g_fork[64];
+static thread_local ForkJoin g_fork[64];
 
 static ForkJoin* fork_join_for_current_device() {
     int dev = -1;
@@ -2078,7 +2079,6 @@ int tiled_attention_bwd(const Geo& gin, float scale, int dist, const float* q, c
     if (rc) return rc;
     const bool small = (long)g.Np * g.units < 2048L * sm_count();      // fewer than ~4 CTAs per SM per sweep
     if (small && tune_int("CIRCATT_CONCURRENT", 1)) {
-        std::lock_guard<std::mutex> lock(g_fork_mutex);
         ForkJoin* f = fork_join_for_current_device();
         if (f && cudaEventRecord(f->fork, st) == cudaSuccess && cudaStreamWaitEvent(f->side, f->fork, 0) == cudaSuccess) {
             rc = run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, f->side);
