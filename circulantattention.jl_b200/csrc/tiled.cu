@@ -1013,7 +1013,7 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
                                          const u64 (&dy)[NQ][8], u64 (&dq)[NQ][8], const u64 (&nL2)[NQ],
                                          const u64 (&nD2)[NQ], const float (&bq)[NQ], float (&sumds)[NQ],
                                          float (&aux)[NQ], int slab = 0) {
-#pragma unroll 1
+#pragma unroll 2      // two keys in flight: the second key's loads overlap the first key's FMAs
     for (int di = 0; di < ws; ++di) {
         const uint32_t a0 = rowbase + di * (kRowBytes * NS);
         float dp[NQ];
@@ -1777,7 +1777,9 @@ int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q,
     Launch L{};
     const int ns = slabs_of(g);
     if (ns > 1 && mode) return CA_ERR_UNSUPPORTED;             // the entmax variants exist for one-slab units
-    const int nq = mode ? 4 : (ns > 1 ? (g.ws <= 9 ? 2 : 4) : pick_nq(g, 4, 2, "CIRCATT_DQ_NQ"));
+    // two query columns per thread measured faster than four at every size for the softmax dq sweep of one-slab
+    // units (160 registers, three blocks per SM, against 255 and two)
+    const int nq = mode ? 4 : (ns > 1 ? (g.ws <= 9 ? 2 : 4) : tune_int("CIRCATT_DQ_NQ", 2));
     int rc = prepare(g, P, nq, 17 * nq, "CIRCATT_DQ_WARPS", kv, nullptr, &L, mode == 0 && ns == 1, 4, ns);
     if (rc) return rc;
     L.a.scale = scale; L.a.c0 = q; L.a.c1 = dy; L.a.cs0 = stats; L.a.cs1 = D; L.a.o0 = dq; L.a.ostats = Dout;
