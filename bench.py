@@ -687,11 +687,24 @@ def main():
         ops.release_scratch()
         torch.cuda.empty_cache()
         timed = make_timer(torch, flush)
+        # the headline above stands on its own: a failure in one of the side measurements is recorded in its
+        # place instead of costing the whole line (every rank takes the same branch: the failures that can
+        # happen here -- memory, an unsupported shape -- are the same on all ranks)
         if world == 1:
             gen = torch.Generator(device=dev).manual_seed(0)
-            other = {name: time_config(ca, torch, timed, gen, cfg, ffma_tflops) for name, cfg in OTHER_CONFIGS.items()}
-        sharded["units_c5"] = units_c5(ca, torch, dist, dev, world, rank, 2)
-        sharded["band_c5"] = band_c5(ca, torch, dist, dev, world, rank, 3)
+            other = {}
+            for name, cfg in OTHER_CONFIGS.items():
+                try:
+                    other[name] = time_config(ca, torch, timed, gen, cfg, ffma_tflops)
+                except Exception as e:                      # noqa: BLE001
+                    other[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+                    torch.cuda.empty_cache()
+        for name, fn, n_ in (("units_c5", units_c5, 2), ("band_c5", band_c5, 3)):
+            try:
+                sharded[name] = fn(ca, torch, dist, dev, world, rank, n_)
+            except Exception as e:                          # noqa: BLE001
+                sharded[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+                torch.cuda.empty_cache()
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
