@@ -20,7 +20,9 @@ def ext_cols(x, start, width, p):
 @pytest.mark.parametrize("simname", ["dot", "distance"])
 @pytest.mark.parametrize("shape,ws,nheads,world", [((40, 36, 32, 1), 7, 2, 3),     # tiled kernels (16 ch/head)
                                                    ((24, 30, 12, 2), 5, 2, 2),     # generic kernels
-                                                   ((33, 28, 16, 1), 9, 1, 2)])
+                                                   ((33, 28, 16, 1), 9, 1, 2),
+                                                   ((32, 24, 16, 1), 15, 1, 3),    # bands of 8 columns: halo 7 <= band < window 15
+                                                   ((24, 18, 6, 1), 9, 1, 3)])     # the same on the generic kernels (bands of 6, halo 4)
 def test_band_split_equals_full_circular_attention(ca, shape, ws, nheads, world, simname):
     rng = np.random.default_rng(0)
     p = ws // 2
