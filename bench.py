@@ -367,6 +367,7 @@ SLICES = {
     "c2": ((128, 96, 64, 2), 15, 4, 0, 0, False, False, "f32"),
     "c4": ((320, 320, 32, 2), 7, 1, 0, 0, True, True, "c64"),
     "c5": ((1024, 1024, 32, 1), 21, 2, 0, 0, False, False, "f32"),       # two units of config 5 (0.13 GB per tensor)
+    "w7": ((320, 320, 32, 2), 7, 2, 0, 0, False, False, "f32"),          # a 7 x 7 window at 16 channels per head
 }
 
 
@@ -615,6 +616,14 @@ def main():
     keep = [None, None]                 # tensors of a slot stay referenced until its copies have finished
     host_busy = [0.0]                   # host time spent enqueueing (waits for the device excluded)
     losses = []
+    # per slot, made once: the Julia-shaped views of the staging buffer (q, k, v as leaves that require a
+    # gradient, the loss weights) and the views of the output buffer the gradients and the loss are written to
+    slot_in, slot_out = [], []
+    for s_ in range(2):
+        views = [t.permute(3, 2, 1, 0) for t in dev_in[s_]]
+        slot_in.append([v_.detach().requires_grad_(True) for v_ in views[:3]] + [views[3]])
+        slot_out.append([dev_out[s_][j_ * n_el:(j_ + 1) * n_el].view(shape_t).permute(3, 2, 1, 0) for j_ in range(3)]
+                        + [dev_out[s_][3 * n_el:]])
 
     def e2e_step(i):
         slot = i % 2
@@ -628,14 +637,14 @@ def main():
         with torch.cuda.stream(s_cmp):
             s_cmp.wait_event(ev_in[slot])
             s_cmp.wait_event(ev_out[slot])                   # dev_out[slot] has been copied out
-            ins = [t.permute(3, 2, 1, 0) for t in dev_in[slot]]
-            qd, kd, vd = (t.detach().requires_grad_(True) for t in ins[:3])
+            qd, kd, vd, rd = slot_in[slot]
+            qd.grad = kd.grad = vd.grad = None
             yy, _ = ca.circulant_mh_attention(ca.DotSimilarity(), qd, kd, vd, ws, nheads, return_A=False)
-            loss = (yy * ins[3]).sum()
+            loss = (yy * rd).sum()
             loss.backward()
-            for j_, t in enumerate((qd, kd, vd)):
-                dev_out[slot][j_ * n_el:(j_ + 1) * n_el].view(shape_t).copy_(jl.colmajor(t.grad).permute(3, 2, 1, 0))
-            dev_out[slot][3 * n_el:].copy_(loss.detach().reshape(1))
+            for dst_, t in zip(slot_out[slot], (qd, kd, vd)):
+                dst_.copy_(t.grad)
+            slot_out[slot][3].copy_(loss.detach().reshape(1))
             ev_cmp[slot].record(s_cmp)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_cmp[slot])
@@ -683,7 +692,7 @@ def main():
     # ---- the other BASELINE configurations (one GPU) and the sharded config-5 runs (every N)
     other, sharded = None, {}
     if not args.no_other_configs:
-        del q, k, v, r, y, stats, D, sws, dq, dk, dv, dev_in, dev_out, keep
+        del q, k, v, r, y, stats, D, sws, dq, dk, dv, dev_in, dev_out, keep, slot_in, slot_out
         ops.release_scratch()
         torch.cuda.empty_cache()
         timed = make_timer(torch, flush)

@@ -323,31 +323,38 @@ class _ApplyFn(torch.autograd.Function):
 
 
 class _AttentionFn(torch.autograd.Function):
-    """Fused circulant_attention on head-split tensors with a direct pullback
-    equal to the composition of the reference's rrules (src/rrules.jl:1-72)."""
+    """Fused circulant_(mh_)attention with a direct pullback equal to the composition of the reference's
+    rrules (src/rrules.jl:1-72).  The head split (src/attention.jl:44, a reshape) happens inside, so the
+    autograd graph holds one node for the whole call instead of one per reshape."""
 
     @staticmethod
-    def forward(ctx, q, k, v, kind, ws, normalizer, want_A, scale=None):
+    def forward(ctx, q, k, v, kind, ws, normalizer, want_A, scale=None, nheads=1):
+        qr, kr, vr = (splitheads(t, nheads) for t in (q, k, v)) if nheads != 1 else (q, k, v)
         # the forward's workspace (the packed copy of k and v) is kept for the pullback, like the
         # intermediates the reference's pullback closures capture (src/rrules.jl:44-55)
-        y, nz, stats, fws = ops.attention_fwd(kind, normalizer, q, k, v, ws, want_A, scale=scale, keep_workspace=True)
+        y, nz, stats, fws = ops.attention_fwd(kind, normalizer, qr, kr, vr, ws, want_A, scale=scale, keep_workspace=True)
         ctx.set_materialize_grads(False)      # an unused A must arrive as None, not as zeros, in backward
-        ctx.save_for_backward(q, k, v, y, stats, nz if want_A else None)
+        ctx.save_for_backward(qr, kr, vr, y, stats, nz if want_A else None)
         ctx.fws = fws if normalizer == 0 else None
-        ctx.cfg = (kind, ws, normalizer, want_A, scale)
-        return (y, nz) if want_A else (y, None)
+        ctx.cfg = (kind, ws, normalizer, want_A, scale, nheads, tuple(q.shape))
+        yo = jl.reshape(y, tuple(q.shape)) if nheads != 1 else y
+        return (yo, nz) if want_A else (yo, None)
 
     @staticmethod
     def backward(ctx, dy, dnz):
         q, k, v, y, stats, nz = ctx.saved_tensors
-        kind, ws, normalizer, want_A, scale = ctx.cfg
+        kind, ws, normalizer, want_A, scale, nheads, shape = ctx.cfg
         if dy is None:
             dy = jl.zeros(y.shape, y.dtype, y.device)
+        elif nheads != 1:
+            dy = splitheads(dy, nheads)
         # the saved A (when the forward materialised it) spares the operator-chain backward a recomputation
         dq, dk, dv = ops.attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=nz, dA=dnz, scale=scale,
                                        fwd_workspace=ctx.fws)
         ctx.fws = None
-        return dq, dk, dv, None, None, None, None, None
+        if nheads != 1:
+            dq, dk, dv = (jl.reshape(t, shape) for t in (dq, dk, dv))
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 # ----------------------------------------------------------------- L2: similarity / adjacency
@@ -428,9 +435,8 @@ def _fused(simfun, q, k, v, W, nheads, normalizer, return_A):
     if not (q.shape == k.shape == v.shape and q.dtype == k.dtype == v.dtype):
         raise TypeError("q, k, v must have the same element type and size")
     B = q.shape[-1]
-    qr, kr, vr = (splitheads(t, nheads) for t in (q, k, v))
-    y, nz = _AttentionFn.apply(qr, kr, vr, _kind(simfun), int(W), normalizer, bool(return_A))
-    y = jl.reshape(y, tuple(q.shape))
+    assert q.shape[-2] % nheads == 0, f"channels ({q.shape[-2]}) must be divisible by nheads ({nheads})"
+    y, nz = _AttentionFn.apply(q, k, v, _kind(simfun), int(W), normalizer, bool(return_A), None, int(nheads))
     if not return_A:
         return y, None
     nz = jl.reshape(nz, (nz.shape[0], nheads, B))

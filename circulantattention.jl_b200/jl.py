@@ -78,5 +78,12 @@ def reshape(t: torch.Tensor, *shape) -> torch.Tensor:
         known = int(np.prod([s for s in shape if s != -1])) if len(shape) > 1 else 1
         shape[shape.index(-1)] = n // max(known, 1)
     t = colmajor(t)
+    if not (torch.is_grad_enabled() and t.requires_grad):
+        # nothing to differentiate through: one strided view of the same column-major memory
+        strides, acc = [], 1
+        for n_ in shape:
+            strides.append(acc)
+            acc *= n_
+        return t.as_strided(tuple(shape), tuple(strides), t.storage_offset())
     flat = t.permute(_rev(t.ndim)).reshape(tuple(reversed(shape)))
     return flat.permute(_rev(len(shape)))
