@@ -205,6 +205,18 @@ def exchange_halos(xs, p: int, group=None, ring: "Ring" = None):
     return [ext.permute(tuple(range(ext.ndim - 1, -1, -1))) for ext in exts]
 
 
+_SIDE = {}
+
+
+def _side_stream(device):
+    """One helper stream per device for the exchange that overlaps the dq sweep."""
+    s = _SIDE.get(device.index)
+    if s is None:
+        s = torch.cuda.Stream(device=device)
+        _SIDE[device.index] = s
+    return s
+
+
 def exchange_halo(x: torch.Tensor, p: int, group=None) -> torch.Tensor:
     """Extended slab of one tensor (see exchange_halos)."""
     return exchange_halos([x], p, group)[0]
@@ -228,14 +240,32 @@ def band_attention_bwd(kind, q, k, v, y, dy, stats, k_ext, v_ext, ws, group=None
     Wb = q.shape[1]
     H, units = q.shape[0], q.shape[-1]
     D = ops.attention_bwd_pre(kind, normalizer, q, k, v, y, dy, stats, ws)
-    dq = ops.attention_bwd_dq(kind, normalizer, q, k_ext, v_ext, dy, stats, D, ws, band=(Wb + 2 * p, p))
-    if q.dtype == torch.float32:
-        # the two scalar planes ride in the same message as q and dy
-        q_ext, dy_ext, stats_ext, D_ext = exchange_halos(
-            [q, dy, jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group, ring)
+
+    def second_exchange():
+        if q.dtype == torch.float32:
+            # the two scalar planes ride in the same message as q and dy
+            return exchange_halos([q, dy, jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group, ring)
+        return (exchange_halos([q, dy], p, group, ring) +
+                exchange_halos([jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group, ring))
+
+    if q.is_cuda:
+        # the exchange runs on a side stream next to the dq sweep (which needs nothing from the neighbours
+        # beyond the forward's slabs); the dk/dv sweep waits for both
+        main, side = torch.cuda.current_stream(q.device), _side_stream(q.device)
+        ready = torch.cuda.Event()
+        ready.record(main)                                   # q, dy, stats, D are final here
+        dq = ops.attention_bwd_dq(kind, normalizer, q, k_ext, v_ext, dy, stats, D, ws, band=(Wb + 2 * p, p))
+        with torch.cuda.stream(side):
+            side.wait_event(ready)
+            q_ext, dy_ext, stats_ext, D_ext = second_exchange()
+            done = torch.cuda.Event()
+            done.record(side)
+        for t in (q_ext, dy_ext, stats_ext, D_ext):
+            t.record_stream(main)                            # allocated on the side stream, read on the main one
+        main.wait_event(done)
     else:
-        q_ext, dy_ext = exchange_halos([q, dy], p, group, ring)
-        stats_ext, D_ext = exchange_halos([jl.reshape(stats, (H, Wb, units)), jl.reshape(D, (H, Wb, units))], p, group, ring)
+        dq = ops.attention_bwd_dq(kind, normalizer, q, k_ext, v_ext, dy, stats, D, ws, band=(Wb + 2 * p, p))
+        q_ext, dy_ext, stats_ext, D_ext = second_exchange()
     dk, dv = ops.attention_bwd_dkdv(kind, normalizer, q_ext, k, v, dy_ext,
                                     jl.reshape(stats_ext, (H * (Wb + 2 * p), units)),
                                     jl.reshape(D_ext, (H * (Wb + 2 * p), units)), ws, band=(Wb + 2 * p, p))
