@@ -8,7 +8,7 @@ import subprocess
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 OUT = os.path.join(PKG_DIR, "libcircatt_b200.so")
-SOURCES = ["api.cu", "tiled.cu", "static_scratch.cu", "comm.cu"]
+SOURCES = ["api.cu", "tiled.cu", "static_scratch.cu", "comm.cu", "line.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC"]
 

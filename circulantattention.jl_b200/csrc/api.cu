@@ -3,6 +3,7 @@
 #include "rowops.cuh"
 #include "window_generic.cuh"
 #include "tiled.cuh"
+#include "line.cuh"
 
 #include <string.h>
 #include <atomic>
@@ -329,6 +330,7 @@ static bool composed_path(const ca_desc* d, const Geo& g, bool backward = false,
 size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {
     Geo g;
     if (make_geo(d, &g, true)) return 0;
+    if (!want_nz && line_shape_ok(g)) return 0;              // the 1-D kernels stage from the tensors themselves
     if (d->normalizer == CA_ENTMAX15) {
         // scores (unless they are written to nz) followed by the packed operand of the tiled operators
         const bool band = g.Wk != g.W;
@@ -352,6 +354,12 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
     const int dist = d->similarity == CA_DISTANCE;
 
     const bool ent = d->normalizer == CA_ENTMAX15;
+    if (!nz) {
+        // 1-D signals in flash mode: sliding-window kernels, softmax and entmax, no scratch
+        rc = line_attention_fwd(g, d->scale, dist, ent, (const float*)q, (const float*)k, (const float*)v,
+                                (float*)y, stats, st);
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+    }
     if (ent && (rc = no_bf16(g, "ca_attention_fwd with entmax"))) return rc;
     if (ent || (composed_path(d, g) && (nz || workspace))) {
         // scores -> row normaliser (threshold or log-sum-exp per row) -> apply; the scores live in
@@ -508,6 +516,14 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
     if (rc) return rc;
     if (!workspace) { set_error("workspace of ca_attention_bwd_workspace() bytes is NULL"); return CA_ERR_NULL; }
     float* D = (float*)workspace;
+    if (!dA && line_shape_ok(g)) {
+        const bool ent = d->normalizer == CA_ENTMAX15;
+        if (!q || !k || !v || (!ent && !y) || !dy || !stats || !dq || !dk || !dv) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
+        rc = line_attention_bwd(g, d->scale, d->similarity == CA_DISTANCE, ent, (const float*)q, (const float*)k,
+                                (const float*)v, (const float*)y, (const float*)dy, stats, D, (float*)dq, (float*)dk,
+                                (float*)dv, as_stream(stream));
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+    }
     if (d->normalizer == CA_ENTMAX15 && !dA && g.wsw != 1) {
         // fused kernels with the entmax weights recomputed from tau (no A-sized traffic).  2-D only:
         // on folded 1-D signals the three sweeps are shared-memory bound and the generic kernels win.

@@ -14,8 +14,9 @@ extern "C" {
 /* Number of kernels this library has launched in the calling process so far. */
 int64_t ca_probe_launch_count(void);
 
-/* Of those, the launches of the TMA-tiled kernels (the tests use the difference around a call
- * to assert that the call ran on the tiled path and not on the generic kernels). */
+/* Of those, the launches of the fused fast-path kernels: the TMA-tiled ones and the sliding-tile kernels for
+ * 1-D signals (the tests use the difference around a call to assert that the call ran on that path and not
+ * on the generic kernels). */
 int64_t ca_probe_tiled_launch_count(void);
 
 /* Launches one kernel of `blocks` x 256 threads; each thread runs `iters`
