@@ -365,6 +365,8 @@ def units_c5(ca, torch, dist, dev, world, rank, steps):
 SLICES = {
     # small cases of the same kernels for profiler captures: name -> a time_config tuple
     "c2": ((128, 96, 64, 2), 15, 4, 0, 0, False, False, "f32"),
+    "c3": ((16384, 64, 4), 127, 8, 1, 1, False, False, "f32"),           # a quarter of config 3's batch (32 units)
+    "c3s": ((16384, 64, 4), 127, 8, 1, 0, False, False, "f32"),          # the same with softmax
     "c4": ((320, 320, 32, 2), 7, 1, 0, 0, True, True, "c64"),
     "c5": ((1024, 1024, 32, 1), 21, 2, 0, 0, False, False, "f32"),       # two units of config 5 (0.13 GB per tensor)
     "w7": ((320, 320, 32, 2), 7, 2, 0, 0, False, False, "f32"),          # a 7 x 7 window at 16 channels per head

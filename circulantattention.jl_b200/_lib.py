@@ -65,6 +65,7 @@ PROTOTYPES = {
     "ca_attention_bwd_dkdv": (C.c_int, [_D] + [_p] * 11),
     "ca_status_word": (C.c_int, [_p]),
     "ca_stage_timeouts": (C.c_int, [C.POINTER(C.c_int32)]),
+    "ca_entmax_scratch_limit": (C.c_int64, [C.c_int64]),
     "ca_comm_unique_id": (C.c_int, [_p]),
     "ca_comm_init": (C.c_int, [_i32, _i32, _p, C.POINTER(C.c_void_p)]),
     "ca_comm_destroy": (C.c_int, [_p]),

@@ -316,8 +316,7 @@ static size_t score_bytes(const Geo& g) {
 
 // Attention as a chain of the tiled operators (similarity -> row normaliser -> apply, and the
 // reference's own pullback chain of src/rrules.jl backwards) with the scores in scratch memory.
-// Used where no fused tiled kernel exists: entmax (forward; backward of wide or 1-D units) and a
-// cotangent on A.  The scratch is A-sized, so the chain is taken only while A fits Int32 indexing and 4 GiB.
+// Used where no fused kernel exists: entmax with A materialised or with wide units, and a cotangent on A.  The scratch is A-sized, so the chain is taken only while A fits Int32 indexing and 4 GiB.
 static bool composed_path(const ca_desc* d, const Geo& g, bool backward = false, bool has_dA = false) {
     if (g.bf16 || g.Wk != g.W || !tiled_operator_workspace(g)) return false;
     // 1-D windows are long (the scores of a row do not stay in cache between the operators): the
@@ -327,13 +326,30 @@ static bool composed_path(const ca_desc* d, const Geo& g, bool backward = false,
     return d->normalizer == CA_ENTMAX15 || has_dA;
 }
 
+static std::atomic<int64_t> g_entmax_scratch_limit{(int64_t)256 << 20};
+
+int64_t ca_entmax_scratch_limit(int64_t bytes) {
+    if (bytes < 0) return g_entmax_scratch_limit.load(std::memory_order_relaxed);
+    return g_entmax_scratch_limit.exchange(bytes, std::memory_order_relaxed);
+}
+
+// Flash-mode entmax forward on the repeated tiled sweeps instead of the operator chain: when the shape is
+// covered and the chain's score buffer would exceed the limit (or cannot be indexed at all).
+static bool entmax_fwd_on_sweeps(const Geo& g, bool want_nz) {
+    if (want_nz || g.Wk != g.W || !tiled_fwd_entmax_workspace(g)) return false;
+    if ((int64_t)g.Np * g.K > INT32_MAX) return true;
+    return (int64_t)score_bytes(g) > g_entmax_scratch_limit.load(std::memory_order_relaxed);
+}
+
 size_t ca_attention_fwd_workspace(const ca_desc* d, int32_t want_nz) {
     Geo g;
     if (make_geo(d, &g, true)) return 0;
     if (!want_nz && line_shape_ok(g)) return 0;              // the 1-D kernels stage from the tensors themselves
     if (d->normalizer == CA_ENTMAX15) {
-        // scores (unless they are written to nz) followed by the packed operand of the tiled operators
         const bool band = g.Wk != g.W;
+        // flash mode on the fused sweeps: the packed (k|v) and one scalar plane, nothing A-sized
+        if (entmax_fwd_on_sweeps(g, want_nz != 0)) return tiled_fwd_entmax_workspace(g);
+        // otherwise: scores (unless they are written to nz) followed by the packed operand of the tiled operators
         return (want_nz ? 0 : score_bytes(g)) + (band ? 0 : tiled_operator_workspace(g));
     }
     if (composed_path(d, g)) return (want_nz ? 0 : score_bytes(g)) + tiled_operator_workspace(g);
@@ -361,6 +377,12 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
     if (ent && (rc = no_bf16(g, "ca_attention_fwd with entmax"))) return rc;
+    if (ent && workspace && entmax_fwd_on_sweeps(g, nz != nullptr)) {
+        // 2-D (and wide 1-D) flash mode: repeated sweeps of the tiled kernels, the threshold search included
+        rc = tiled_attention_fwd_entmax(g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v,
+                                        (float*)y, stats, workspace, st);
+        if (rc != CA_ERR_UNSUPPORTED) return rc;
+    }
     if (ent || (composed_path(d, g) && (nz || workspace))) {
         // scores -> row normaliser (threshold or log-sum-exp per row) -> apply; the scores live in
         // nz or in the workspace

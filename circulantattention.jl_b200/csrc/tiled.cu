@@ -85,6 +85,7 @@ struct TileArgs {
     int stage_bytes;        // bytes of one stage buffer (multiple of 1024)
     int nsplit;             // 1 or 2 groups of warps sharing the stages of a tile
     int which;              // half of the packed pair a single-tensor kernel streams (0 or 1)
+    int iter;               // entmax threshold search: number of the step (late steps fall back to Newton)
     int row_bytes;          // bytes of one packed pixel row: 144 per 16-channel slab
     int nstages;            // copy stages in flight per part: 2 or 3 (kStages)
     const float* c0;        // centre tensors (reference layout)
@@ -100,6 +101,7 @@ struct TileArgs {
 
 constexpr int kStages = 3;
 constexpr uint32_t kWaitTries = 1u << 20;
+constexpr int kEntmaxFwdSteps = 16;            // launches of the entmax threshold step (settled blocks leave at once)
 
 // Number of CTAs that gave up waiting for a stage copy (stays 0 in a healthy run).
 __device__ int g_stage_timeouts = 0;
@@ -1011,16 +1013,20 @@ __global__ void __launch_bounds__(128, 3) apply_tiled_kernel(TileArgs a, const _
 // =====================================================================
 // MODE 0: softmax, P = 2^chain.  MODE 1: 1.5-entmax, g = max(chain, 0) with the chain = s/2 - tau, dS = g*(dP - D).
 // MODE 2: the entmax pre-pass: only num += g*dP and den += g (in aux and sumds), D = num/den.
+// The same query-owned sweep serves the entmax forward, which has no dy: MODE 3 the row maximum of s/2 (in aux);
+// MODE 4 one step of the threshold search: with t = chain = s/2 - tau, the sum of max(t, 0) (sumds), of its
+// square (aux), the size of the support {t > 0}, its smallest member and the largest t outside (ex[0..2]);
+// MODE 5 the apply: dq (here y) += max(chain, 0)^2 * v.
 template <bool DIST, int MASK, int NQ, int MODE, int NS = 1>
 __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[NQ][8],
                                          const u64 (&dy)[NQ][8], u64 (&dq)[NQ][8], const u64 (&nL2)[NQ],
                                          const u64 (&nD2)[NQ], const float (&bq)[NQ], float (&sumds)[NQ],
-                                         float (&aux)[NQ], int slab = 0) {
+                                         float (&aux)[NQ], float (&ex)[NQ][3], int slab = 0) {
 #pragma unroll 2      // two keys in flight: the second key's loads overlap the first key's FMAs
     for (int di = 0; di < ws; ++di) {
         const uint32_t a0 = rowbase + di * (kRowBytes * NS);
         float dp[NQ];
-        {
+        if (MODE <= 2) {
             u64 v2[8];
             lds_slab16<NS>(a0, 1, slab, v2);
 #pragma unroll
@@ -1049,7 +1055,25 @@ __device__ __forceinline__ void dq_stage(uint32_t rowbase, int ws, int rm, float
 #pragma unroll
                 for (int i = 0; i < 8; ++i) t = fma2(q[r][i], k2[i], t);
                 const float chain = lane_sum<NS>(hsum2(t));
-                if (MODE == 2) {
+                if (MODE == 3) {
+                    aux[r] = fmaxf(aux[r], chain);
+                } else if (MODE == 4) {
+                    const bool in = chain > 0.f;
+                    const float tp = fmaxf(chain, 0.f);
+                    sumds[r] += tp;
+                    aux[r] = fmaf(tp, tp, aux[r]);
+                    ex[r][0] += in ? 1.f : 0.f;
+                    ex[r][1] = fminf(ex[r][1], in ? chain : INFINITY);
+                    ex[r][2] = fmaxf(ex[r][2], in ? -INFINITY : chain);
+                } else if (MODE == 5) {
+                    u64 v2[8];
+                    lds_slab16<NS>(a0, 1, slab, v2);
+                    const float tp = fmaxf(chain, 0.f);
+                    const float w = tp * tp;
+                    const u64 w2 = pack2(w, w);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) dq[r][i] = fma2(w2, v2[i], dq[r][i]);
+                } else if (MODE == 2) {
                     const float gg = fmaxf(chain, 0.f);
                     aux[r] = fmaf(gg, dp[r], aux[r]);
                     sumds[r] += gg;
@@ -1073,6 +1097,20 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
     const int NSTAGES = g.wsw + NQ - 1;
     const int w0 = blockIdx.x * NQ, h0 = blockIdx.y * a.TH, u = blockIdx.z;
     const float sl2 = MODE ? 0.5f * a.scale : a.scale * kLog2e;     // entmax: the chain is s/2 - tau
+    bool settled[NQ];                                               // MODE 4: rows whose threshold is final
+    if (MODE == 4) {
+        // a block whose rows all have their final threshold leaves before any barrier or copy exists
+        // (launched without a stage split and for one-slab units: thread = row)
+        const int hh = h0 + (int)threadIdx.x;
+        bool mine = true;
+#pragma unroll
+        for (int r = 0; r < NQ; ++r) {
+            settled[r] = true;
+            if (hh < g.H && w0 + r < g.W) settled[r] = __ldg(a.cs1 + (int64_t)u * g.Np + hh + g.H * (w0 + r)) != 0.f;
+            mine = mine && settled[r];
+        }
+        if (__syncthreads_and(mine)) return;
+    }
     CA_PIPE_PROLOGUE(false)
     const int slab = NS == 1 ? 0 : (lt % NS);
     const int lr = NS == 1 ? lt : (lt >> 5) * (32 / NS) + (lt & 31) / NS, h = h0 + lr;
@@ -1080,17 +1118,27 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
 
     u64 q[NQ][8], dy[NQ][8], dq[NQ][8];
     load_centre<CPE, NQ, NCRT>(a.c0, g, u, h, w0, active, sl2, q, 16 * slab);
-    load_centre<CPE, NQ, NCRT>(a.c1, g, u, h, w0, active, 1.f, dy, 16 * slab);
+    if (MODE <= 2) {
+        load_centre<CPE, NQ, NCRT>(a.c1, g, u, h, w0, active, 1.f, dy, 16 * slab);
+    } else {
+#pragma unroll
+        for (int r = 0; r < NQ; ++r)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dy[r][i] = zero2();
+    }
     u64 nL2[NQ], nD2[NQ];
-    float bq[NQ], sumds[NQ], aux[NQ];
+    float bq[NQ], sumds[NQ], aux[NQ], ex[NQ][3];
 #pragma unroll
     for (int r = 0; r < NQ; ++r) {
         const bool ok = active && (w0 + r < g.W) && slab == 0;       // row scalars enter the lane sums once
         const int64_t o = (int64_t)u * g.Np + h + g.H * (w0 + r);
-        nL2[r] = pack2(ok ? -__ldg(a.cs0 + o) * (MODE ? 1.f : kLog2e) : 0.f, 0.f);
-        nD2[r] = pack2((ok && MODE != 2) ? -__ldg(a.cs1 + o) : 0.f, 0.f);
+        nL2[r] = pack2((ok && MODE != 3) ? -__ldg(a.cs0 + o) * (MODE ? 1.f : kLog2e) : 0.f, 0.f);
+        nD2[r] = pack2((ok && MODE <= 1) ? -__ldg(a.cs1 + o) : 0.f, 0.f);
         sumds[r] = 0.f;
-        aux[r] = 0.f;
+        aux[r] = MODE == 3 ? -INFINITY : 0.f;
+        ex[r][0] = 0.f;
+        ex[r][1] = INFINITY;
+        ex[r][2] = -INFINITY;
         bq[r] = 0.f;
         if (DIST) {
             u64 n = zero2();
@@ -1105,9 +1153,40 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
     CA_PIPE_LOOP({
         const int mask = stage_mask<NQ>(s, radius_w(g));
         CA_MASK_SWITCH(((1 << NQ) - 1), mask, (dq_stage<DIST, MK, NQ, MODE, NS>(smem_u32(pipe.vec(buf)) + (lr + a.roff) * (kRowBytes * NS), g.ws, mask,
-                                                     sl2, q, dy, dq, nL2, nD2, bq, sumds, aux, slab)));
+                                                     sl2, q, dy, dq, nL2, nD2, bq, sumds, aux, ex, slab)));
     })
 
+    if (MODE == 3) {
+        // first threshold of the search: tau >= max - 1 always
+#pragma unroll
+        for (int r = 0; r < NQ; ++r)
+            if (active && slab == 0 && w0 + r < g.W)
+                a.ostats[(int64_t)u * g.Np + h + g.H * (w0 + r)] = aux[r] - 1.f + ca_poison;
+        return;
+    }
+    if (MODE == 4) {
+        // the quadratic sum_S (t - d)^2 = 1 solved on the support S of the current tau; final when tau + d has
+        // the same support and the step was short against the distances it was computed from
+#pragma unroll
+        for (int r = 0; r < NQ; ++r)
+            if (active && slab == 0 && w0 + r < g.W && !settled[r]) {
+                const int64_t o = (int64_t)u * g.Np + h + g.H * (w0 + r);
+                const float n = ex[r][0], sa = sumds[r], sb = aux[r];
+                float d = 0.f;
+                bool same = true;
+                if (n > 0.f) {
+                    const float disc = fmaxf(fmaf(sa, sa, -n * (sb - 1.f)), 0.f);
+                    d = (sa - sqrtf(disc)) / n;
+                    same = (d >= 0.f ? d < ex[r][1] : d >= ex[r][2]) && d * n <= 0.5f * sa;
+                    if (!same && a.iter >= 10) d = 0.5f * (sb - 1.f) / sa;     // late steps: Newton on the convex sum
+                }
+                float ntau, zero;
+                unpack2(nL2[r], ntau, zero);
+                a.ostats[o] = d - ntau + ca_poison;
+                a.o1[o] = same ? 1.f : 0.f;
+            }
+        return;
+    }
     if (MODE == 2) {
         // pre-pass of the entmax pullback: D = sum g*dP / sum g per query row (launched without a stage split)
 #pragma unroll
@@ -1152,8 +1231,13 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) dq_tiled_kernel(TileAr
                     float x, y, qx, qy;
                     unpack2(dq[r][i], x, y);
                     unpack2(q[r][i], qx, qy);
-                    x = a.scale * x - (DIST ? sumds[r] * qx * qfac : 0.f) + ca_poison;
-                    y = a.scale * y - (DIST ? sumds[r] * qy * qfac : 0.f) + ca_poison;
+                    if (MODE == 5) {
+                        x += ca_poison;
+                        y += ca_poison;
+                    } else {
+                        x = a.scale * x - (DIST ? sumds[r] * qx * qfac : 0.f) + ca_poison;
+                        y = a.scale * y - (DIST ? sumds[r] * qy * qfac : 0.f) + ca_poison;
+                    }
                     store_centre<CPE, NCRV, BF>(a.o0, g, u, h, w0, active, r, i, x, y);
                 }
             })
@@ -1780,6 +1864,7 @@ int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q,
     Launch L{};
     const int ns = slabs_of(g);
     if (ns > 1 && mode) return CA_ERR_UNSUPPORTED;             // the entmax variants exist for one-slab units
+    if (mode >= 3) return CA_ERR_UNSUPPORTED;                  // the forward's sweeps go through run_entmax_fwd_sweep
     // two query columns per thread measured faster than four at every size for the softmax dq sweep of one-slab
     // units (160 registers, three blocks per SM, against 255 and two)
     const int nq = mode ? 4 : (ns > 1 ? (g.ws <= 9 ? 2 : 4) : tune_int("CIRCATT_DQ_NQ", 2));
@@ -1795,6 +1880,23 @@ int run_dq(const Geo& g, const Padded& P, float scale, int dist, const float* q,
     else if (nq == 2) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 2, 0, 16, L, st);
     else CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 0, 16, L, st);
     CA_CHECK_LAUNCH("tiled dq kernel");
+    return CA_OK;
+}
+
+// One sweep of the entmax forward over the packed (k|v): mode 3 row maximum -> first threshold (tau),
+// 4 one step of the threshold search (tau and `settled` updated in place), 5 y = sum max(s/2 - tau, 0)^2 v.
+int run_entmax_fwd_sweep(const Geo& g, const Padded& P, float scale, int dist, const float* q, const float* kv,
+                         float* tau, float* settled, float* y, int mode, int iter, cudaStream_t st) {
+    Launch L{};
+    if (slabs_of(g) > 1) return CA_ERR_UNSUPPORTED;
+    int rc = prepare(g, P, 4, 17 * 4, "CIRCATT_DQ_WARPS", kv, nullptr, &L, false, 4, 1);
+    if (rc) return rc;
+    L.a.scale = scale; L.a.c0 = q; L.a.cs0 = tau; L.a.cs1 = settled; L.a.o0 = y; L.a.o1 = settled; L.a.ostats = tau;
+    L.a.iter = iter;
+    if (mode == 3) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 3, 16, L, st);
+    else if (mode == 4) CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 4, 16, L, st);
+    else CA_DIST_CPE_NQ(dq_tiled_kernel, dist, g.cpe, 4, 5, 16, L, st);
+    CA_CHECK_LAUNCH("tiled entmax forward sweep");
     return CA_OK;
 }
 
@@ -2126,6 +2228,42 @@ int tiled_attention_bwd_entmax(const Geo& gin, float scale, int dist, const floa
     if ((rc = launch_pack(pb, st))) return rc;
     if ((rc = run_dq(g, P, scale, dist, q, dy, stats, D, kv, dq, st, 1))) return rc;
     return run_dkdv(g, P, scale, dist, k, v, qdy, planes, dk, dv, st, true);
+}
+
+// The 1.5-entmax forward in flash mode without A-sized memory: the packed (k|v) is swept once for the row
+// maxima, a fixed number of times for the thresholds (blocks whose rows are all final leave at once) and once
+// for y.  `stats` (nullable) receives tau and doubles as the search's state; the `settled` plane and a tau plane
+// for callers without `stats` live behind the pair in the workspace (tiled_fwd_entmax_workspace bytes).
+size_t tiled_fwd_entmax_workspace(const Geo& gin) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return 0;
+    if (!tiled_shape_ok(g) || g.bf16 || slabs_of(g) > 1) return 0;
+    return padded_of(g).pair_floats * sizeof(float) + 2 * (size_t)g.Np * g.units * sizeof(float);
+}
+
+int tiled_attention_fwd_entmax(const Geo& gin, float scale, int dist, const float* q, const float* k, const float* v,
+                               float* y, float* stats, void* workspace, cudaStream_t st) {
+    Geo g;
+    if (!fold_geo(gin, &g)) return CA_ERR_UNSUPPORTED;
+    if (!tiled_shape_ok(g) || g.Wk != g.W || g.bf16 || slabs_of(g) > 1) return CA_ERR_UNSUPPORTED;
+    if (!workspace) return CA_ERR_UNSUPPORTED;
+    const Padded P = padded_of(g);
+    float* kv = static_cast<float*>(workspace);
+    float* settled = kv + P.pair_floats;
+    if (!stats) stats = settled + (size_t)g.Np * g.units;       // a caller that does not want tau
+    PackArgs pa{};
+    pa.g = g; pa.pp = P.pp; pa.Hp = P.Hp; pa.npairs = 1;
+    pa.src[0] = k; pa.src[1] = v; pa.dst[0] = kv;
+    int rc = launch_pack(pa, st);
+    if (rc) return rc;
+    cudaError_t e = cudaMemsetAsync(settled, 0, (size_t)g.Np * g.units * sizeof(float), st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync");
+    if ((rc = run_entmax_fwd_sweep(g, P, scale, dist, q, kv, stats, settled, nullptr, 3, 0, st))) return rc;
+    // the support iteration ends after 3-5 steps on ordinary rows; the steps past the tenth are Newton steps,
+    // which converge for every row
+    for (int it = 0; it < kEntmaxFwdSteps; ++it)
+        if ((rc = run_entmax_fwd_sweep(g, P, scale, dist, q, kv, stats, settled, nullptr, 4, it, st))) return rc;
+    return run_entmax_fwd_sweep(g, P, scale, dist, q, kv, stats, settled, y, 5, 0, st);
 }
 
 // ---------------------------------------------------------------- stand-alone operators

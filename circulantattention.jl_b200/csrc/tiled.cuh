@@ -27,6 +27,11 @@ int tiled_attention_bwd_dkdv(const Geo& g, float scale, int dist, const float* q
 int tiled_attention_bwd_entmax(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
                                const float* dy, const float* stats, float* D, float* dq, float* dk, float* dv,
                                void* workspace, cudaStream_t st);
+// The 1.5-entmax forward in flash mode (y and stats = tau) by repeated sweeps over the packed (k|v): no
+// A-sized memory.  One-slab units only; workspace of tiled_fwd_entmax_workspace bytes (0: shape not covered).
+size_t tiled_fwd_entmax_workspace(const Geo& g);
+int tiled_attention_fwd_entmax(const Geo& g, float scale, int dist, const float* q, const float* k, const float* v,
+                               float* y, float* stats, void* workspace, cudaStream_t st);
 // Copies the count of stage-copy timeouts to the host (synchronises the device).
 int tiled_stage_timeouts(int* count);
 // Launches the one-CTA self test of the bounded stage wait (`out`: nullable device int, 1 = the wait ran out).

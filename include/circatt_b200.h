@@ -210,6 +210,14 @@ int ca_attention_bwd_dkdv(const ca_desc* d, const void* q, const void* k, const 
 int ca_status_word(int32_t* device_word);
 int ca_stage_timeouts(int32_t* count);
 
+/* The 1.5-entmax forward in flash mode (nz == NULL) has two routes on 2-D problems of 8 or 16 real channels
+ * per unit: the operator chain (scores -> threshold -> apply) on an A-sized scratch buffer, which is the
+ * faster one while that buffer is small, and repeated sweeps of the fused tiled kernels (row maximum, a few
+ * steps of the threshold search, apply), which need only the packed (k|v) and two scalar planes.  The chain
+ * is taken while its scratch stays within this limit (default 256 MiB); ca_attention_fwd_workspace follows
+ * the same rule.  Sets the limit when `bytes` >= 0 and returns the previous one (process-wide). */
+int64_t ca_entmax_scratch_limit(int64_t bytes);
+
 /* ---------------------------------------------------------------- multi-GPU halo exchange
  * Band split of very large images (no counterpart in the reference, which is a
  * single-device package): one process per GPU owns a band of columns and needs
