@@ -287,6 +287,12 @@ def attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=None, dA=None,
     return dq, dk, dv
 
 
+def entmax_scratch_limit(nbytes: int = -1) -> int:
+    """Largest A-sized scratch (bytes) the flash-mode entmax forward may use before it switches to the
+    scratch-free sweeps; sets it when `nbytes` >= 0.  Returns the previous limit."""
+    return int(lib.ca_entmax_scratch_limit(int(nbytes)))
+
+
 # ------------------------------------------------------------------ algebra
 def axpby(alpha, x, beta=0.0, y=None):
     require_cuda(x, y)

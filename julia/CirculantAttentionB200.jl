@@ -38,6 +38,14 @@ simcode(::DotSimilarity) = Int32(0)
 simcode(::DistanceSimilarity) = Int32(1)
 
 lasterror() = unsafe_string(ccall((:ca_last_error, LIB), Cstring, ()))
+
+"""
+    entmax_scratch_limit!(bytes) -> previous limit
+
+Largest A-sized scratch buffer (bytes) the flash-mode 1.5-entmax forward may use; larger problems run on
+repeated sweeps of the fused kernels, which need no A-sized memory.  A negative argument only queries.
+"""
+entmax_scratch_limit!(bytes::Integer) = ccall((:ca_entmax_scratch_limit, LIB), Int64, (Int64,), bytes)
 check(rc::Integer) = rc == 0 ? nothing : throw(ErrorException("circatt_b200 status $rc: $(lasterror())"))
 stream() = CUDA.stream().handle
 
