@@ -29,6 +29,16 @@ class ca_desc(C.Structure):
     ]
 
 
+class ca_chunk_job(C.Structure):
+    _fields_ = [
+        ("src", C.c_void_p), ("dst", C.c_void_p), ("chunk_bytes", C.c_int64), ("nchunks", C.c_int64),
+        ("src_stride_bytes", C.c_int64), ("dst_stride_bytes", C.c_int64),
+    ]
+
+
+CA_MAX_CHUNK_JOBS = 32
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -70,6 +80,7 @@ PROTOTYPES = {
     "ca_comm_init": (C.c_int, [_i32, _i32, _p, C.POINTER(C.c_void_p)]),
     "ca_comm_destroy": (C.c_int, [_p]),
     "ca_halo_exchange": (C.c_int, [_p, _p, _p, _p, _p, C.c_size_t, _p]),
+    "ca_copy_chunks": (C.c_int, [C.POINTER(ca_chunk_job), _i32, _p]),
     "ca_axpby": (C.c_int, [_i64, _f32, _p, _f32, _p, _p, _p]),
     "ca_scale_batch": (C.c_int, [_i64, _i32, _i32, _p, _i32, _i32, _p, _i32, _i32, _p, _p]),
     "ca_dot_batch": (C.c_int, [_i64, _i32, _i32, _p, _i32, _i32, _p, _i32, _i32, _p, _p]),

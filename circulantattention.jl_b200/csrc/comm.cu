@@ -10,6 +10,7 @@
 #include <dlfcn.h>
 #include <string.h>
 #include <nccl.h>
+#include <algorithm>
 #include <mutex>
 
 namespace ca {
@@ -26,6 +27,47 @@ struct NcclApi {
     ncclResult_t (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
 };
+
+// Several strided copies in one launch: job j copies nchunks pieces of chunk_bytes from src (pieces
+// src_stride_bytes apart) to dst (dst_stride_bytes apart).  Block (x, j) walks the 32 KB segments x, x + gridDim.x,
+// ... of job j's pieces; 16-byte accesses when every address of the job allows them.
+struct ChunkJobs {
+    ca_chunk_job job[CA_MAX_CHUNK_JOBS];
+    int n;
+};
+
+constexpr int64_t kChunkSegment = 32 * 1024;      // bytes one block copies at a time
+
+__global__ void __launch_bounds__(256) copy_chunks_kernel(const __grid_constant__ ChunkJobs jobs) {
+    const ca_chunk_job& b = jobs.job[blockIdx.y];
+    const char* src = static_cast<const char*>(b.src);
+    char* dst = static_cast<char*>(b.dst);
+    const bool wide = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | (uintptr_t)b.chunk_bytes |
+                        (uintptr_t)b.src_stride_bytes | (uintptr_t)b.dst_stride_bytes) & 15) == 0;
+    const bool words = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | (uintptr_t)b.chunk_bytes |
+                         (uintptr_t)b.src_stride_bytes | (uintptr_t)b.dst_stride_bytes) & 3) == 0;
+    // work items: (piece, 32 KB segment of the piece)
+    const int64_t segs = (b.chunk_bytes + kChunkSegment - 1) / kChunkSegment;
+    const int64_t items = b.nchunks * segs;
+    for (int64_t it = blockIdx.x; it < items; it += gridDim.x) {
+        const int64_t c = it / segs, sg = it - c * segs;
+        const int64_t begin = sg * kChunkSegment;
+        const int64_t len = min(kChunkSegment, b.chunk_bytes - begin);
+        const char* s = src + c * b.src_stride_bytes + begin;
+        char* d = dst + c * b.dst_stride_bytes + begin;
+        if (wide) {
+            const int64_t n = len >> 4;
+            for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
+                reinterpret_cast<uint4*>(d)[i] = __ldg(reinterpret_cast<const uint4*>(s) + i);
+        } else if (words) {
+            const int64_t n = len >> 2;
+            for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
+                reinterpret_cast<uint32_t*>(d)[i] = __ldg(reinterpret_cast<const uint32_t*>(s) + i);
+        } else {
+            for (int64_t i = threadIdx.x; i < len; i += blockDim.x) d[i] = s[i];
+        }
+    }
+}
 
 std::mutex g_nccl_mutex;
 NcclApi g_nccl;
@@ -121,6 +163,27 @@ int ca_comm_destroy(void* comm) {
     }
     delete c;
     return rc;
+}
+
+int ca_copy_chunks(const ca_chunk_job* jobs, int32_t njobs, void* stream) {
+    if (njobs < 0 || njobs > CA_MAX_CHUNK_JOBS) { set_error("njobs=%d outside 0..%d", njobs, CA_MAX_CHUNK_JOBS); return CA_ERR_BAD_DESC; }
+    if (njobs == 0) return CA_OK;
+    if (!jobs) { set_error("jobs is NULL"); return CA_ERR_NULL; }
+    ChunkJobs pack{};
+    int64_t most = 0;
+    for (int j = 0; j < njobs; ++j) {
+        const ca_chunk_job& b = jobs[j];
+        if (b.chunk_bytes < 0 || b.nchunks < 0) { set_error("job %d has a negative size", j); return CA_ERR_BAD_DESC; }
+        if (b.chunk_bytes > 0 && b.nchunks > 0 && (!b.src || !b.dst)) { set_error("job %d has a NULL buffer", j); return CA_ERR_NULL; }
+        pack.job[j] = b;
+        most = std::max(most, b.nchunks * ((b.chunk_bytes + kChunkSegment - 1) / kChunkSegment));
+    }
+    pack.n = njobs;
+    if (most == 0) return CA_OK;
+    const dim3 grid((unsigned)std::min<int64_t>(most, 148 * 8), (unsigned)njobs);
+    copy_chunks_kernel<<<grid, 256, 0, as_stream(stream)>>>(pack);
+    CA_CHECK_LAUNCH("chunk copy kernel");
+    return CA_OK;
 }
 
 int ca_halo_exchange(void* comm, const void* send_left, const void* send_right, void* recv_left, void* recv_right,

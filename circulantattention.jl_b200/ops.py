@@ -287,6 +287,16 @@ def attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=None, dA=None,
     return dq, dk, dv
 
 
+def copy_chunks(jobs):
+    """Several strided device copies in one launch (ca_copy_chunks).  `jobs`: tuples
+    (src_ptr, dst_ptr, chunk_bytes, nchunks, src_stride_bytes, dst_stride_bytes) with integer addresses;
+    longer lists are split into launches of CA_MAX_CHUNK_JOBS."""
+    for i in range(0, len(jobs), _lib.CA_MAX_CHUNK_JOBS):
+        part = jobs[i:i + _lib.CA_MAX_CHUNK_JOBS]
+        arr = (_lib.ca_chunk_job * len(part))(*[_lib.ca_chunk_job(*j) for j in part])
+        check(lib.ca_copy_chunks(arr, len(part), _stream()))
+
+
 def entmax_scratch_limit(nbytes: int = -1) -> int:
     """Largest A-sized scratch (bytes) the flash-mode entmax forward may use before it switches to the
     scratch-free sweeps; sets it when `nbytes` >= 0.  Returns the previous limit."""

@@ -146,6 +146,7 @@ def exchange_halos(xs, p: int, group=None, ring: "Ring" = None):
     if not xs:
         return []
     ts, exts = [], []
+    on_gpu = xs[0].is_cuda
     for x in xs:
         if x.ndim < 2:
             raise ValueError("expected a (H, W, ...) tensor")
@@ -156,31 +157,65 @@ def exchange_halos(xs, p: int, group=None, ring: "Ring" = None):
             raise TypeError("tensors of one exchange must share dtype and device")
         t = _cview(x)                                        # (..., Wb, H)
         ext = torch.empty(t.shape[:-2] + (Wb + 2 * p, t.shape[-1]), dtype=t.dtype, device=t.device)
-        ext.narrow(-2, p, Wb).copy_(t)
+        if not on_gpu:
+            ext.narrow(-2, p, Wb).copy_(t)
         ts.append(t)
         exts.append(ext)
     if ring is not None:
         world = ring.world
     else:
         world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    dtype, device = ts[0].dtype, ts[0].device
+    esize = ts[0].element_size()
+    sizes = [t.numel() // t.shape[-2] * p for t in ts]
+    total = sum(sizes)
+
+    def geometry(t):
+        """(trailing index count, bytes of one column, band columns) of a (..., Wb, H) view."""
+        Wb, H = t.shape[-2], t.shape[-1]
+        return t.numel() // (Wb * H), H * esize, Wb
+
     if world == 1:
-        for t, ext in zip(ts, exts):
-            Wb = t.shape[-2]
-            ext.narrow(-2, 0, p).copy_(t.narrow(-2, Wb - p, p))
-            ext.narrow(-2, p + Wb, p).copy_(t.narrow(-2, 0, p))
+        if on_gpu:
+            # one launch: the bands into their slabs, and the wrapped columns into the halos
+            jobs = []
+            for t, ext in zip(ts, exts):
+                outer, col, Wb = geometry(t)
+                src, dst, ss, ds = t.data_ptr(), ext.data_ptr(), Wb * col, (Wb + 2 * p) * col
+                jobs.append((src, dst + p * col, Wb * col, outer, ss, ds))
+                jobs.append((src + (Wb - p) * col, dst, p * col, outer, ss, ds))
+                jobs.append((src, dst + (p + Wb) * col, p * col, outer, ss, ds))
+            with ops._on_device(device):
+                ops.copy_chunks(jobs)
+        else:
+            for t, ext in zip(ts, exts):
+                Wb = t.shape[-2]
+                ext.narrow(-2, 0, p).copy_(t.narrow(-2, Wb - p, p))
+                ext.narrow(-2, p + Wb, p).copy_(t.narrow(-2, 0, p))
     else:
-        dtype, device = ts[0].dtype, ts[0].device
-        sizes = [t.numel() // t.shape[-2] * p for t in ts]
-        total = sum(sizes)
         to_right, to_left = _staging("to_right", total, dtype, device), _staging("to_left", total, dtype, device)
         from_left, from_right = _staging("from_left", total, dtype, device), _staging("from_right", total, dtype, device)
-        off = 0
-        for t, n in zip(ts, sizes):
-            Wb = t.shape[-2]
-            shape = t.shape[:-2] + (p, t.shape[-1])
-            to_right[off:off + n].view(shape).copy_(t.narrow(-2, Wb - p, p))   # the right neighbour's left halo
-            to_left[off:off + n].view(shape).copy_(t.narrow(-2, 0, p))         # the left neighbour's right halo
-            off += n
+        if on_gpu:
+            # one launch gathers the outgoing columns of every tensor into the two messages and copies the
+            # bands into their slabs; one more scatters the incoming columns
+            jobs, off = [], 0
+            for t, ext, n in zip(ts, exts, sizes):
+                outer, col, Wb = geometry(t)
+                src, ss = t.data_ptr(), Wb * col
+                jobs.append((src, ext.data_ptr() + p * col, Wb * col, outer, ss, (Wb + 2 * p) * col))
+                jobs.append((src + (Wb - p) * col, to_right.data_ptr() + off * esize, p * col, outer, ss, p * col))
+                jobs.append((src, to_left.data_ptr() + off * esize, p * col, outer, ss, p * col))
+                off += n
+            with ops._on_device(device):
+                ops.copy_chunks(jobs)
+        else:
+            off = 0
+            for t, n in zip(ts, sizes):
+                Wb = t.shape[-2]
+                shape = t.shape[:-2] + (p, t.shape[-1])
+                to_right[off:off + n].view(shape).copy_(t.narrow(-2, Wb - p, p))   # the right neighbour's left halo
+                to_left[off:off + n].view(shape).copy_(t.narrow(-2, 0, p))         # the left neighbour's right halo
+                off += n
         if ring is not None:
             ring.exchange(to_left, to_right, from_left, from_right)
         else:
@@ -195,13 +230,24 @@ def exchange_halos(xs, p: int, group=None, ring: "Ring" = None):
             ])
             for r in reqs:
                 r.wait()
-        off = 0
-        for t, ext, n in zip(ts, exts, sizes):
-            Wb = t.shape[-2]
-            shape = t.shape[:-2] + (p, t.shape[-1])
-            ext.narrow(-2, 0, p).copy_(from_left[off:off + n].view(shape))
-            ext.narrow(-2, p + Wb, p).copy_(from_right[off:off + n].view(shape))
-            off += n
+        if on_gpu:
+            jobs, off = [], 0
+            for t, ext, n in zip(ts, exts, sizes):
+                outer, col, Wb = geometry(t)
+                ds = (Wb + 2 * p) * col
+                jobs.append((from_left.data_ptr() + off * esize, ext.data_ptr(), p * col, outer, p * col, ds))
+                jobs.append((from_right.data_ptr() + off * esize, ext.data_ptr() + (p + Wb) * col, p * col, outer, p * col, ds))
+                off += n
+            with ops._on_device(device):
+                ops.copy_chunks(jobs)
+        else:
+            off = 0
+            for t, ext, n in zip(ts, exts, sizes):
+                Wb = t.shape[-2]
+                shape = t.shape[:-2] + (p, t.shape[-1])
+                ext.narrow(-2, 0, p).copy_(from_left[off:off + n].view(shape))
+                ext.narrow(-2, p + Wb, p).copy_(from_right[off:off + n].view(shape))
+                off += n
     return [ext.permute(tuple(range(ext.ndim - 1, -1, -1))) for ext in exts]
 
 

@@ -231,6 +231,23 @@ int64_t ca_entmax_scratch_limit(int64_t bytes);
  * tensors of one exchange into one message), ordered on `stream`.  NCCL is
  * bound at run time; CA_ERR_COMM reports a missing library or a failed call. */
 int ca_comm_unique_id(void* id128);
+
+/* Several strided device-to-device copies in ONE launch: job j copies `nchunks` pieces of `chunk_bytes` bytes,
+ * `src_stride_bytes` apart at the source and `dst_stride_bytes` apart at the destination.  The halo columns
+ * of a column-major (H, W, ...) tensor are such pieces (H*p elements per trailing index, H*W elements
+ * apart), so one call gathers the outgoing halos of all tensors of an exchange into the two messages (and
+ * copies the bands into their extended slabs), and a second one scatters the incoming halos.  `jobs` is a
+ * HOST array of at most CA_MAX_CHUNK_JOBS entries (it is passed to the kernel by value). */
+#define CA_MAX_CHUNK_JOBS 32
+typedef struct ca_chunk_job {
+    const void* src;
+    void* dst;
+    int64_t chunk_bytes;
+    int64_t nchunks;
+    int64_t src_stride_bytes;
+    int64_t dst_stride_bytes;
+} ca_chunk_job;
+int ca_copy_chunks(const ca_chunk_job* jobs, int32_t njobs, void* stream);
 int ca_comm_init(int32_t rank, int32_t world, const void* id128, void** comm);
 int ca_comm_destroy(void* comm);
 int ca_halo_exchange(void* comm, const void* send_left, const void* send_right,

@@ -75,3 +75,30 @@ def test_band_driver_single_rank(ca):
     dqo, dko, dvo = orc.mh_attention_pullback(orc.DOT, up(qn), up(kn), up(vn), ws, nheads, up(rn))
     for got, want in ((y, yo), (dq, dqo), (dk, dko), (dv, dvo)):
         assert rel_err(ca.jl.to_numpy(got), want) < TOL
+
+
+@pytest.mark.parametrize("dtype,H", [(torch.float32, 64), (torch.float32, 37), (torch.bfloat16, 33), (torch.uint8, 13)])
+def test_copy_chunks_gathers_strided_columns(ca, dtype, H):
+    """ca_copy_chunks: several strided copies in one launch (16-byte, 4-byte and byte paths), checked against
+    torch slicing: the halo columns of two tensors gathered into one message, and a band copied into its slab."""
+    torch.manual_seed(0)
+    W, p, outer = 24, 3, 5
+    mk = lambda *shape: (torch.randn(*shape, device="cuda") * 50).to(dtype)
+    a, b = mk(outer, W, H), mk(2 * outer, W, H)                   # C-order views of (H, W, outer) tensors
+    es = a.element_size()
+    col = H * es
+    msg = torch.zeros((outer + 2 * outer) * p * H, dtype=dtype, device="cuda")
+    ext = torch.zeros(outer, W + 2 * p, H, dtype=dtype, device="cuda")
+    jobs = [
+        (a.data_ptr() + (W - p) * col, msg.data_ptr(), p * col, outer, W * col, p * col),
+        (b.data_ptr() + (W - p) * col, msg.data_ptr() + outer * p * col, p * col, 2 * outer, W * col, p * col),
+        (a.data_ptr(), ext.data_ptr() + p * col, W * col, outer, W * col, (W + 2 * p) * col),
+    ]
+    ca.ops.copy_chunks(jobs)
+    torch.cuda.synchronize()
+    want = torch.cat([a[:, W - p:, :].reshape(-1), b[:, W - p:, :].reshape(-1)])
+    assert torch.equal(msg.view(torch.uint8), want.contiguous().view(torch.uint8))
+    assert torch.equal(ext[:, p:p + W, :].contiguous().view(torch.uint8), a.view(torch.uint8))
+    assert float(ext[:, :p, :].float().abs().max()) == 0.0 and float(ext[:, p + W:, :].float().abs().max()) == 0.0
+    with pytest.raises(RuntimeError, match="njobs"):
+        ca.ops.lib.ca_copy_chunks(None, 33, None) and None or ca.ops.check(ca.ops.lib.ca_copy_chunks(None, 33, None))
