@@ -397,6 +397,16 @@ halo_exchange!(h, send_left::CuArray, send_right::CuArray, recv_left::CuArray, r
                 (Ptr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, Csize_t, Ptr{Cvoid}),
                 h, send_left, send_right, recv_left, recv_right, sizeof(send_left), stream()))
 
+# Several strided device copies in one launch (ca_copy_chunks): the halo columns of a (H, W, c, units) array are
+# H*p elements per trailing index, H*W elements apart, so one call gathers the outgoing columns of all tensors
+# of an exchange into the two messages and one more scatters the incoming ones.
+struct ChunkJob
+    src::CuPtr{Cvoid}; dst::CuPtr{Cvoid}
+    chunk_bytes::Int64; nchunks::Int64; src_stride_bytes::Int64; dst_stride_bytes::Int64
+end
+copy_chunks!(jobs::Vector{ChunkJob}) =
+    check(ccall((:ca_copy_chunks, LIB), Cint, (Ptr{ChunkJob}, Int32, Ptr{Cvoid}), jobs, length(jobs), stream()))
+
 # ------------------------------------------------------------------ algebra and sums (src/array.jl:66-189)
 function axpby(α, X::Circulant, β, Y::Union{Circulant,Nothing})
     out = similar(nzval(X))
