@@ -307,8 +307,8 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
 }
 
 // ------------------------------------------------------------------------------------------------ dq, D
-// Query-owned.  softmax: D = dy . y, dS = P (dP - D); entmax: g = max(z - tau, 0), D = sum g dP / sum g
-// (one more sweep), dS = g (dP - D).  dq = scale * sum dS k  (Distance: - scale * q * sum dS).
+// Query-owned.  softmax: D = dy . y, dS = P (dP - D); entmax: g = max(z - tau, 0), D = sum g dP / sum g,
+// dS = g (dP - D).  dq = scale * sum dS k  (Distance: - scale * q * sum dS).
 template <int CR, int NQ, bool DIST, bool ENT>
 __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_dq_kernel(LineArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -348,10 +348,23 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_dq_kernel(LineArgs 
         Dq[r] = dyy;
     }
 
-    if (ENT) {
-        float num[NQ], den[NQ];
+    float dqa[NQ][CR], sds[NQ];
 #pragma unroll
-        for (int r = 0; r < NQ; ++r) { num[r] = 0.f; den[r] = 0.f; }
+    for (int r = 0; r < NQ; ++r) {
+        sds[r] = 0.f;
+#pragma unroll
+        for (int cc = 0; cc < CR; ++cc) dqa[r][cc] = 0.f;
+    }
+    if (ENT) {
+        // one sweep: with w = g dP, dq = sum (w - D g) k = sum w k - D sum g k and D = sum w / sum g, so the
+        // sums with and without dP are accumulated side by side and combined at the end (sum dS = 0 exactly)
+        float gk[NQ][CR], num[NQ], den[NQ];
+#pragma unroll
+        for (int r = 0; r < NQ; ++r) {
+            num[r] = 0.f; den[r] = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < CR; ++cc) gk[r][cc] = 0.f;
+        }
         sweep<NQ>(ws, [&](auto mk, int t) {
             constexpr int M = decltype(mk)::value;
             float kk[CR], vv[CR];
@@ -362,38 +375,36 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_dq_kernel(LineArgs 
             for (int r = 0; r < NQ; ++r)
                 if ((M >> r) & 1) {
                     const float gg = fmaxf(dot<CR>(q[r], kk, DIST ? c0[r] + bkk : c0[r]), 0.f);
-                    const float dp = dot<CR>(dy[r], vv, 0.f);
-                    num[r] = fmaf(gg, dp, num[r]);
+                    const float w = gg * dot<CR>(dy[r], vv, 0.f);
+                    num[r] += w;
                     den[r] += gg;
+                    axpy<CR>(w, kk, dqa[r]);
+                    axpy<CR>(gg, kk, gk[r]);
                 }
         });
 #pragma unroll
-        for (int r = 0; r < NQ; ++r) Dq[r] = num[r] / den[r];
+        for (int r = 0; r < NQ; ++r) {
+            Dq[r] = num[r] / den[r];
+#pragma unroll
+            for (int cc = 0; cc < CR; ++cc) dqa[r][cc] = fmaf(-Dq[r], gk[r][cc], dqa[r][cc]);
+        }
+    } else {
+        sweep<NQ>(ws, [&](auto mk, int t) {
+            constexpr int M = decltype(mk)::value;
+            float kk[CR], vv[CR];
+            ld_vec<CR>(Kg, a.PP, pad<NQ>(tb + t), kk);
+            ld_vec<CR>(Vg, a.PP, pad<NQ>(tb + t), vv);
+            const float bkk = DIST ? bk[pad<NQ>(tb + t)] : 0.f;
+#pragma unroll
+            for (int r = 0; r < NQ; ++r)
+                if ((M >> r) & 1) {
+                    const float z = dot<CR>(q[r], kk, DIST ? c0[r] + bkk : c0[r]);
+                    const float ds = fast_exp2(z) * dot<CR>(dy[r], vv, -Dq[r]);
+                    if (DIST) sds[r] += ds;
+                    axpy<CR>(ds, kk, dqa[r]);
+                }
+        });
     }
-
-    float dqa[NQ][CR], sds[NQ];
-#pragma unroll
-    for (int r = 0; r < NQ; ++r) {
-        sds[r] = 0.f;
-#pragma unroll
-        for (int cc = 0; cc < CR; ++cc) dqa[r][cc] = 0.f;
-    }
-    sweep<NQ>(ws, [&](auto mk, int t) {
-        constexpr int M = decltype(mk)::value;
-        float kk[CR], vv[CR];
-        ld_vec<CR>(Kg, a.PP, pad<NQ>(tb + t), kk);
-        ld_vec<CR>(Vg, a.PP, pad<NQ>(tb + t), vv);
-        const float bkk = DIST ? bk[pad<NQ>(tb + t)] : 0.f;
-#pragma unroll
-        for (int r = 0; r < NQ; ++r)
-            if ((M >> r) & 1) {
-                const float z = dot<CR>(q[r], kk, DIST ? c0[r] + bkk : c0[r]);
-                const float w = ENT ? fmaxf(z, 0.f) : fast_exp2(z);
-                const float ds = w * dot<CR>(dy[r], vv, -Dq[r]);
-                if (DIST) sds[r] += ds;
-                axpy<CR>(ds, kk, dqa[r]);
-            }
-    });
 
 #pragma unroll
     for (int r = 0; r < NQ; ++r) {
