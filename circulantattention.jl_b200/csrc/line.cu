@@ -8,8 +8,9 @@
 // planar tensors (circular indices), four channels of a pixel per 16-byte slot; the slots carry one slot of
 // padding per NQ pixels, which makes the 128-bit loads of a warp (lanes NQ pixels apart) conflict-free.
 //
-// Without the scores of a row in memory, a row quantity that needs all of them is found by sweeping the
-// window again: the forward sweeps once for the row maximum and once to accumulate; the 1.5-entmax
+// The softmax forward is one sweep with an online sum.  Without the scores of a row in memory, a row quantity
+// that needs all of them is found by sweeping the window again: the entmax forward sweeps once for the row
+// maximum and once to accumulate; the 1.5-entmax
 // threshold tau (sum_k max(z_k - tau, 0)^2 = 1, z = s/2) takes a few sweeps in between, each of which
 // solves the quadratic exactly on the current support {z > tau} and stops when that support reproduces
 // itself; the backward recomputes the weights from the saved row statistic (log-sum-exp or tau).
@@ -125,28 +126,41 @@ __device__ __forceinline__ void stage_norms(float* dst, const float4* grp, int P
 }
 
 // One sweep of a thread's NQ owned pixels over the ws + NQ - 1 staged pixels they pair with.  Step t pairs
-// owned pixel r with staged pixel (thread base + t) iff 0 <= t - r < ws; `f(mask, t)` gets the paired r as a
-// compile-time bit mask.  Needs ws >= NQ - 1.
+// owned pixel r with staged pixel (tb + t) iff 0 <= t - r < ws; `f(mask, slot)` gets the paired r as a
+// compile-time bit mask and the slot of the staged pixel.  tb = NQ * thread, so the slot of step NQ*j + i is
+// (NQ + 1) * (thread + j) + i: the steps are walked in aligned groups of NQ whose slots are one running value
+// plus a compile-time i, which leaves the loads with immediate offsets.  Needs ws >= NQ - 1.
 template <int NQ, int T, class F>
-__device__ __forceinline__ void sweep_head(F& f) {
+__device__ __forceinline__ void sweep_head(F& f, int slot0) {
     if constexpr (T < NQ - 1) {
-        f(ic<(1 << (T + 1)) - 1>{}, T);
-        sweep_head<NQ, T + 1>(f);
+        f(ic<(1 << (T + 1)) - 1>{}, slot0 + T);
+        sweep_head<NQ, T + 1>(f, slot0);
+    }
+}
+template <int NQ, int I, class F>
+__device__ __forceinline__ void sweep_group(F& f, int slot0) {
+    if constexpr (I < NQ) {
+        f(ic<(1 << NQ) - 1>{}, slot0 + I);
+        sweep_group<NQ, I + 1>(f, slot0);
     }
 }
 template <int NQ, int E, class F>
-__device__ __forceinline__ void sweep_tail(F& f, int ws) {
+__device__ __forceinline__ void sweep_tail(F& f, int tb, int ws) {
     if constexpr (E < NQ - 1) {
-        f(ic<((1 << NQ) - 1) & ~((1 << (E + 1)) - 1)>{}, ws + E);
-        sweep_tail<NQ, E + 1>(f, ws);
+        f(ic<((1 << NQ) - 1) & ~((1 << (E + 1)) - 1)>{}, pad<NQ>(tb + ws + E));
+        sweep_tail<NQ, E + 1>(f, tb, ws);
     }
 }
 template <int NQ, class F>
-__device__ __forceinline__ void sweep(int ws, F&& f) {
-    sweep_head<NQ, 0>(f);
-#pragma unroll 2
-    for (int t = NQ - 1; t < ws; ++t) f(ic<(1 << NQ) - 1>{}, t);
-    sweep_tail<NQ, 0>(f, ws);
+__device__ __forceinline__ void sweep(int tb, int ws, F&& f) {
+    int slot0 = pad<NQ>(tb);                       // tb is a multiple of NQ
+    sweep_head<NQ, 0>(f, slot0);
+    f(ic<(1 << NQ) - 1>{}, slot0 + NQ - 1);        // step NQ - 1: the first one every owned pixel pairs with
+    int t = NQ;
+    slot0 += NQ + 1;
+    for (; t + NQ <= ws; t += NQ, slot0 += NQ + 1) sweep_group<NQ, 0>(f, slot0);
+    for (; t < ws; ++t) f(ic<(1 << NQ) - 1>{}, pad<NQ>(tb + t));
+    sweep_tail<NQ, 0>(f, tb, ws);
 }
 
 // Scale of the stored scores: z = f * sim(q, k) is the log2-domain score (softmax) or s / 2 (entmax).
@@ -154,6 +168,7 @@ template <bool ENT>
 __device__ __forceinline__ float score_factor(float scale) { return ENT ? 0.5f * scale : scale * kLog2e; }
 
 constexpr int kMaxTauSweeps = 24;
+constexpr float kLineHeadroom = 12.f;          // log2 units between the softmax reference and the score that set it
 
 // ------------------------------------------------------------------------------------------------ forward
 template <int CR, int NQ, bool DIST, bool ENT>
@@ -186,15 +201,24 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
         bq[r] = DIST ? -0.5f * invf * dot<CR>(q[r], q[r], 0.f) : 0.f;
     }
 
-    // row maximum
+    // entmax: the row maximum.  softmax: an online sum against a reference that starts kLineHeadroom above the
+    // score of the centre key and moves only when a score climbs past it (then the sums are rescaled)
     float m[NQ];
 #pragma unroll
     for (int r = 0; r < NQ; ++r) m[r] = -INFINITY;
-    sweep<NQ>(ws, [&](auto mk, int t) {
+    if (!ENT) {
+#pragma unroll
+        for (int r = 0; r < NQ; ++r) {
+            float kk[CR];
+            ld_vec<CR>(Kg, a.PP, pad<NQ>(tb + r + g.p), kk);
+            m[r] = dot<CR>(q[r], kk, DIST ? bq[r] + bk[pad<NQ>(tb + r + g.p)] : 0.f) + kLineHeadroom;
+        }
+    }
+    if (ENT) sweep<NQ>(tb, ws, [&](auto mk, int slot) {
         constexpr int M = decltype(mk)::value;
         float kk[CR];
-        ld_vec<CR>(Kg, a.PP, pad<NQ>(tb + t), kk);
-        const float bkk = DIST ? bk[pad<NQ>(tb + t)] : 0.f;
+        ld_vec<CR>(Kg, a.PP, slot, kk);
+        const float bkk = DIST ? bk[slot] : 0.f;
 #pragma unroll
         for (int r = 0; r < NQ; ++r)
             if ((M >> r) & 1) m[r] = fmaxf(m[r], dot<CR>(q[r], kk, DIST ? bq[r] + bkk : 0.f));
@@ -221,11 +245,11 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
                 tmin[r] = INFINITY;         // smallest t > 0 (support)
                 tneg[r] = -INFINITY;        // largest t <= 0 (outside)
             }
-            sweep<NQ>(ws, [&](auto mk, int t) {
+            sweep<NQ>(tb, ws, [&](auto mk, int slot) {
                 constexpr int M = decltype(mk)::value;
                 float kk[CR];
-                ld_vec<CR>(Kg, a.PP, pad<NQ>(tb + t), kk);
-                const float bkk = DIST ? bk[pad<NQ>(tb + t)] : 0.f;
+                ld_vec<CR>(Kg, a.PP, slot, kk);
+                const float bkk = DIST ? bk[slot] : 0.f;
 #pragma unroll
                 for (int r = 0; r < NQ; ++r)
                     if ((M >> r) & 1) {
@@ -271,21 +295,30 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
 #pragma unroll
         for (int cc = 0; cc < CR; ++cc) acc[r][cc] = 0.f;
     }
-    sweep<NQ>(ws, [&](auto mk, int t) {
+    sweep<NQ>(tb, ws, [&](auto mk, int slot) {
         constexpr int M = decltype(mk)::value;
         float kk[CR], vv[CR];
-        ld_vec<CR>(Kg, a.PP, pad<NQ>(tb + t), kk);
-        ld_vec<CR>(Vg, a.PP, pad<NQ>(tb + t), vv);
-        const float bkk = DIST ? bk[pad<NQ>(tb + t)] : 0.f;
+        ld_vec<CR>(Kg, a.PP, slot, kk);
+        ld_vec<CR>(Vg, a.PP, slot, vv);
+        const float bkk = DIST ? bk[slot] : 0.f;
 #pragma unroll
         for (int r = 0; r < NQ; ++r)
             if ((M >> r) & 1) {
-                const float tt = dot<CR>(q[r], kk, DIST ? (bq[r] - off[r]) + bkk : -off[r]);
+                float tt = dot<CR>(q[r], kk, DIST ? (bq[r] - off[r]) + bkk : -off[r]);
                 float w;
                 if (ENT) {
                     const float tp = fmaxf(tt, 0.f);
                     w = tp * tp;
                 } else {
+                    if (tt > 0.f) {                  // rare: this score is above the reference; move it up
+                        const float up = tt + kLineHeadroom;
+                        const float corr = fast_exp2(-up);
+                        l[r] *= corr;
+#pragma unroll
+                        for (int cc = 0; cc < CR; ++cc) acc[r][cc] *= corr;
+                        off[r] += up;
+                        tt = -kLineHeadroom;
+                    }
                     w = fast_exp2(tt);
                     l[r] += w;
                 }
@@ -301,7 +334,7 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
 #pragma unroll
             for (int cc = 0; cc < CR; ++cc)
                 if (cc < g.cr) a.o[eoff(g.cpe, u, g.c, cc, N, pix)] = acc[r][cc] * inv;
-            if (a.ostats) a.ostats[(int64_t)u * N + pix] = ENT ? off[r] : (m[r] + log2f(l[r])) * kLn2;
+            if (a.ostats) a.ostats[(int64_t)u * N + pix] = ENT ? off[r] : (off[r] + log2f(l[r])) * kLn2;
         }
     }
 }
@@ -365,12 +398,12 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_dq_kernel(LineArgs 
 #pragma unroll
             for (int cc = 0; cc < CR; ++cc) gk[r][cc] = 0.f;
         }
-        sweep<NQ>(ws, [&](auto mk, int t) {
+        sweep<NQ>(tb, ws, [&](auto mk, int slot) {
             constexpr int M = decltype(mk)::value;
             float kk[CR], vv[CR];
-            ld_vec<CR>(Kg, a.PP, pad<NQ>(tb + t), kk);
-            ld_vec<CR>(Vg, a.PP, pad<NQ>(tb + t), vv);
-            const float bkk = DIST ? bk[pad<NQ>(tb + t)] : 0.f;
+            ld_vec<CR>(Kg, a.PP, slot, kk);
+            ld_vec<CR>(Vg, a.PP, slot, vv);
+            const float bkk = DIST ? bk[slot] : 0.f;
 #pragma unroll
             for (int r = 0; r < NQ; ++r)
                 if ((M >> r) & 1) {
@@ -389,12 +422,12 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_dq_kernel(LineArgs 
             for (int cc = 0; cc < CR; ++cc) dqa[r][cc] = fmaf(-Dq[r], gk[r][cc], dqa[r][cc]);
         }
     } else {
-        sweep<NQ>(ws, [&](auto mk, int t) {
+        sweep<NQ>(tb, ws, [&](auto mk, int slot) {
             constexpr int M = decltype(mk)::value;
             float kk[CR], vv[CR];
-            ld_vec<CR>(Kg, a.PP, pad<NQ>(tb + t), kk);
-            ld_vec<CR>(Vg, a.PP, pad<NQ>(tb + t), vv);
-            const float bkk = DIST ? bk[pad<NQ>(tb + t)] : 0.f;
+            ld_vec<CR>(Kg, a.PP, slot, kk);
+            ld_vec<CR>(Vg, a.PP, slot, vv);
+            const float bkk = DIST ? bk[slot] : 0.f;
 #pragma unroll
             for (int r = 0; r < NQ; ++r)
                 if ((M >> r) & 1) {
@@ -478,10 +511,9 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_dkdv_kernel(LineArg
 #pragma unroll
         for (int cc = 0; cc < CR; ++cc) { dka[r][cc] = 0.f; dva[r][cc] = 0.f; }
     }
-    sweep<NQ>(ws, [&](auto mk, int t) {
+    sweep<NQ>(tb, ws, [&](auto mk, int slot) {
         constexpr int M = decltype(mk)::value;
         float qq[CR], yy[CR];
-        const int slot = pad<NQ>(tb + t);
         ld_vec<CR>(Qg, a.PP, slot, qq);
         ld_vec<CR>(Yg, a.PP, slot, yy);
         const float4 sc = Sg[slot];
