@@ -382,6 +382,10 @@ int ca_attention_fwd(const ca_desc* d, const void* q, const void* k, const void*
         rc = tiled_attention_fwd_entmax(g, d->scale, dist, (const float*)q, (const float*)k, (const float*)v,
                                         (float*)y, stats, workspace, st);
         if (rc != CA_ERR_UNSUPPORTED) return rc;
+        // the workspace was sized for the sweeps (ca_attention_fwd_workspace follows the same rule), so the chain
+        // below, which needs an A-sized buffer, must not run on it
+        set_error("entmax forward: the fused sweeps do not cover this launch (grid limits); raise ca_entmax_scratch_limit to use the operator chain");
+        return CA_ERR_UNSUPPORTED;
     }
     if (ent || (composed_path(d, g) && (nz || workspace))) {
         // scores -> row normaliser (threshold or log-sum-exp per row) -> apply; the scores live in
