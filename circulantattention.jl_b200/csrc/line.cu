@@ -583,7 +583,8 @@ constexpr int kFwdNQ8 = 4, kFwdNQ16 = 4, kBwdNQ8 = 4, kBwdNQ16 = 2;
 }  // namespace
 
 bool line_shape_ok(const Geo& g) {
-    return g.wsw == 1 && g.W == 1 && g.Wk == g.W && !g.bf16 && g.cr >= 1 && g.cr <= 16 && g.ws >= 5 &&
+    // windows up to 511: every kernel's staged tile then fits the shared memory of one block
+    return g.wsw == 1 && g.W == 1 && g.Wk == g.W && !g.bf16 && g.cr >= 1 && g.cr <= 16 && g.ws >= 5 && g.ws <= 511 &&
            g.Np >= g.ws;
 }
 

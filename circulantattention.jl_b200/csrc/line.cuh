@@ -4,7 +4,7 @@
 
 namespace ca {
 
-// 1-D signals of at most 16 real channels per unit with a window of at least 5, Float32 or ComplexF32.
+// 1-D signals of at most 16 real channels per unit with a window of 5 to 511, Float32 or ComplexF32.
 bool line_shape_ok(const Geo& g);
 
 // Flash-mode forward (y and the row statistic: log-sum-exp, or the entmax threshold), no scratch memory.
