@@ -109,6 +109,12 @@ __device__ __forceinline__ float dot(const float (&a)[CR], const float (&b)[CR],
     return s;
 }
 
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int CR>
 __device__ __forceinline__ void axpy(float w, const float (&x)[CR], float (&y)[CR]) {
 #pragma unroll
@@ -238,12 +244,14 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
             done[r] = false;
         }
         for (int it = 0; it < kMaxTauSweeps; ++it) {
-            float n[NQ], sa[NQ], sb[NQ], tmin[NQ], tneg[NQ];
+            // the support's nearest members on both sides of tau through reciprocals: max 1/t is 1/(smallest t > 0),
+            // min 1/t is 1/(largest t < 0) -- one reciprocal and two min/max per pair, no selects
+            float n[NQ], sa[NQ], sb[NQ], rmax[NQ], rmin[NQ];
 #pragma unroll
             for (int r = 0; r < NQ; ++r) {
                 n[r] = 0.f; sa[r] = 0.f; sb[r] = 0.f;
-                tmin[r] = INFINITY;         // smallest t > 0 (support)
-                tneg[r] = -INFINITY;        // largest t <= 0 (outside)
+                rmax[r] = 0.f;
+                rmin[r] = 0.f;
             }
             sweep<NQ>(tb, ws, [&](auto mk, int slot) {
                 constexpr int M = decltype(mk)::value;
@@ -254,13 +262,13 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
                 for (int r = 0; r < NQ; ++r)
                     if ((M >> r) & 1) {
                         const float tt = dot<CR>(q[r], kk, DIST ? (bq[r] - off[r]) + bkk : -off[r]);
-                        const bool in = tt > 0.f;
                         const float tp = fmaxf(tt, 0.f);
                         sa[r] += tp;
                         sb[r] = fmaf(tp, tp, sb[r]);
-                        n[r] += in ? 1.f : 0.f;
-                        tmin[r] = fminf(tmin[r], in ? tt : INFINITY);
-                        tneg[r] = fmaxf(tneg[r], in ? -INFINITY : tt);
+                        n[r] += tt > 0.f ? 1.f : 0.f;
+                        const float rt = fast_rcp(tt);
+                        rmax[r] = fmaxf(rmax[r], rt);
+                        rmin[r] = fminf(rmin[r], rt);
                     }
             });
             bool all = true;
@@ -275,7 +283,8 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
                         // final when the support reproduces itself and the step was short against the
                         // distances it was computed from (a long step leaves tau with the rounding error
                         // of those larger numbers: one more sweep, now around the new tau, removes it)
-                        const bool same = (d >= 0.f ? d < tmin[r] : d >= tneg[r]) && d * n[r] <= 0.5f * sa[r];
+                        // d < tmin  <=>  d * rmax < 1 (rmax > 0);  d >= tneg  <=>  d * rmin <= 1 (d, rmin < 0)
+                        const bool same = (d >= 0.f ? d * rmax[r] < 1.f : d * rmin[r] <= 1.f) && d * n[r] <= 0.5f * sa[r];
                         // a row that keeps changing its support falls back to Newton steps on
                         // f(tau) = sum max(z - tau, 0)^2 - 1 (convex, converges from either side)
                         if (!same && it >= 10) d = 0.5f * (sb[r] - 1.f) / sa[r];

@@ -24,6 +24,7 @@ CASES = [
     ((600, 12, 2), 15, 2, False),        # 6 channels per head (zero-extended to 8)
     ((520, 8, 2), 21, 2, True),          # ComplexF32: 4 complex = 8 real channels per head
     ((300, 3, 1), 5, 1, False),          # 3 channels, the shortest window the kernels take
+    ((900, 8, 1), 255, 1, False),        # a long window: more than 48 KB of shared memory per block
 ]
 
 
