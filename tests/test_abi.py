@@ -95,3 +95,37 @@ def test_julia_shaped_tensors(ca):
     assert np.array_equal(ca.jl.to_numpy(r), a.reshape((6, 4), order="F"))
     s = ca.splitheads(ca.jl.from_numpy(np.asfortranarray(np.zeros((5, 6, 2), np.float32)), device="cpu"), 3)
     assert tuple(s.shape) == (5, 2, 6)
+
+
+def test_entmax_scratch_limit_round_trip(ca):
+    """Process-wide setting: a negative argument queries, a non-negative one sets and returns the previous value;
+    the workspace query follows it (a 32 x 32 image of 16 channels, ws 5: 205 KB of scores)."""
+    from circatt_b200._lib import lib
+    assert lib.ca_entmax_scratch_limit(-1) == 256 << 20
+    d = _desc(ca, H=32, W=32, channels=16, normalizer=1)
+    chain = lib.ca_attention_fwd_workspace(d, 0)
+    assert chain >= 1024 * 25 * 2 * 4
+    assert lib.ca_entmax_scratch_limit(0) == 256 << 20
+    try:
+        sweeps = lib.ca_attention_fwd_workspace(d, 0)
+        assert 0 < sweeps != chain                       # the packed (k|v) and two planes instead of the scores
+    finally:
+        assert lib.ca_entmax_scratch_limit(256 << 20) == 0
+    assert lib.ca_attention_fwd_workspace(d, 0) == chain
+
+
+def test_copy_chunks_validates_on_the_host(ca):
+    from circatt_b200._lib import lib, last_error
+    assert lib.ca_copy_chunks(None, 0, None) == 0
+    assert lib.ca_copy_chunks(None, 33, None) == -1 and "njobs" in last_error()
+    assert lib.ca_copy_chunks(None, 2, None) == -3
+
+
+def test_line_kernels_need_no_workspace_query(ca):
+    """1-D signals of up to 16 real channels per unit in flash mode: no scratch at all, entmax included."""
+    from circatt_b200._lib import lib
+    for nrm in (0, 1):
+        d = _desc(ca, H=4096, W=1, ndim=1, channels=8, units=4, ws=127, normalizer=nrm)
+        assert lib.ca_attention_fwd_workspace(d, 0) == 0
+    wide = _desc(ca, H=4096, W=1, ndim=1, channels=32, units=4, ws=127, normalizer=0)
+    assert lib.ca_attention_fwd_workspace(wide, 0) > 0
