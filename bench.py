@@ -433,6 +433,8 @@ def main():
                     help="time the stand-alone operators at the bench shape instead of the headline step")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the other BASELINE configurations and the "
                     "sharded config-5 runs (they add a few seconds)")
+    ap.add_argument("--no-graph", action="store_true", help="run the end-to-end step eagerly instead of replaying "
+                    "its CUDA graph")
     ap.add_argument("--slice", default=None, choices=sorted(SLICES),
                     help="run a few passes of a small slice of a configuration (for profiler captures) and exit")
     args = ap.parse_args()
@@ -609,26 +611,41 @@ def main():
         host_in[i_].copy_(t_)
     host_out = torch.empty(3 * n_el + 1, dtype=torch.float32).pin_memory()
     n_e2e = max(5, min(steps, 30))
+    NSLOT = 3                           # buffer slots: the host waits for the copy-out of step i - 3 only
     s_in, s_cmp, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
-    dev_in = [torch.empty_like(host_in, device=dev) for _ in range(2)]
-    dev_out = [torch.empty(3 * n_el + 1, dtype=torch.float32, device=dev) for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_cmp = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
-    keep = [None, None]                 # tensors of a slot stay referenced until its copies have finished
+    dev_in = [torch.empty_like(host_in, device=dev) for _ in range(NSLOT)]
+    dev_out = [torch.empty(3 * n_el + 1, dtype=torch.float32, device=dev) for _ in range(NSLOT)]
+    ev_in = [torch.cuda.Event() for _ in range(NSLOT)]
+    ev_cmp = [torch.cuda.Event() for _ in range(NSLOT)]
+    ev_out = [torch.cuda.Event() for _ in range(NSLOT)]
+    keep = [None] * NSLOT                 # tensors of a slot stay referenced until its copies have finished
     host_busy = [0.0]                   # host time spent enqueueing (waits for the device excluded)
     losses = []
     # per slot, made once: the Julia-shaped views of the staging buffer (q, k, v as leaves that require a
     # gradient, the loss weights) and the views of the output buffer the gradients and the loss are written to
     slot_in, slot_out = [], []
-    for s_ in range(2):
+    for s_ in range(NSLOT):
         views = [t.permute(3, 2, 1, 0) for t in dev_in[s_]]
         slot_in.append([v_.detach().requires_grad_(True) for v_ in views[:3]] + [views[3]])
         slot_out.append([dev_out[s_][j_ * n_el:(j_ + 1) * n_el].view(shape_t).permute(3, 2, 1, 0) for j_ in range(3)]
                         + [dev_out[s_][3 * n_el:]])
 
+    def compute(slot):
+        """The step itself through the public API: forward, loss, backward, results into the slot's output buffer."""
+        qd, kd, vd, rd = slot_in[slot]
+        qd.grad = kd.grad = vd.grad = None
+        yy, _ = ca.circulant_mh_attention(ca.DotSimilarity(), qd, kd, vd, ws, nheads, return_A=False)
+        loss = (yy * rd).sum()
+        loss.backward()
+        for dst_, t in zip(slot_out[slot], (qd, kd, vd)):
+            dst_.copy_(t.grad)
+        slot_out[slot][3].copy_(loss.detach().reshape(1))
+        return yy, loss
+
+    graphs = [None] * NSLOT               # per slot: the step recorded into a CUDA graph (ca.capture)
+
     def e2e_step(i):
-        slot = i % 2
+        slot = i % NSLOT
         ev_out[slot].synchronize()      # the slot's previous outputs have left the device
         losses.append(float(host_out[-1]))
         t_h = time.perf_counter()
@@ -639,29 +656,39 @@ def main():
         with torch.cuda.stream(s_cmp):
             s_cmp.wait_event(ev_in[slot])
             s_cmp.wait_event(ev_out[slot])                   # dev_out[slot] has been copied out
-            qd, kd, vd, rd = slot_in[slot]
-            qd.grad = kd.grad = vd.grad = None
-            yy, _ = ca.circulant_mh_attention(ca.DotSimilarity(), qd, kd, vd, ws, nheads, return_A=False)
-            loss = (yy * rd).sum()
-            loss.backward()
-            for dst_, t in zip(slot_out[slot], (qd, kd, vd)):
-                dst_.copy_(t.grad)
-            slot_out[slot][3].copy_(loss.detach().reshape(1))
+            if graphs[slot] is not None:
+                graphs[slot].replay()
+            else:
+                keep[slot] = compute(slot) + tuple(slot_in[slot])
             ev_cmp[slot].record(s_cmp)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_cmp[slot])
             host_out.copy_(dev_out[slot], non_blocking=True)
             ev_out[slot].record(s_out)
-        keep[slot] = (yy, qd, kd, vd, loss)
         host_busy[0] += time.perf_counter() - t_h
 
-    for i in range(3):
+    for i in range(NSLOT + 1):
         e2e_step(i)
     barrier()
+    # the step is launch- and host-bound (five kernels of ~50 us behind ~0.6 ms of Python and autograd), so it is
+    # recorded once per slot into a CUDA graph and replayed; a failed capture leaves the eager step in place
+    graph_note = None
+    if not args.no_graph:
+        try:
+            for slot_ in range(NSLOT):
+                graphs[slot_], kept = ca.capture(lambda s_=slot_: compute(s_), stream=s_cmp, warmup=0)
+                keep[slot_] = kept + tuple(slot_in[slot_])
+        except Exception as e:                              # noqa: BLE001
+            graphs = [None] * NSLOT
+            graph_note = f"{type(e).__name__}: {e}"[:200]
+        barrier()
+        for i in range(NSLOT):
+            e2e_step(3 + i)
+        barrier()
     host_busy[0] = 0.0
     t0 = time.perf_counter()
     for i in range(n_e2e):
-        e2e_step(3 + i)
+        e2e_step(2 * NSLOT + 1 + i)
     barrier()
     e2e_wall = time.perf_counter() - t0
     losses.append(float(host_out[-1]))
@@ -739,10 +766,13 @@ def main():
                     "steps": n_e2e, "link_bound_px_per_s": link_bound, "frac_of_link_bound": e2e_value / link_bound,
                     "link_gbs_h2d": 4 * nbytes * n_e2e * world / float(link_t.item()) / 1e9,
                     "host_enqueue_ms_per_step": host_busy[0] / n_e2e * 1e3,
+                    "cuda_graph": graphs[0] is not None, **({"cuda_graph_error": graph_note} if graph_note else {}),
                     "timing": "wall clock around the steps, synchronised on both sides, max over ranks; one pinned "
                               "staging buffer and one copy per direction per step; copy-in, compute and copy-out of "
-                              "neighbouring steps overlap on three streams; link_bound = the same copies with "
-                              "nothing computed"},
+                              "neighbouring steps overlap on three streams; the compute of a step "
+                              "(circulant_mh_attention + backward through the public API) is recorded once per "
+                              "buffer slot into a CUDA graph (ca.capture) and replayed when cuda_graph is true; "
+                              "link_bound = the same copies with nothing computed"},
             "other_configs": other, **sharded,
             "gpu_launches": int(launches), "clocks": clocks,
         }

@@ -2,10 +2,11 @@
 
 The package is a thin host layer: `api` mirrors the reference's Julia methods,
 `ops` calls the C ABI of `libcircatt_b200.so` (hand-written sm_100a kernels in
-`csrc/`), `jl` provides Julia-shaped column-major tensors, and `parallel` shards
-the work over GPUs.  There is no CPU or PyTorch fallback.
+`csrc/`), `jl` provides Julia-shaped column-major tensors, `parallel` shards
+the work over GPUs, and `graphs` records calls into CUDA graphs.  There is no CPU or PyTorch fallback.
 """
-from . import jl, ops, parallel  # noqa: F401
+from . import graphs, jl, ops, parallel  # noqa: F401
+from .graphs import capture  # noqa: F401
 from ._lib import CircAttError, LIB_PATH, lib  # noqa: F401
 from .api import (  # noqa: F401
     AbstractSimilarity, BatchedTranspose, Circulant, LazyAdjacency, CuSparseArrayCSR, DistanceSimilarity, DotSimilarity,
