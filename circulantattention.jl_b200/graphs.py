@@ -25,6 +25,8 @@ def capture(fn, stream=None, warmup=2):
             fn()
     torch.cuda.current_stream().wait_stream(side)
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
+    # thread_local: other host threads (a process group's watchdog, a data loader) may keep calling the CUDA
+    # runtime while this thread records
+    with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
         result = fn()
     return graph, result
