@@ -365,6 +365,8 @@ def units_c5(ca, torch, dist, dev, world, rank, steps):
 SLICES = {
     # small cases of the same kernels for profiler captures: name -> a time_config tuple
     "c2": ((128, 96, 64, 2), 15, 4, 0, 0, False, False, "f32"),
+    "c2e": ((128, 96, 64, 2), 15, 4, 0, 1, False, False, "f32"),         # the bench shape with entmax: operator chain
+    "c2e_sweeps": ((128, 96, 64, 2), 15, 4, 0, 1, False, False, "f32"),  # the same on the scratch-free sweeps
     "c3": ((16384, 64, 4), 127, 8, 1, 1, False, False, "f32"),           # a quarter of config 3's batch (32 units)
     "c3s": ((16384, 64, 4), 127, 8, 1, 0, False, False, "f32"),          # the same with softmax
     "c4": ((320, 320, 32, 2), 7, 1, 0, 0, True, True, "c64"),
@@ -383,6 +385,8 @@ def slice_main(args):
     gen = torch.Generator(device="cuda").manual_seed(0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     timed = make_timer(torch, flush)
+    if args.slice.endswith("_sweeps"):
+        ca.ops.entmax_scratch_limit(0)               # entmax forward: never the A-sized operator chain
     res = time_config(ca, torch, lambda fn: timed(fn, n=3, warm=2), gen, SLICES[args.slice], NOMINAL_FFMA_TFLOPS)
     print(json.dumps({"slice": args.slice, "config": SLICES[args.slice][:5], **res}))
 
