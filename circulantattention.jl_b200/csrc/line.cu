@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
                         // distances it was computed from (a long step leaves tau with the rounding error
                         // of those larger numbers: one more sweep, now around the new tau, removes it)
                         // d < tmin  <=>  d * rmax < 1 (rmax > 0);  d >= tneg  <=>  d * rmin <= 1 (d, rmin < 0)
-                        const bool same = (d >= 0.f ? d * rmax[r] < 1.f : d * rmin[r] <= 1.f) && d * n[r] <= 0.5f * sa[r];
+                        const bool same = (d >= 0.f ? d * rmax[r] < 1.f : d * rmin[r] <= 1.f) && d * n[r] <= 0.75f * sa[r];
                         // a row that keeps changing its support falls back to Newton steps on
                         // f(tau) = sum max(z - tau, 0)^2 - 1 (convex, converges from either side)
                         if (!same && it >= 10) d = 0.5f * (sb[r] - 1.f) / sa[r];
