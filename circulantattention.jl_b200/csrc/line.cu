@@ -174,6 +174,7 @@ template <bool ENT>
 __device__ __forceinline__ float score_factor(float scale) { return ENT ? 0.5f * scale : scale * kLog2e; }
 
 constexpr int kMaxTauSweeps = 24;
+constexpr unsigned kCoopRows = 16;            // open rows per warp (of 32 * NQ) below which the warp finishes them together
 constexpr float kLineHeadroom = 12.f;          // log2 units between the softmax reference and the score that set it
 
 // ------------------------------------------------------------------------------------------------ forward
@@ -293,7 +294,68 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
                     }
                     all = all && done[r];
                 }
-            if (__all_sync(0xffffffffu, all)) break;
+            (void)all;
+            // rows of this warp that are still open; when only a few are left (after the fourth sweep about
+            // one row in a hundred), the warp finishes them one at a time, the window's keys spread over its
+            // lanes, instead of sweeping all 32 * NQ rows again for their sake
+            unsigned open_rows = 0;
+#pragma unroll
+            for (int r = 0; r < NQ; ++r) open_rows += done[r] ? 0u : 1u;
+            const unsigned warp_open = __reduce_add_sync(0xffffffffu, open_rows);
+            if (warp_open == 0) break;
+            if (warp_open > kCoopRows) continue;
+            const int lane = lt & 31;
+            unsigned pend = __ballot_sync(0xffffffffu, open_rows != 0);
+            while (pend) {
+                const int src = __ffs(pend) - 1;
+                pend &= pend - 1;
+#pragma unroll
+                for (int r = 0; r < NQ; ++r) {
+                    if (!__shfl_sync(0xffffffffu, done[r] ? 0 : 1, src)) continue;        // warp-uniform
+                    float qq[CR];
+#pragma unroll
+                    for (int cc = 0; cc < CR; ++cc) qq[cc] = __shfl_sync(0xffffffffu, q[r][cc], src);
+                    const float bqq = DIST ? __shfl_sync(0xffffffffu, bq[r], src) : 0.f;
+                    float tau = __shfl_sync(0xffffffffu, off[r], src);
+                    const int base = NQ * ((lt & ~31) + src) + r;        // staged pixel of the row's first key
+                    for (int ci = 0; ci < kMaxTauSweeps; ++ci) {
+                        float n1 = 0.f, sa1 = 0.f, sb1 = 0.f, rmx = 0.f, rmn = 0.f;
+                        for (int d = lane; d < ws; d += 32) {
+                            const int slot = pad<NQ>(base + d);
+                            float kk[CR];
+                            ld_vec<CR>(Kg, a.PP, slot, kk);
+                            const float tt = dot<CR>(qq, kk, DIST ? (bqq - tau) + bk[slot] : -tau);
+                            const float tp = fmaxf(tt, 0.f);
+                            sa1 += tp;
+                            sb1 = fmaf(tp, tp, sb1);
+                            n1 += tt > 0.f ? 1.f : 0.f;
+                            const float rt = fast_rcp(tt);
+                            rmx = fmaxf(rmx, rt);
+                            rmn = fminf(rmn, rt);
+                        }
+#pragma unroll
+                        for (int m = 16; m >= 1; m >>= 1) {
+                            n1 += __shfl_xor_sync(0xffffffffu, n1, m);
+                            sa1 += __shfl_xor_sync(0xffffffffu, sa1, m);
+                            sb1 += __shfl_xor_sync(0xffffffffu, sb1, m);
+                            rmx = fmaxf(rmx, __shfl_xor_sync(0xffffffffu, rmx, m));
+                            rmn = fminf(rmn, __shfl_xor_sync(0xffffffffu, rmn, m));
+                        }
+                        if (n1 == 0.f) break;
+                        const float disc = fmaxf(fmaf(sa1, sa1, -n1 * (sb1 - 1.f)), 0.f);
+                        float d = (sa1 - sqrtf(disc)) / n1;
+                        const bool same = (d >= 0.f ? d * rmx < 1.f : d * rmn <= 1.f) && d * n1 <= 0.75f * sa1;
+                        if (!same && ci >= 10) d = 0.5f * (sb1 - 1.f) / sa1;
+                        tau += d;
+                        if (same) break;
+                    }
+                    if (lane == src) {
+                        off[r] = tau;
+                        done[r] = true;
+                    }
+                }
+            }
+            break;
         }
     }
 
