@@ -551,8 +551,9 @@ int ca_attention_bwd(const ca_desc* d, const void* q, const void* k, const void*
         if (rc != CA_ERR_UNSUPPORTED) return rc;
     }
     if (d->normalizer == CA_ENTMAX15 && !dA && g.wsw != 1) {
-        // fused kernels with the entmax weights recomputed from tau (no A-sized traffic).  2-D only:
-        // on folded 1-D signals the three sweeps are shared-memory bound and the generic kernels win.
+        // fused kernels with the entmax weights recomputed from tau (no A-sized traffic).  2-D only: 1-D
+        // signals took the sliding-tile kernels above; what is left of 1-D (wide units, windows under 5) is
+        // shared-memory bound on the folded tiled kernels and runs the generic ones.
         if (!q || !k || !v || !dy || !stats || !dq || !dk || !dv) { set_error("a required pointer is NULL"); return CA_ERR_NULL; }
         rc = tiled_attention_bwd_entmax(g, d->scale, d->similarity == CA_DISTANCE, (const float*)q, (const float*)k,
                                         (const float*)v, (const float*)dy, stats, D, (float*)dq, (float*)dk,
