@@ -1626,6 +1626,97 @@ __global__ void __launch_bounds__(128) pack_rows_kernel(PackArgs a) {
     else pack_rows_body<CPE, NCRT, false>(a, tile);
 }
 
+// The same for units of NS = 2 or 4 slabs (32 / 64 real channels), Float32 or ComplexF32: a block gathers 128 / NS
+// packed rows, thread (row, slab) the two 16-channel slabs of its row and slab (consecutive lanes on consecutive
+// rows: coalesced planar loads), into a [128 / NS][36 * NS] tile in the packed order [tensor][4-channel chunk]
+// [slab][4], and writes the tile out as one contiguous run.  The direct form writes 16 * NS-byte pieces 144 * NS
+// bytes apart.  In the planes slot the NS threads of a row share the dy . y sum through the tile.
+template <int CPE, int NCRT>
+__global__ void __launch_bounds__(128) pack_rows_wide_kernel(PackArgs a) {
+    constexpr int NS = NCRT / 16, RB = 128 / NS, RF = kRowFloats * NS;
+    __shared__ __align__(16) float tile[RB][RF];
+    const Geo& g = a.g;
+    const int rl = threadIdx.x % RB, slab = threadIdx.x / RB;
+    const int rr0 = blockIdx.x * RB, rr = rr0 + rl;
+    const int w = blockIdx.y;
+    const int slots = a.npairs + (a.planes ? 1 : 0);
+    const int u = blockIdx.z / slots, slot = blockIdx.z % slots;
+    const bool in_rows = rr < a.Hp;
+    const bool real_row = in_rows && rr < g.H + 2 * a.pp;
+    int pix = 0;
+    if (real_row) {
+        if (g.wsw == 1) {
+            pix = (g.H * w + rr - a.pp) % g.Npk;
+            if (pix < 0) pix += g.Npk;
+        } else {
+            pix = (rr - a.pp + g.H) % g.H + g.H * w;
+        }
+    }
+    if (slot < a.npairs) {
+        float4* trow = reinterpret_cast<float4*>(tile[rl]);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const float* src = a.src[2 * slot + t];
+            float4 vals[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int cc = 16 * slab + 4 * c;
+                if (!real_row) {
+                    vals[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else if (CPE == 1) {
+                    const int64_t o = goff<1, NCRT>(u, cc, g.Npk, pix);
+                    vals[c] = make_float4(__ldg(src + o), __ldg(src + o + g.Npk), __ldg(src + o + 2 * (int64_t)g.Npk),
+                                          __ldg(src + o + 3 * (int64_t)g.Npk));
+                } else {
+                    const float2 lo = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCRT>(u, cc, g.Npk, pix)));
+                    const float2 hi = __ldg(reinterpret_cast<const float2*>(src + goff<2, NCRT>(u, cc + 2, g.Npk, pix)));
+                    vals[c] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) trow[t * (4 * NS) + c * NS + slab] = vals[c];
+        }
+        trow[8 * NS + slab] = make_float4(0.f, 0.f, 0.f, 0.f);                 // padding words
+        __syncthreads();
+        const int nrows = min(RB, a.Hp - rr0);
+        float4* out = reinterpret_cast<float4*>(a.dst[slot] + (((int64_t)u * g.Wk + w) * a.Hp + rr0) * RF);
+        const float4* tin = reinterpret_cast<const float4*>(&tile[0][0]);
+        for (int i = threadIdx.x; i < nrows * (RF / 4); i += 128) out[i] = tin[i];
+        return;
+    }
+    // scalar planes: L and D = dy . y (or the given D); every thread sums its slab's 16 channels
+    float part = 0.f;
+    if (real_row && !a.Din) {
+        float dyv[16], yv[16];
+#pragma unroll
+        for (int cc = 0; cc < 16; ++cc) {
+            const int64_t o = goff<CPE, NCRT>(u, 16 * slab + cc, g.Npk, pix);
+            dyv[cc] = __ldg(a.dy + o);
+            yv[cc] = __ldg(a.y + o);
+        }
+#pragma unroll
+        for (int cc = 0; cc < 16; ++cc) part = fmaf(dyv[cc], yv[cc], part);
+    }
+    tile[rl][slab] = part;
+    __syncthreads();
+    if (slab != 0 || !in_rows) return;
+    float L = 0.f, D = 0.f;
+    if (real_row) {
+        const int64_t so = (int64_t)u * g.Npk + pix;
+        L = __ldg(a.stats + so) * a.stat_mul;
+        if (a.Din) {
+            D = __ldg(a.Din + so);
+        } else {
+#pragma unroll
+            for (int sl = 0; sl < NS; ++sl) D += tile[rl][sl];
+            if (a.Dout && rr >= a.pp && rr < a.pp + g.H) a.Dout[so] = D;
+        }
+    }
+    const int64_t plane = (int64_t)g.Wk * a.Hp;
+    a.planes[(2 * (int64_t)u) * plane + (int64_t)w * a.Hp + rr] = L;
+    a.planes[(2 * (int64_t)u + 1) * plane + (int64_t)w * a.Hp + rr] = D;
+}
+
 // ---------------------------------------------------------------- host side
 struct Padded {
     int pp, Hp;
@@ -1714,6 +1805,20 @@ int launch_pack(const PackArgs& a, cudaStream_t st) {
         } else {
             if (cr == 8) pack_rows_kernel<2, 8><<<grid2, 128, 0, st>>>(a);
             else pack_rows_kernel<2, 16><<<grid2, 128, 0, st>>>(a);
+        }
+        CA_CHECK_LAUNCH("pack kernel");
+        return CA_OK;
+    }
+    if (!a.single && (cr == 32 || cr == 64) && !a.g.bf16) {
+        // wide pairs: the shared-memory form with 128 / NS rows per block
+        const int rb = 128 / (cr / 16);
+        dim3 grid2((a.Hp + rb - 1) / rb, grid.y, a.g.units * (a.npairs + (a.planes ? 1 : 0)));
+        if (a.g.cpe == 1) {
+            if (cr == 32) pack_rows_wide_kernel<1, 32><<<grid2, 128, 0, st>>>(a);
+            else pack_rows_wide_kernel<1, 64><<<grid2, 128, 0, st>>>(a);
+        } else {
+            if (cr == 32) pack_rows_wide_kernel<2, 32><<<grid2, 128, 0, st>>>(a);
+            else pack_rows_wide_kernel<2, 64><<<grid2, 128, 0, st>>>(a);
         }
         CA_CHECK_LAUNCH("pack kernel");
         return CA_OK;
