@@ -78,3 +78,38 @@ def test_line_forward_needs_no_workspace(ca):
     for nrm in (ca.SOFTMAX, ca.ENTMAX15):
         d = m.desc(similarity=orc.DISTANCE, normalizer=nrm, scale=0.3)
         assert ca.ops.lib.ca_attention_fwd_workspace(d, 0) == 0
+
+
+def _random_cases(n, seed):
+    rng = np.random.default_rng(seed)
+    cases = []
+    for _ in range(n):
+        ws = int(rng.choice([5, 7, 9, 13, 21, 33, 63, 127]))
+        N = int(rng.integers(ws, 4 * ws + 1200))
+        cplx = bool(rng.integers(0, 2))
+        cper = int(rng.integers(1, 9 if cplx else 17))          # channels per head: up to 16 real
+        heads = int(rng.integers(1, 4))
+        cases.append(((N, cper * heads, int(rng.integers(1, 3))), ws, heads, cplx,
+                      ["dot", "distance"][int(rng.integers(0, 2))], ["softmax", "entmax"][int(rng.integers(0, 2))]))
+    return cases
+
+
+@pytest.mark.parametrize("shape,ws,nheads,cplx,simname,norm", _random_cases(14, 2024))
+def test_line_kernels_random_shapes(ca, shape, ws, nheads, cplx, simname, norm):
+    """Seeded random lengths, windows, channel counts (zero-extended to 8 or 16), heads, similarity and normaliser:
+    block tails, wraps shorter and longer than a block, every template instantiation."""
+    rng = np.random.default_rng(hash((shape, ws, nheads)) % (2 ** 32))
+    qn, kn, vn, rn = (randn(rng, shape, cplx, scale=1.2) for _ in range(4))
+    q, k, v = (ca.jl.from_numpy(t).requires_grad_(True) for t in (qn, kn, vn))
+    nrm, onorm = (ca.SOFTMAX, orc.SOFTMAX) if norm == "softmax" else (ca.ENTMAX15, orc.ENTMAX15)
+    before = ca._lib.lib.ca_probe_tiled_launch_count()
+    y, _ = ca.circulant_mh_attention(sim_of(ca, simname), q, k, v, ws, nheads, normalizer=nrm, return_A=False)
+    loss = (y * ca.jl.from_numpy(rn).conj()).real.sum() if cplx else (y * ca.jl.from_numpy(rn)).sum()
+    loss.backward()
+    assert ca._lib.lib.ca_probe_tiled_launch_count() - before == 3
+    yo, _ = orc.mh_attention(KIND[simname], up(qn), up(kn), up(vn), ws, nheads, onorm)
+    dqo, dko, dvo = orc.mh_attention_pullback(KIND[simname], up(qn), up(kn), up(vn), ws, nheads, up(rn), norm=onorm)
+    assert_close(ca.jl.to_numpy(y), yo, "y")
+    assert_close(ca.jl.to_numpy(q.grad), dqo, "dq", tol=2 * TOL, elem_tol=4e-5)
+    assert_close(ca.jl.to_numpy(k.grad), dko, "dk", tol=2 * TOL, elem_tol=4e-5)
+    assert_close(ca.jl.to_numpy(v.grad), dvo, "dv")
