@@ -66,22 +66,38 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+_NVTX = [False]
+
+
+def enable_nvtx(flag: bool = True) -> bool:
+    """NVTX ranges ("circatt.fwd", "circatt.bwd", "circatt.halo") around the library's calls, for timeline
+    profilers; off by default (a range costs two host calls).  Returns the previous setting."""
+    old, _NVTX[0] = _NVTX[0], bool(flag)
+    return old
+
+
 class _on_device:
     """`with _on_device(t.device)`: makes that device current for the C ABI calls inside, without the cost of
-    a device switch when it already is (the common case)."""
-    __slots__ = ("index", "prev")
+    a device switch when it already is (the common case).  With a `name` and NVTX enabled the block is also
+    an NVTX range."""
+    __slots__ = ("index", "prev", "name")
 
-    def __init__(self, device):
+    def __init__(self, device, name=None):
         self.index = device.index if device.index is not None else torch.cuda.current_device()
         self.prev = None
+        self.name = name if (name and _NVTX[0]) else None
 
     def __enter__(self):
         cur = torch.cuda.current_device()
         if cur != self.index:
             self.prev = cur
             torch.cuda.set_device(self.index)
+        if self.name:
+            torch.cuda.nvtx.range_push(self.name)
 
     def __exit__(self, *exc):
+        if self.name:
+            torch.cuda.nvtx.range_pop()
         if self.prev is not None:
             torch.cuda.set_device(self.prev)
         return False
@@ -259,7 +275,7 @@ def attention_fwd(kind, normalizer, q, k, v, ws, want_nz, scale=None, band=None,
     nz = jl.empty((m.Np * m.K, m.units), torch.float32, q.device) if want_nz else None
     stats = jl.empty((m.Np, m.units), torch.float32, q.device)
     nbytes = lib.ca_attention_fwd_workspace(d, int(want_nz))
-    with _on_device(q.device):
+    with _on_device(q.device, "circatt.fwd"):
         _status_word(q.device)
         if keep_workspace:
             wsb = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
@@ -279,7 +295,7 @@ def attention_bwd(kind, normalizer, q, k, v, y, dy, stats, ws, nz=None, dA=None,
     dq, dk, dv = (jl.empty(q.shape, q.dtype, q.device) for _ in range(3))
     if dA is not None:
         dA = jl.colmajor(dA)
-    with _on_device(q.device):
+    with _on_device(q.device, "circatt.bwd"):
         _status_word(q.device)
         wsb = _scratch("bwd", lib.ca_attention_bwd_workspace(d, int(dA is not None)), q.device)
         check(lib.ca_attention_bwd(d, ptr(q), ptr(k), ptr(v), ptr(y), ptr(dy), ptr(stats), ptr(nz), ptr(dA),

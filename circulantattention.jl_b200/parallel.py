@@ -185,7 +185,7 @@ def exchange_halos(xs, p: int, group=None, ring: "Ring" = None):
                 jobs.append((src, dst + p * col, Wb * col, outer, ss, ds))
                 jobs.append((src + (Wb - p) * col, dst, p * col, outer, ss, ds))
                 jobs.append((src, dst + (p + Wb) * col, p * col, outer, ss, ds))
-            with ops._on_device(device):
+            with ops._on_device(device, "circatt.halo"):
                 ops.copy_chunks(jobs)
         else:
             for t, ext in zip(ts, exts):
@@ -206,7 +206,7 @@ def exchange_halos(xs, p: int, group=None, ring: "Ring" = None):
                 jobs.append((src + (Wb - p) * col, to_right.data_ptr() + off * esize, p * col, outer, ss, p * col))
                 jobs.append((src, to_left.data_ptr() + off * esize, p * col, outer, ss, p * col))
                 off += n
-            with ops._on_device(device):
+            with ops._on_device(device, "circatt.halo"):
                 ops.copy_chunks(jobs)
         else:
             off = 0
@@ -238,7 +238,7 @@ def exchange_halos(xs, p: int, group=None, ring: "Ring" = None):
                 jobs.append((from_left.data_ptr() + off * esize, ext.data_ptr(), p * col, outer, p * col, ds))
                 jobs.append((from_right.data_ptr() + off * esize, ext.data_ptr() + (p + Wb) * col, p * col, outer, p * col, ds))
                 off += n
-            with ops._on_device(device):
+            with ops._on_device(device, "circatt.halo"):
                 ops.copy_chunks(jobs)
         else:
             off = 0

@@ -43,3 +43,15 @@ def test_captured_step_replays_like_the_eager_call(ca, shape, ws, nheads, norm):
         for got, w in zip((y, q.grad, k.grad, v.grad), want):
             assert torch.equal(got, w)                # the same kernels on the same values: bit-identical
     ca.ops.check_status(q.device)
+
+
+def test_nvtx_ranges_are_optional_and_harmless(ca):
+    """NVTX ranges around the fused calls: off by default, switchable, results unchanged."""
+    x = ca.jl.randn(64, 32, 16, 2)
+    y0, _, _ = ca.ops.attention_fwd(0, 0, x, x, x, 7, False)
+    assert ca.ops.enable_nvtx(True) is False
+    try:
+        y1, _, _ = ca.ops.attention_fwd(0, 0, x, x, x, 7, False)
+    finally:
+        assert ca.ops.enable_nvtx(False) is True
+    assert torch.equal(y0, y1)
