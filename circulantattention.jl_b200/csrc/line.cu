@@ -169,11 +169,30 @@ __device__ __forceinline__ void sweep(int tb, int ws, F&& f) {
     sweep_tail<NQ, 0>(f, tb, ws);
 }
 
+// One step of the entmax threshold search from the statistics of a sweep at the current tau, with t = z - tau:
+// n = |{t > 0}| (the support S), sa = sum_S t, sb = sum_S t^2, rmax = max 1/t = 1 / (smallest t > 0),
+// rmin = min 1/t = 1 / (largest t < 0).  Returns the step d that solves sum_S (t - d)^2 = 1 and sets `same` when
+// tau + d has the support S again (d < smallest t > 0, or d >= largest t < 0) -- then tau + d is exact for S -- and
+// the step was short against the distances it was computed from (a long step leaves tau with the rounding error
+// of those larger numbers: one more sweep, now around the new tau, removes it).  `late`: a row that keeps
+// changing its support takes Newton steps on f(tau) = sum max(z - tau, 0)^2 - 1 (convex: they converge from
+// either side).  An empty support cannot happen for tau < max; it ends the search where it is.
+__device__ __forceinline__ float tau_step(float n, float sa, float sb, float rmax, float rmin, bool late, bool& same) {
+    same = true;
+    if (n == 0.f) return 0.f;
+    const float disc = fmaxf(fmaf(sa, sa, -n * (sb - 1.f)), 0.f);
+    float d = (sa - sqrtf(disc)) / n;
+    same = (d >= 0.f ? d * rmax < 1.f : d * rmin <= 1.f) && d * n <= 0.75f * sa;
+    if (!same && late) d = 0.5f * (sb - 1.f) / sa;
+    return d;
+}
+
 // Scale of the stored scores: z = f * sim(q, k) is the log2-domain score (softmax) or s / 2 (entmax).
 template <bool ENT>
 __device__ __forceinline__ float score_factor(float scale) { return ENT ? 0.5f * scale : scale * kLog2e; }
 
 constexpr int kMaxTauSweeps = 24;
+constexpr int kNewtonAfter = 10;              // threshold steps before the search falls back to Newton steps
 constexpr unsigned kCoopRows = 16;            // open rows per warp (of 32 * NQ) below which the warp finishes them together
 constexpr float kLineHeadroom = 12.f;          // log2 units between the softmax reference and the score that set it
 
@@ -272,29 +291,13 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
                         rmin[r] = fminf(rmin[r], rt);
                     }
             });
-            bool all = true;
 #pragma unroll
             for (int r = 0; r < NQ; ++r)
                 if (!done[r]) {
-                    if (n[r] == 0.f) {          // cannot happen for tau < max; leave tau as it is
-                        done[r] = true;
-                    } else {
-                        const float disc = fmaxf(fmaf(sa[r], sa[r], -n[r] * (sb[r] - 1.f)), 0.f);
-                        float d = (sa[r] - sqrtf(disc)) / n[r];
-                        // final when the support reproduces itself and the step was short against the
-                        // distances it was computed from (a long step leaves tau with the rounding error
-                        // of those larger numbers: one more sweep, now around the new tau, removes it)
-                        // d < tmin  <=>  d * rmax < 1 (rmax > 0);  d >= tneg  <=>  d * rmin <= 1 (d, rmin < 0)
-                        const bool same = (d >= 0.f ? d * rmax[r] < 1.f : d * rmin[r] <= 1.f) && d * n[r] <= 0.75f * sa[r];
-                        // a row that keeps changing its support falls back to Newton steps on
-                        // f(tau) = sum max(z - tau, 0)^2 - 1 (convex, converges from either side)
-                        if (!same && it >= 10) d = 0.5f * (sb[r] - 1.f) / sa[r];
-                        off[r] += d;
-                        done[r] = same;
-                    }
-                    all = all && done[r];
+                    bool same;
+                    off[r] += tau_step(n[r], sa[r], sb[r], rmax[r], rmin[r], it >= kNewtonAfter, same);
+                    done[r] = same;
                 }
-            (void)all;
             // rows of this warp that are still open; when only a few are left (after the fourth sweep about
             // one row in a hundred), the warp finishes them one at a time, the window's keys spread over its
             // lanes, instead of sweeping all 32 * NQ rows again for their sake
@@ -341,12 +344,8 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_fwd_kernel(LineArgs
                             rmx = fmaxf(rmx, __shfl_xor_sync(0xffffffffu, rmx, m));
                             rmn = fminf(rmn, __shfl_xor_sync(0xffffffffu, rmn, m));
                         }
-                        if (n1 == 0.f) break;
-                        const float disc = fmaxf(fmaf(sa1, sa1, -n1 * (sb1 - 1.f)), 0.f);
-                        float d = (sa1 - sqrtf(disc)) / n1;
-                        const bool same = (d >= 0.f ? d * rmx < 1.f : d * rmn <= 1.f) && d * n1 <= 0.75f * sa1;
-                        if (!same && ci >= 10) d = 0.5f * (sb1 - 1.f) / sa1;
-                        tau += d;
+                        bool same;
+                        tau += tau_step(n1, sa1, sb1, rmx, rmn, ci >= kNewtonAfter, same);
                         if (same) break;
                     }
                     if (lane == src) {
@@ -618,11 +617,6 @@ __global__ void __launch_bounds__(kLT, CR <= 8 ? 3 : 2) line_dkdv_kernel(LineArg
 }
 
 // ------------------------------------------------------------------------------------------------ host
-struct LinePlan {
-    int CR, NQ;
-    size_t smem_fwd, smem_bwd;
-};
-
 int prepare(LineArgs& a, int nq, int groups, int scalar_planes, size_t* smem) {
     a.P = kLT * nq + a.g.ws - 1;
     a.PP = a.P + (a.P - 1) / nq + 1;
