@@ -2136,6 +2136,10 @@ int tiled_attention_fwd(const Geo& gin, float scale, int dist, const float* q, c
     // instructions of the 7 x 7 forward), else chunks of 4 with checks
     if (ns == 2 && nq == 2 && g.ws % 7 == 0) CA_FWD2(7, true, 2, 32);
     else if (ns == 4 && nq == 2 && g.ws % 7 == 0) CA_FWD2(7, true, 2, 64);
+    else if (ns == 2 && nq == 4 && g.ws % 7 == 0) CA_FWD2(7, true, 4, 32);       // windows 21, 35, 49, 63
+    else if (ns == 4 && nq == 4 && g.ws % 7 == 0) CA_FWD2(7, true, 4, 64);
+    else if (ns == 2 && nq == 4 && g.ws % 5 == 0) CA_FWD2(5, true, 4, 32);       // windows 15, 25, 45, 55
+    else if (ns == 4 && nq == 4 && g.ws % 5 == 0) CA_FWD2(5, true, 4, 64);
     else if (ns == 2 && nq == 2) CA_FWD2(4, false, 2, 32);
     else if (ns == 2) CA_FWD2(4, false, 4, 32);
     else if (ns == 4 && nq == 2) CA_FWD2(4, false, 2, 64);

@@ -72,6 +72,8 @@ CASES = [
     ((37, 29, 16, 2), 9, 2, False),      # 8 channels per head: fused kernels on zero-extended units
     ((40, 21, 8, 2), 7, 2, True),        # 4 complex = 8 real channels per head
     ((256, 16, 2), 9, 2, False),         # 1-D, 8 channels per head
+    ((40, 34, 64, 1), 15, 2, False),     # 32 channels per head, window 15: unchecked chunks of 5 keys
+    ((44, 40, 64, 1), 21, 1, False),     # 64 channels per head, window 21: unchecked chunks of 7 keys
     ((32, 30, 32, 1), 29, 1, False),     # 32 channels per unit, window 29: wide units on the fused kernels
     ((34, 33, 64, 1), 31, 1, False),     # 64 channels per unit, window 31
     ((128, 32, 2), 33, 1, False),        # 1-D, 32 channels per unit
