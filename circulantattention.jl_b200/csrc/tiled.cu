@@ -466,6 +466,31 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
     }
 }
 
+// The ws keys of one window column.  EXACT: ws is a multiple of DC.  Otherwise (DC == 4): chunks of four keys, then
+// the remaining one to three keys as one chunk of exactly that length, so that no chunk carries bounds checks
+// (a checked chunk keeps its prefetched vector alive across branches, which costs a register copy per loaded
+// word and made windows such as 13 slower than 15).
+template <int DC, bool DIST, bool EXACT, int NQ, int NS>
+__device__ __forceinline__ void fwd_window(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[NQ][8],
+                                           u64 (&acc)[NQ][8], u64 (&nm2)[NQ], float (&l)[NQ], const float (&bq)[NQ],
+                                           int slab) {
+    constexpr int FULLM = (1 << NQ) - 1;
+    if (EXACT) {
+        fwd_stage<DC, DIST, FULLM, true, NQ, NS>(rowbase, ws, rm, sl2, q, acc, nm2, l, bq, slab);
+        return;
+    }
+    static_assert(EXACT || DC == 4, "windows without a dividing chunk length run chunks of four plus a tail");
+    const int main = ws & ~3;
+    fwd_stage<4, DIST, FULLM, true, NQ, NS>(rowbase, main, rm, sl2, q, acc, nm2, l, bq, slab);
+    const uint32_t tail = rowbase + main * (kRowBytes * NS);
+    switch (ws - main) {                                     // warp-uniform
+        case 1: fwd_stage<1, DIST, FULLM, true, NQ, NS>(tail, 1, rm, sl2, q, acc, nm2, l, bq, slab); break;
+        case 2: fwd_stage<2, DIST, FULLM, true, NQ, NS>(tail, 2, rm, sl2, q, acc, nm2, l, bq, slab); break;
+        case 3: fwd_stage<3, DIST, FULLM, true, NQ, NS>(tail, 3, rm, sl2, q, acc, nm2, l, bq, slab); break;
+        default: break;
+    }
+}
+
 // First score of each centre pixel that starts in this stage: the reference
 // point of its running maximum.
 template <bool DIST, int NQ, int NS = 1>
@@ -544,12 +569,12 @@ __global__ void __launch_bounds__(128, (NQ <= 2 ? 3 : 2)) fwd_tiled_kernel(TileA
             u64 nmE[NQ];
 #pragma unroll
             for (int r = 0; r < NQ; ++r) nmE[r] = ((mask >> r) & 1) ? nm2[r] : pack2(-INFINITY, 0.f);
-            fwd_stage<DC, DIST, (1 << NQ) - 1, EXACT, NQ, NS>(rowbase, g.ws, mask, sl2, q, acc, nmE, l, bq, slab);
+            fwd_window<DC, DIST, EXACT, NQ, NS>(rowbase, g.ws, mask, sl2, q, acc, nmE, l, bq, slab);
 #pragma unroll
             for (int r = 0; r < NQ; ++r)
                 if ((mask >> r) & 1) nm2[r] = nmE[r];
         } else {
-            fwd_stage<DC, DIST, (1 << NQ) - 1, EXACT, NQ, NS>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq, slab);
+            fwd_window<DC, DIST, EXACT, NQ, NS>(rowbase, g.ws, mask, sl2, q, acc, nm2, l, bq, slab);
         }
     })
 
@@ -1782,15 +1807,6 @@ int tune_int(const char* name, int dflt) {
 inline int tune_int(const char*, int dflt) { return dflt; }
 #endif
 
-int pick_dc(int ws) {
-    int best = 5, waste = 1 << 30;
-    for (int dc : {3, 4, 5, 7}) {
-        const int w = (ws + dc - 1) / dc * dc - ws;
-        if (w < waste || (w == waste && dc > best)) { waste = w; best = dc; }
-    }
-    return best;
-}
-
 int launch_pack(const PackArgs& a, cudaStream_t st) {
     dim3 grid((a.Hp + 127) / 128, a.g.Wk, a.g.units * ((a.single ? 1 : 2) * a.npairs + (a.planes ? 1 : 0)));
     const int cr = a.g.cr;
@@ -2110,7 +2126,6 @@ int tiled_attention_fwd(const Geo& gin, float scale, int dist, const float* q, c
     const int nq = g.ws <= 9 ? tune_int("CIRCATT_FWD_NQ", 2) : (ns > 1 ? 4 : pick_nq(g, 4, 2, "CIRCATT_FWD_NQ"));
     if ((rc = prepare(g, P, nq, 18 * nq, "CIRCATT_FWD_WARPS", kv, nullptr, &L, ns == 1, 4, ns))) return rc;
     L.a.scale = scale; L.a.c0 = q; L.a.o0 = y; L.a.ostats = stats;
-    const int dc = ns > 1 ? 4 : pick_dc(g.ws);
 #define CA_FWD2(DCV, EX, NQV, NCRV_)                                                            \
     do {                                                                                 \
         if (g.cpe == 1) {                                                                \
@@ -2123,17 +2138,10 @@ int tiled_attention_fwd(const Geo& gin, float scale, int dist, const float* q, c
     } while (0)
 #define CA_FWD(DCV)                                                                      \
     do {                                                                                 \
-        if (nq == 2) {                                                                   \
-            if (g.ws % DCV == 0) CA_FWD2(DCV, true, 2, 16);                              \
-            else CA_FWD2(DCV, false, 2, 16);                                             \
-        } else {                                                                         \
-            if (g.ws % DCV == 0) CA_FWD2(DCV, true, 4, 16);                              \
-            else CA_FWD2(DCV, false, 4, 16);                                             \
-        }                                                                                \
+        if (nq == 2) CA_FWD2(DCV, true, 2, 16);                                          \
+        else CA_FWD2(DCV, true, 4, 16);                                                  \
     } while (0)
-    // wide units: chunks of 7 keys without bounds checks where the window is a multiple of 7 (the checked form
-    // keeps its prefetched vector alive across branches, which costs a register copy per loaded word: 22 % of the
-    // instructions of the 7 x 7 forward), else chunks of 4 with checks
+    // wide units: chunks of 7 or 5 keys where they divide the window, else chunks of four plus a tail
     if (ns == 2 && nq == 2 && g.ws % 7 == 0) CA_FWD2(7, true, 2, 32);
     else if (ns == 4 && nq == 2 && g.ws % 7 == 0) CA_FWD2(7, true, 2, 64);
     else if (ns == 2 && nq == 4 && g.ws % 7 == 0) CA_FWD2(7, true, 4, 32);       // windows 21, 35, 49, 63
@@ -2144,12 +2152,11 @@ int tiled_attention_fwd(const Geo& gin, float scale, int dist, const float* q, c
     else if (ns == 2) CA_FWD2(4, false, 4, 32);
     else if (ns == 4 && nq == 2) CA_FWD2(4, false, 2, 64);
     else if (ns == 4) CA_FWD2(4, false, 4, 64);
-    else switch (dc) {
-        case 3: CA_FWD(3); break;
-        case 4: CA_FWD(4); break;
-        case 7: CA_FWD(7); break;
-        default: CA_FWD(5); break;
-    }
+    else if (g.ws % 7 == 0) CA_FWD(7);
+    else if (g.ws % 5 == 0) CA_FWD(5);
+    else if (g.ws % 3 == 0) CA_FWD(3);
+    else if (nq == 2) CA_FWD2(4, false, 2, 16);
+    else CA_FWD2(4, false, 4, 16);
 #undef CA_FWD2
 #undef CA_FWD
     CA_CHECK_LAUNCH("tiled forward kernel");
