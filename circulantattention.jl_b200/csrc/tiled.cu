@@ -360,7 +360,7 @@ constexpr float kHeadroom = 12.f;
 // NS lanes share a pixel (units of 16*NS real channels): every lane holds one 16-channel slab of q and
 // of the accumulator, scores are the lane sums of the per-slab partial dot products, and the terms that
 // enter a score once (the running reference, in nm2) sit on slab 0 only.
-template <int DC, bool DIST, int MASK, bool EXACT, int NQ, int NS = 1>
+template <int DC, bool DIST, int MASK, int NQ, int NS = 1>
 __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, float sl2, const u64 (&q)[NQ][8],
                                           u64 (&acc)[NQ][8], u64 (&nm2)[NQ], float (&l)[NQ], const float (&bq)[NQ],
                                           int slab = 0) {
@@ -373,11 +373,11 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
         lds_slab16<NS>(cb, 0, slab, nxt);
 #pragma unroll
         for (int t = 0; t < DC; ++t) {
-            if (EXACT || c0 + t < ws) {
+            {
                 u64 k2[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) k2[i] = nxt[i];
-                if (t + 1 < DC && (EXACT || c0 + t + 1 < ws)) lds_slab16<NS>(cb + (t + 1) * RB, 0, slab, nxt);
+                if (t + 1 < DC) lds_slab16<NS>(cb + (t + 1) * RB, 0, slab, nxt);
                 else lds_slab16<NS>(cb, 1, slab, nxt);
                 float bk = 0.f;
                 if (DIST) {
@@ -413,9 +413,6 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
                             sc[r][t] = -INFINITY;
                         }
                 }
-            } else {
-#pragma unroll
-                for (int r = 0; r < NQ; ++r) sc[r][t] = -INFINITY;
             }
         }
         // any relative score >= 0 ?  (sign bit clear)
@@ -447,11 +444,11 @@ __device__ __forceinline__ void fwd_stage(uint32_t rowbase, int ws, int rm, floa
         }
 #pragma unroll
         for (int t = 0; t < DC; ++t) {
-            if (EXACT || c0 + t < ws) {
+            {
                 u64 v2[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v2[i] = nxt[i];
-                if (t + 1 < DC && (EXACT || c0 + t + 1 < ws)) lds_slab16<NS>(cb + (t + 1) * RB, 1, slab, nxt);
+                if (t + 1 < DC) lds_slab16<NS>(cb + (t + 1) * RB, 1, slab, nxt);
 #pragma unroll
                 for (int r = 0; r < NQ; ++r)
                     if (CA_ON(r)) {
@@ -476,17 +473,17 @@ __device__ __forceinline__ void fwd_window(uint32_t rowbase, int ws, int rm, flo
                                            int slab) {
     constexpr int FULLM = (1 << NQ) - 1;
     if (EXACT) {
-        fwd_stage<DC, DIST, FULLM, true, NQ, NS>(rowbase, ws, rm, sl2, q, acc, nm2, l, bq, slab);
+        fwd_stage<DC, DIST, FULLM, NQ, NS>(rowbase, ws, rm, sl2, q, acc, nm2, l, bq, slab);
         return;
     }
     static_assert(EXACT || DC == 4, "windows without a dividing chunk length run chunks of four plus a tail");
     const int main = ws & ~3;
-    fwd_stage<4, DIST, FULLM, true, NQ, NS>(rowbase, main, rm, sl2, q, acc, nm2, l, bq, slab);
+    fwd_stage<4, DIST, FULLM, NQ, NS>(rowbase, main, rm, sl2, q, acc, nm2, l, bq, slab);
     const uint32_t tail = rowbase + main * (kRowBytes * NS);
     switch (ws - main) {                                     // warp-uniform
-        case 1: fwd_stage<1, DIST, FULLM, true, NQ, NS>(tail, 1, rm, sl2, q, acc, nm2, l, bq, slab); break;
-        case 2: fwd_stage<2, DIST, FULLM, true, NQ, NS>(tail, 2, rm, sl2, q, acc, nm2, l, bq, slab); break;
-        case 3: fwd_stage<3, DIST, FULLM, true, NQ, NS>(tail, 3, rm, sl2, q, acc, nm2, l, bq, slab); break;
+        case 1: fwd_stage<1, DIST, FULLM, NQ, NS>(tail, 1, rm, sl2, q, acc, nm2, l, bq, slab); break;
+        case 2: fwd_stage<2, DIST, FULLM, NQ, NS>(tail, 2, rm, sl2, q, acc, nm2, l, bq, slab); break;
+        case 3: fwd_stage<3, DIST, FULLM, NQ, NS>(tail, 3, rm, sl2, q, acc, nm2, l, bq, slab); break;
         default: break;
     }
 }
